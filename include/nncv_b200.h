@@ -1,0 +1,165 @@
+/* C ABI of libnncv_b200.so: the sm_100a (B200) implementation of nncv's compiled vision-model
+ * forward pass behind nncv's own runtime surface.
+ *
+ * Every entry point takes plain pointers and sizes.  Citations name the interface of the nncv
+ * source tree that each declaration replaces or mirrors.
+ *
+ * Threading: calls are serialised by one library-wide mutex.  One model is loaded per process
+ * and lives on the CUDA device that was current when it was loaded (one process per GPU).
+ * There is no CPU fallback: every compute entry point fails with NNCV_B200_ENODEVICE when no
+ * sm_100 device is usable.
+ */
+#ifndef NNCV_B200_H_
+#define NNCV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- descriptors: nncv::rt::MemRefDescriptor<T,N>, include/libnncv/DataType.hpp:129-136.
+ * Strides count elements.  T is float, or uint16_t carrying fp16 bits (DataType.hpp:124-127). */
+typedef struct {
+  void* allocated;
+  void* aligned;
+  intptr_t offset;
+  intptr_t sizes[1];
+  intptr_t strides[1];
+} nncv_memref1;
+typedef struct {
+  void* allocated;
+  void* aligned;
+  intptr_t offset;
+  intptr_t sizes[2];
+  intptr_t strides[2];
+} nncv_memref2;
+typedef struct {
+  void* allocated;
+  void* aligned;
+  intptr_t offset;
+  intptr_t sizes[4];
+  intptr_t strides[4];
+} nncv_memref4;
+
+/* ---- split-params container records, include/libnncv/DataType.hpp:144-162 (224 and 24 bytes). */
+typedef struct {
+  char name[128];
+  size_t dims;
+  size_t shape[8];
+  size_t eleWidth;
+  size_t aligned;
+  size_t dataOffset;
+} nncv_memref_indexer;
+typedef struct {
+  int64_t magicNumber; /* 0x42 */
+  size_t memRefIndexStartOffset;
+  size_t numMemRefIndex;
+} nncv_memref_magic_head;
+
+/* ---- status codes (the reference returns void / bool and exits on error,
+ * src/nncv/compiler/Pipeline/DnnModelLowering.cpp:222-230, src/libnncv/DataType.cpp:55-59). */
+enum {
+  NNCV_B200_OK = 0,
+  NNCV_B200_EINVAL = 1,     /* bad argument, shape, stride or dtype */
+  NNCV_B200_EIO = 2,        /* file missing, truncated, bad magic */
+  NNCV_B200_ENODEVICE = 3,  /* no usable sm_100 device / CUDA error at start-up */
+  NNCV_B200_ECUDA = 4,      /* CUDA runtime error during a call */
+  NNCV_B200_ENOMODEL = 5,   /* forward called with no model loaded and params unusable */
+  NNCV_B200_ETIMEOUT = 6,   /* a bounded device-side wait ran out (kernel reported it) */
+  NNCV_B200_ENOMEM = 7
+};
+
+enum { NNCV_B200_F32 = 0, NNCV_B200_F16 = 1, NNCV_B200_BF16 = 2 };
+
+typedef struct {
+  int compute_dtype; /* NNCV_B200_F32 (CUDA-core fp32 path), _F16 or _BF16 (tcgen05 path);
+                        -1 = follow the params file: eleWidth 4 -> F32, 2 -> F16 */
+  int reserved[7];
+} nncv_b200_opts;
+
+/* ---- the drop-in boundary --------------------------------------------------------------
+ * examples/Res18/main.cpp:18-23: the C-interface wrapper MLIR emits for @forward under
+ * -wrap-c-interface (DnnModelLowering.cpp:769-771) with the split-params argument inserted as
+ * function argument #1 (SplitParamsFlatArray.cpp:189-192).
+ *   dst    [N,1000] logits, written in place at dst->aligned + dst->offset (strides honoured).
+ *          If dst->aligned is NULL the buffer is malloc'ed and the descriptor filled in.
+ *   src    [N,3,H,W] dense NCHW.  N is taken from the descriptor at run time.
+ *   params nncv_memref1* over the whole parameter blob (what MemRefFlatArray::get() returns,
+ *          DataType.hpp:179, DataType.cpp:89-119).  If no model is loaded yet, a ResNet-18 (or
+ *          ResNet-50, by element count) plan is built from this blob on first use.
+ * dst / src may point to host memory (as in the reference) or to device memory of the model's
+ * GPU; element type is float when the params are 4 bytes wide, fp16 bits when 2 bytes wide.
+ * Returns void like the reference; the outcome is in nncv_b200_last_status(). */
+void _mlir_ciface_forward(nncv_memref2* dst, nncv_memref4* src, void* params);
+
+/* Weight loading: the counterpart of `nncv-c -split-params` + MemRefFlatArray::read
+ * (src/nncv/compiler/main.cpp:102-103, src/libnncv/DataType.cpp:48-87): parses the container,
+ * checks it against the named network ("resnet18" or "resnet50"), uploads the blob once, folds
+ * batch-norm into per-channel scale/shift and packs the conv/FC weights for the kernels. */
+int nncv_b200_load(const char* net, const char* model_bin_path, const nncv_b200_opts* opts);
+/* Same, from a blob already in host memory (tensors back to back in file order). */
+int nncv_b200_load_blob(const char* net, const void* blob, size_t n_elements, size_t ele_width,
+                        const nncv_b200_opts* opts);
+int nncv_b200_unload(void);
+/* Forward with an explicit CUDA stream and device-resident src/dst; does not synchronise.
+ * The same computation as _mlir_ciface_forward without the host copies. */
+int nncv_b200_forward_device(nncv_memref2* dst, nncv_memref4* src, void* cuda_stream);
+int nncv_b200_last_status(void);
+const char* nncv_b200_last_error(void);
+/* Number of kernels of this library launched since load (for benchmark accounting). */
+long long nncv_b200_launch_count(void);
+
+/* ---- container reader / writer: MemRefFlatArray::read/write, DataType.cpp:9-87 ----------
+ * read: returns a handle (NULL on error); tensors are addressed by index in file order. */
+typedef struct nncv_flat_array nncv_flat_array;
+nncv_flat_array* nncv_flat_array_read(const char* path);
+void nncv_flat_array_free(nncv_flat_array* a);
+size_t nncv_flat_array_count(const nncv_flat_array* a);
+const nncv_memref_indexer* nncv_flat_array_indexer(const nncv_flat_array* a, size_t i);
+const void* nncv_flat_array_data(const nncv_flat_array* a, size_t i);
+/* The rank-1 descriptor over the whole blob (MemRefFlatArray::wrap, DataType.cpp:89-119). */
+nncv_memref1* nncv_flat_array_wrapped(nncv_flat_array* a);
+int nncv_flat_array_write(const char* path, size_t n, const nncv_memref_indexer* indexers,
+                          const void* const* data);
+
+/* ---- single kernels (device pointers; `stream` is a cudaStream_t; no synchronisation) ----
+ * linalg.matmul C[M,N] = A[M,K] * B[K,N], row-major (tests/MatMulOptimization/MatMulNv.mlir:6-9),
+ * optional bias[N] (fp32) and ReLU.  ab_dtype F16/BF16: tcgen05 with fp32 accumulate, K % 8 == 0;
+ * ab_dtype F32: CUDA-core fp32.  c_dtype is F32 or ab_dtype.  B is repacked into a scratch
+ * buffer owned by the library (grown with cudaMalloc on demand). */
+int nncv_b200_matmul(const void* A, const void* B, void* C, int M, int N, int K, int ab_dtype,
+                     int c_dtype, const float* bias, int relu, void* stream);
+
+/* linalg.conv_2d_nchw_fchw (tests/Nets/Res18.mlir:125) + folded batch-norm / residual / ReLU
+ * epilogue, on NHWC activations.  Weights are prepared once into a plan. */
+typedef struct nncv_b200_conv nncv_b200_conv;
+/* weights: host or device [Kout,C,R,S] of w_dtype.  dtype: activation type (F16/BF16 -> tcgen05
+ * implicit GEMM, F32 -> CUDA-core).  algo: 0 = implicit GEMM, 1 = Winograd F(2x2,3x3) (3x3
+ * stride-1 pad-1 only).  Activation channel count is C rounded up to 8 (F16/BF16) or 4 (F32). */
+nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout, int C, int R,
+                                      int S, int stride, int pad, int dtype, int algo);
+void nncv_b200_conv_destroy(nncv_b200_conv* c);
+/* in [N,H,W,Cpad], out/residual [N,OH,OW,Kout]; scale/shift fp32 [Kout] or NULL. */
+int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int H, int W,
+                       const float* scale, const float* shift, const void* residual, int relu,
+                       void* stream);
+
+/* tensor.pad(-inf) + linalg.pooling_nchw_max (Res18.mlir:144-151), NHWC. */
+int nncv_b200_maxpool_nhwc(const void* in, void* out, int dtype, int N, int H, int W, int C,
+                           int k, int stride, int pad, void* stream);
+/* linalg.pooling_nchw_sum over the map + divf (Res18.mlir:606-614), NHWC -> [N,C]. */
+int nncv_b200_avgpool_nhwc(const void* in, void* out, int dtype, int N, int HW, int C,
+                           void* stream);
+/* NCHW -> NHWC with channels zero-padded to Cpad. */
+int nncv_b200_nchw_to_nhwc(const void* in, int in_dtype, void* out, int out_dtype, int N, int C,
+                           int H, int W, int Cpad, void* stream);
+/* Batch-norm folding (Res18.mlir:127-137): scale = gamma*rsqrt(var+1e-5f), shift = beta-mean*scale. */
+int nncv_b200_bn_fold(const void* gamma, const void* beta, const void* mean, const void* var,
+                      int dtype, int C, float* scale, float* shift, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNCV_B200_H_ */

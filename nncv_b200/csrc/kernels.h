@@ -1,0 +1,84 @@
+// Internal launch interface between the host runtime and the CUDA kernels.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace nncv_b200 {
+
+enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
+
+inline size_t dtype_size(DType t) { return t == kF32 ? 4 : 2; }
+
+// Error words a kernel can leave in the device-side status flag.
+enum KernelError : int {
+  kErrNone = 0,
+  kErrWaitProducer = 1,  // A-tile producer gave up waiting for a free stage
+  kErrWaitLoader = 2,    // weight loader gave up waiting for a free stage
+  kErrWaitMma = 3,       // MMA issuer gave up waiting for a full stage
+  kErrWaitEpilogue = 4,  // epilogue gave up waiting for the accumulator
+};
+
+// ---- implicit-GEMM convolution / GEMM on tcgen05 ---------------------------------------
+// Activations NHWC with C a multiple of 8, weights packed by launch_pack_weights().
+struct IgemmArgs {
+  const void* in = nullptr;        // [N,H,W,C] fp16/bf16
+  const void* wpack = nullptr;     // packed weight tiles
+  const float* scale = nullptr;    // [Kout] or null (=1)
+  const float* shift = nullptr;    // [Kout] or null (=0)
+  const void* residual = nullptr;  // [M,ldo] same type as in, or null
+  void* out = nullptr;             // [M,ldo] out_dtype
+  int N = 0, H = 0, W = 0, C = 0, OH = 0, OW = 0, Kout = 0, R = 1, S = 1, stride = 1, pad = 0;
+  long long ldo = 0;               // output row pitch in elements (>= Kout)
+  int bn = 64;                     // N tile the weights were packed for (64, 128 or 256)
+  DType ab = kF16;                 // operand type (kF16 or kBF16)
+  DType out_dtype = kF16;          // kF16/kBF16 (same as ab) or kF32
+  int relu = 0;
+  int* error_flag = nullptr;       // device int, receives a KernelError on a timed-out wait
+};
+
+int igemm_k_blocks(int C, int R, int S);
+size_t packed_weight_bytes(int Kout, int C, int R, int S, int bn);
+int igemm_pick_bn(long long M, int Kout);
+cudaError_t launch_conv_igemm(const IgemmArgs& a, cudaStream_t stream);
+
+// Packs weights W[n][c][tap] (element strides sn, sc, stap; type src_dt) into the tile image
+// the kernel bulk-copies to shared memory: k index = tap * Cpad + c, zero padded.
+cudaError_t launch_pack_weights(const void* src, DType src_dt, long long sn, long long sc,
+                                long long stap, int Kout, int C, int Cpad, int taps, int bn,
+                                DType dst_dt, void* dst, cudaStream_t stream);
+
+// ---- fp32 SIMT implicit-GEMM convolution (the fp32-accurate path) ------------------------
+struct SimtConvArgs {
+  const float* in = nullptr;        // [N,H,W,C] fp32, C % 4 == 0
+  const float* w = nullptr;         // [Kout][R][S][C] fp32
+  const float* scale = nullptr;
+  const float* shift = nullptr;
+  const float* residual = nullptr;  // [M,ldo]
+  float* out = nullptr;             // [M,ldo]
+  int N = 0, H = 0, W = 0, C = 0, OH = 0, OW = 0, Kout = 0, R = 1, S = 1, stride = 1, pad = 0;
+  long long ldo = 0;
+  int relu = 0;
+};
+cudaError_t launch_conv_simt_f32(const SimtConvArgs& a, cudaStream_t stream);
+// W[n][c][tap] (strides) -> [Kout][taps][Cpad] fp32
+cudaError_t launch_repack_weights_f32(const void* src, DType src_dt, long long sn, long long sc,
+                                      long long stap, int Kout, int C, int Cpad, int taps,
+                                      float* dst, cudaStream_t stream);
+
+// ---- memory-bound helpers (NHWC, 128-bit accesses) ---------------------------------------
+cudaError_t launch_nchw_to_nhwc(const void* src, DType src_dt, void* dst, DType dst_dt, int N,
+                                int C, int H, int W, int Cpad, cudaStream_t stream);
+cudaError_t launch_maxpool_nhwc(const void* src, void* dst, DType dt, int N, int H, int W, int C,
+                                int k, int stride, int pad, cudaStream_t stream);
+cudaError_t launch_avgpool_nhwc(const void* src, void* dst, DType dt, int N, int HW, int C,
+                                cudaStream_t stream);
+// scale = gamma * rsqrt(var + 1e-5f); shift = beta - mean * scale  (inputs of type dt)
+cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean,
+                           const void* var, DType dt, int C, float* scale, float* shift,
+                           cudaStream_t stream);
+cudaError_t launch_convert(const void* src, DType src_dt, void* dst, DType dst_dt, size_t n,
+                           cudaStream_t stream);
+
+}  // namespace nncv_b200

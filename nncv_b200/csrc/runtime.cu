@@ -1,0 +1,852 @@
+// Host runtime of libnncv_b200.so: the split-params container reader/writer, the params
+// uploader (batch-norm folding, weight packing), the device executor that runs the ResNet
+// forward as a sequence of kernels, and the C ABI declared in include/nncv_b200.h.
+//
+// It takes the place of nncv's libnncv runtime (src/libnncv/DataType.cpp, include/libnncv/
+// DataType.hpp) plus the body MLIR would have generated for @forward (tests/Nets/Res18.mlir).
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/nncv_b200.h"
+#include "kernels.h"
+
+using namespace nncv_b200;
+
+// =====================================================================================
+// status
+// =====================================================================================
+namespace {
+
+thread_local int g_status = NNCV_B200_OK;
+thread_local char g_msg[512] = "";
+std::mutex g_mutex;
+long long g_launches = 0;
+
+int fail(int code, const char* fmt, ...) {
+  g_status = code;
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_msg, sizeof(g_msg), fmt, ap);
+  va_end(ap);
+  return code;
+}
+int ok() {
+  g_status = NNCV_B200_OK;
+  g_msg[0] = 0;
+  return NNCV_B200_OK;
+}
+
+#define CU(call)                                                                          \
+  do {                                                                                    \
+    cudaError_t e__ = (call);                                                             \
+    if (e__ != cudaSuccess)                                                               \
+      return fail(NNCV_B200_ECUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__), \
+                  __FILE__, __LINE__);                                                    \
+  } while (0)
+#define LAUNCH(call)                                                                      \
+  do {                                                                                    \
+    ++g_launches;                                                                         \
+    CU(call);                                                                             \
+  } while (0)
+
+// =====================================================================================
+// device context
+// =====================================================================================
+struct Device {
+  bool ready = false;
+  int id = -1;
+  cudaStream_t stream = nullptr;
+  int* error_flag = nullptr;   // device
+  void* scratch = nullptr;     // grow-only scratch (packed B of nncv_b200_matmul)
+  size_t scratch_bytes = 0;
+};
+Device g_dev;
+
+int device_init() {
+  if (g_dev.ready) return NNCV_B200_OK;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return fail(NNCV_B200_ENODEVICE, "no CUDA device: %s (this library has no CPU fallback)",
+                cudaGetErrorString(e));
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(NNCV_B200_ENODEVICE, "cudaGetDevice failed");
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess)
+    return fail(NNCV_B200_ENODEVICE, "cudaGetDeviceProperties failed");
+  if (prop.major != 10)
+    return fail(NNCV_B200_ENODEVICE, "device %d is sm_%d%d; the kernels are built for sm_100a only",
+                dev, prop.major, prop.minor);
+  g_dev.id = dev;
+  if (cudaStreamCreateWithFlags(&g_dev.stream, cudaStreamNonBlocking) != cudaSuccess)
+    return fail(NNCV_B200_ENODEVICE, "cudaStreamCreate failed");
+  if (cudaMalloc(&g_dev.error_flag, sizeof(int)) != cudaSuccess)
+    return fail(NNCV_B200_ENOMEM, "cudaMalloc(error flag) failed");
+  cudaMemset(g_dev.error_flag, 0, sizeof(int));
+  g_dev.ready = true;
+  return NNCV_B200_OK;
+}
+
+int ensure_scratch(size_t bytes) {
+  if (bytes <= g_dev.scratch_bytes) return NNCV_B200_OK;
+  if (g_dev.scratch) {
+    cudaDeviceSynchronize();
+    cudaFree(g_dev.scratch);
+    g_dev.scratch = nullptr;
+    g_dev.scratch_bytes = 0;
+  }
+  const size_t want = (bytes + (1u << 20) - 1) & ~((size_t)(1u << 20) - 1);
+  if (cudaMalloc(&g_dev.scratch, want) != cudaSuccess)
+    return fail(NNCV_B200_ENOMEM, "cudaMalloc(%zu) for scratch failed", want);
+  g_dev.scratch_bytes = want;
+  return NNCV_B200_OK;
+}
+
+// Reads and clears the device-side status word; call after the stream has been synchronised.
+int check_kernel_status() {
+  int flag = 0;
+  CU(cudaMemcpy(&flag, g_dev.error_flag, sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag != 0) {
+    cudaMemset(g_dev.error_flag, 0, sizeof(int));
+    return fail(NNCV_B200_ETIMEOUT, "a kernel gave up a bounded wait (code %d)", flag);
+  }
+  return NNCV_B200_OK;
+}
+
+bool is_device_ptr(const void* p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+struct DevBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+  ~DevBuf() { if (p) cudaFree(p); }
+  DevBuf() = default;
+  DevBuf(const DevBuf&) = delete;
+  DevBuf& operator=(const DevBuf&) = delete;
+  int reserve(size_t n) {
+    if (n <= bytes) return NNCV_B200_OK;
+    if (p) { cudaFree(p); p = nullptr; bytes = 0; }
+    if (cudaMalloc(&p, n) != cudaSuccess) return fail(NNCV_B200_ENOMEM, "cudaMalloc(%zu) failed", n);
+    bytes = n;
+    return NNCV_B200_OK;
+  }
+};
+
+}  // namespace
+
+// =====================================================================================
+// convolution plan
+// =====================================================================================
+struct nncv_b200_conv {
+  int Kout = 0, C = 0, R = 1, S = 1, stride = 1, pad = 0;
+  int Cpad = 0;
+  DType dtype = kF16;  // activation / operand type
+  int algo = 0;
+  // raw weights on the device, element strides for W[n][c][tap]
+  const void* raw = nullptr;
+  DType raw_dt = kF32;
+  long long sn = 0, sc = 0, stap = 0;
+  DevBuf raw_owned;                                // set when create() copied the weights
+  std::map<int, std::unique_ptr<DevBuf>> packed;   // tcgen05 path: per N-tile width
+  DevBuf w_f32;                                    // fp32 path: [Kout][R*S][Cpad]
+  bool w_f32_ready = false;
+};
+
+namespace {
+
+int conv_prepare(nncv_b200_conv* c, int bn, cudaStream_t st, const void** wpack) {
+  auto it = c->packed.find(bn);
+  if (it == c->packed.end()) {
+    auto buf = std::make_unique<DevBuf>();
+    int rc = buf->reserve(packed_weight_bytes(c->Kout, c->Cpad, c->R, c->S, bn));
+    if (rc) return rc;
+    LAUNCH(launch_pack_weights(c->raw, c->raw_dt, c->sn, c->sc, c->stap, c->Kout, c->C, c->Cpad,
+                               c->R * c->S, bn, c->dtype, buf->p, st));
+    it = c->packed.emplace(bn, std::move(buf)).first;
+  }
+  *wpack = it->second->p;
+  return NNCV_B200_OK;
+}
+
+int conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int H, int W, const float* scale,
+             const float* shift, const void* residual, int relu, DType out_dt, long long ldo,
+             cudaStream_t st) {
+  const int OH = (H + 2 * c->pad - c->R) / c->stride + 1;
+  const int OW = (W + 2 * c->pad - c->S) / c->stride + 1;
+  if (N <= 0 || OH <= 0 || OW <= 0) return fail(NNCV_B200_EINVAL, "conv: empty output");
+  if (c->dtype == kF32) {
+    if (!c->w_f32_ready) {
+      int rc = c->w_f32.reserve((size_t)c->Kout * c->R * c->S * c->Cpad * sizeof(float));
+      if (rc) return rc;
+      LAUNCH(launch_repack_weights_f32(c->raw, c->raw_dt, c->sn, c->sc, c->stap, c->Kout, c->C,
+                                       c->Cpad, c->R * c->S, (float*)c->w_f32.p, st));
+      c->w_f32_ready = true;
+    }
+    SimtConvArgs a;
+    a.in = (const float*)in; a.w = (const float*)c->w_f32.p; a.scale = scale; a.shift = shift;
+    a.residual = (const float*)residual; a.out = (float*)out;
+    a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
+    a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.ldo = ldo; a.relu = relu;
+    LAUNCH(launch_conv_simt_f32(a, st));
+    return NNCV_B200_OK;
+  }
+  const long long M = (long long)N * OH * OW;
+  const int bn = igemm_pick_bn(M, c->Kout);
+  const void* wpack = nullptr;
+  int rc = conv_prepare(c, bn, st, &wpack);
+  if (rc) return rc;
+  IgemmArgs a;
+  a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
+  a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
+  a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.ldo = ldo; a.bn = bn;
+  a.ab = c->dtype; a.out_dtype = out_dt; a.relu = relu; a.error_flag = g_dev.error_flag;
+  LAUNCH(launch_conv_igemm(a, st));
+  return NNCV_B200_OK;
+}
+
+// =====================================================================================
+// network tables (tensor order of the params blob: tests/Nets/Res18.mlir:12-109)
+// =====================================================================================
+struct Group {
+  int cin, cout, k, stride, pad;
+  size_t off_beta, off_gamma, off_var, off_mean, off_w;
+};
+struct NetSpec {
+  int depth = 0;
+  std::vector<Group> groups;  // forward order
+  int fc_in = 0;
+  size_t off_fc_b = 0, off_fc_w = 0, total = 0;
+};
+
+NetSpec build_spec(int depth) {
+  NetSpec s;
+  s.depth = depth;
+  auto add = [&](int cin, int cout, int k, int stride, int pad) {
+    s.groups.push_back(Group{cin, cout, k, stride, pad, 0, 0, 0, 0, 0});
+  };
+  add(3, 64, 7, 2, 3);
+  const int widths[4] = {64, 128, 256, 512};
+  int cin = 64;
+  if (depth == 18) {
+    for (int l = 0; l < 4; ++l)
+      for (int b = 0; b < 2; ++b) {
+        const int stride = (b == 0 && l > 0) ? 2 : 1;
+        add(cin, widths[l], 3, stride, 1);
+        add(widths[l], widths[l], 3, 1, 1);
+        if (b == 0 && l > 0) add(cin, widths[l], 1, 2, 0);
+        cin = widths[l];
+      }
+    s.fc_in = 512;
+  } else {
+    const int blocks[4] = {3, 4, 6, 3};
+    for (int l = 0; l < 4; ++l)
+      for (int b = 0; b < blocks[l]; ++b) {
+        const int stride = (b == 0 && l > 0) ? 2 : 1;
+        add(cin, widths[l], 1, 1, 0);
+        add(widths[l], widths[l], 3, stride, 1);
+        add(widths[l], widths[l] * 4, 1, 1, 0);
+        if (b == 0) add(cin, widths[l] * 4, 1, stride, 0);
+        cin = widths[l] * 4;
+      }
+    s.fc_in = 2048;
+  }
+  size_t off = 0;
+  s.off_fc_b = off; off += 1000;
+  s.off_fc_w = off; off += (size_t)1000 * s.fc_in;
+  for (int i = (int)s.groups.size() - 1; i >= 0; --i) {
+    Group& g = s.groups[i];
+    g.off_beta = off; off += g.cout;
+    g.off_gamma = off; off += g.cout;
+    g.off_var = off; off += g.cout;
+    g.off_mean = off; off += g.cout;
+    g.off_w = off; off += (size_t)g.cout * g.cin * g.k * g.k;
+  }
+  s.total = off;
+  return s;
+}
+
+// =====================================================================================
+// model + executor
+// =====================================================================================
+struct Model {
+  NetSpec spec;
+  size_t ele_width = 4;      // params / io element width
+  DType io_dt = kF32;        // element type of src / dst
+  DType act_dt = kF16;       // activation / compute type
+  DevBuf blob;               // raw params on the device
+  DevBuf folded;             // scale/shift for every group, fp32
+  DevBuf fc_bias;            // fp32
+  std::vector<std::unique_ptr<nncv_b200_conv>> convs;
+  std::vector<float*> scale, shift;
+  std::unique_ptr<nncv_b200_conv> fc;
+  const void* host_blob_id = nullptr;  // pointer identity of the blob the plan was built from
+  // per-shape workspace
+  int wsN = 0, wsH = 0, wsW = 0;
+  DevBuf in_stage, in_nhwc, stem, act[5], pooled, logits32, logits_io;
+};
+std::unique_ptr<Model> g_model;
+
+DType dt_from_width(size_t w) { return w == 4 ? kF32 : kF16; }
+
+int model_build(int depth, const void* host_blob, size_t n_elements, size_t ele_width,
+                const nncv_b200_opts* opts) {
+  int rc = device_init();
+  if (rc) return rc;
+  if (depth != 18 && depth != 50) return fail(NNCV_B200_EINVAL, "unknown network depth %d", depth);
+  if (ele_width != 4 && ele_width != 2) return fail(NNCV_B200_EINVAL, "eleWidth must be 2 or 4");
+  auto m = std::make_unique<Model>();
+  m->spec = build_spec(depth);
+  if (n_elements != m->spec.total)
+    return fail(NNCV_B200_EINVAL, "params hold %zu elements, resnet%d needs %zu", n_elements, depth,
+                m->spec.total);
+  m->ele_width = ele_width;
+  m->io_dt = dt_from_width(ele_width);
+  int cd = opts ? opts->compute_dtype : -1;
+  if (cd < 0) cd = ele_width == 4 ? NNCV_B200_F32 : NNCV_B200_F16;
+  if (cd != NNCV_B200_F32 && cd != NNCV_B200_F16 && cd != NNCV_B200_BF16)
+    return fail(NNCV_B200_EINVAL, "bad compute_dtype %d", cd);
+  m->act_dt = (DType)cd;
+  cudaStream_t st = g_dev.stream;
+  rc = m->blob.reserve(n_elements * ele_width);
+  if (rc) return rc;
+  CU(cudaMemcpyAsync(m->blob.p, host_blob, n_elements * ele_width, cudaMemcpyHostToDevice, st));
+  const char* base = (const char*)m->blob.p;
+  const DType pdt = dt_from_width(ele_width);
+  auto at = [&](size_t off) { return (const void*)(base + off * ele_width); };
+
+  size_t nfold = 0;
+  for (auto& g : m->spec.groups) nfold += 2 * (size_t)g.cout;
+  rc = m->folded.reserve(nfold * sizeof(float));
+  if (rc) return rc;
+  float* fp = (float*)m->folded.p;
+  for (auto& g : m->spec.groups) {
+    auto c = std::make_unique<nncv_b200_conv>();
+    c->Kout = g.cout; c->C = g.cin; c->R = g.k; c->S = g.k; c->stride = g.stride; c->pad = g.pad;
+    c->dtype = m->act_dt;
+    c->Cpad = m->act_dt == kF32 ? (g.cin + 3) / 4 * 4 : (g.cin + 7) / 8 * 8;
+    c->raw = at(g.off_w); c->raw_dt = pdt;
+    c->sn = (long long)g.cin * g.k * g.k; c->sc = (long long)g.k * g.k; c->stap = 1;
+    m->convs.push_back(std::move(c));
+    m->scale.push_back(fp);
+    m->shift.push_back(fp + g.cout);
+    LAUNCH(launch_bn_fold(at(g.off_gamma), at(g.off_beta), at(g.off_mean), at(g.off_var), pdt,
+                          g.cout, fp, fp + g.cout, st));
+    fp += 2 * g.cout;
+  }
+  // FC: weight [1000, fc_in] is already "[Kout][C]" (the forward's transpose generic,
+  // Res18.mlir:617-620, is absorbed by reading it K-major); bias in fp32.
+  m->fc = std::make_unique<nncv_b200_conv>();
+  m->fc->Kout = 1000; m->fc->C = m->spec.fc_in; m->fc->Cpad = m->spec.fc_in; m->fc->dtype = m->act_dt;
+  m->fc->raw = at(m->spec.off_fc_w); m->fc->raw_dt = pdt;
+  m->fc->sn = m->spec.fc_in; m->fc->sc = 1; m->fc->stap = 1;
+  rc = m->fc_bias.reserve(1000 * sizeof(float));
+  if (rc) return rc;
+  LAUNCH(launch_convert(at(m->spec.off_fc_b), pdt, m->fc_bias.p, kF32, 1000, st));
+  CU(cudaStreamSynchronize(st));
+  m->host_blob_id = host_blob;
+  g_model = std::move(m);
+  return ok();
+}
+
+struct Shape { int h, w; };
+
+int ensure_workspace(Model& m, int N, int H, int W) {
+  if (m.wsN == N && m.wsH == H && m.wsW == W) return NNCV_B200_OK;
+  const size_t es = dtype_size(m.act_dt);
+  const int cpad0 = m.convs[0]->Cpad;
+  const int h1 = (H + 6 - 7) / 2 + 1, w1 = (W + 6 - 7) / 2 + 1;
+  const int h2 = (h1 + 2 - 3) / 2 + 1, w2 = (w1 + 2 - 3) / 2 + 1;
+  if (h1 <= 0 || w1 <= 0 || h2 <= 0 || w2 <= 0) return fail(NNCV_B200_EINVAL, "input %dx%d too small", H, W);
+  // largest block activation: the first stage (spatial h2 x w2) with its widest channel count
+  const size_t cmax = m.spec.depth == 18 ? 64 : 256;
+  const size_t act_elems = (size_t)N * h2 * w2 * cmax;
+  int rc = 0;
+  if ((rc = m.in_stage.reserve((size_t)N * 3 * H * W * m.ele_width))) return rc;
+  if ((rc = m.in_nhwc.reserve((size_t)N * H * W * cpad0 * es))) return rc;
+  if ((rc = m.stem.reserve((size_t)N * h1 * w1 * 64 * es))) return rc;
+  for (auto& b : m.act)
+    if ((rc = b.reserve(act_elems * es))) return rc;
+  if ((rc = m.pooled.reserve((size_t)N * m.spec.fc_in * es))) return rc;
+  if ((rc = m.logits32.reserve((size_t)N * 1000 * sizeof(float)))) return rc;
+  if ((rc = m.logits_io.reserve((size_t)N * 1000 * m.ele_width))) return rc;
+  m.wsN = N; m.wsH = H; m.wsW = W;
+  return NNCV_B200_OK;
+}
+
+// Runs the network on a dense NCHW device tensor; logits (io type) land in m.logits_io
+// (or m.logits32 when io is fp32).  Asynchronous on `st`.
+int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cudaStream_t st) {
+  int rc = ensure_workspace(m, N, H, W);
+  if (rc) return rc;
+  const DType adt = m.act_dt;
+  size_t gi = 0;
+  // NCHW -> NHWC (channels padded), io type -> activation type
+  LAUNCH(launch_nchw_to_nhwc(src_dev, m.io_dt, m.in_nhwc.p, adt, N, 3, H, W, m.convs[0]->Cpad, st));
+  int h = H, w = W;
+  auto out_hw = [](int x, const nncv_b200_conv& c) { return (x + 2 * c.pad - c.R) / c.stride + 1; };
+  auto run = [&](size_t idx, const void* in, void* out, int ih, int iw, const void* res, int relu) {
+    nncv_b200_conv& c = *m.convs[idx];
+    return conv_run(&c, in, out, N, ih, iw, m.scale[idx], m.shift[idx], res, relu, adt, c.Kout, st);
+  };
+  // stem (Res18.mlir:118-143) and max-pool (:144-151)
+  rc = run(gi, m.in_nhwc.p, m.stem.p, h, w, nullptr, 1);
+  if (rc) return rc;
+  h = out_hw(h, *m.convs[gi]); w = out_hw(w, *m.convs[gi]);
+  ++gi;
+  LAUNCH(launch_maxpool_nhwc(m.stem.p, m.act[0].p, adt, N, h, w, 64, 3, 2, 1, st));
+  h = (h + 2 - 3) / 2 + 1; w = (w + 2 - 3) / 2 + 1;
+  int xi = 0;  // index of the buffer holding the block input
+  const int nb18[4] = {2, 2, 2, 2}, nb50[4] = {3, 4, 6, 3};
+  const int* nb = m.spec.depth == 18 ? nb18 : nb50;
+  for (int l = 0; l < 4; ++l) {
+    for (int b = 0; b < nb[l]; ++b) {
+      const bool has_ds = m.spec.depth == 18 ? (b == 0 && l > 0) : (b == 0);
+      void* x = m.act[xi].p;
+      void* t1 = m.act[(xi + 1) % 5].p;
+      void* t2 = m.act[(xi + 2) % 5].p;
+      void* ds = m.act[(xi + 3) % 5].p;
+      void* y = m.act[(xi + 4) % 5].p;
+      int h1 = h, w1 = w;
+      const void* last = nullptr;
+      size_t last_idx = 0;
+      if (m.spec.depth == 18) {
+        if ((rc = run(gi, x, t1, h1, w1, nullptr, 1))) return rc;
+        h1 = out_hw(h1, *m.convs[gi]); w1 = out_hw(w1, *m.convs[gi]);
+        ++gi;
+        last = t1; last_idx = gi++;
+      } else {
+        if ((rc = run(gi, x, t1, h1, w1, nullptr, 1))) return rc;
+        ++gi;
+        if ((rc = run(gi, t1, t2, h1, w1, nullptr, 1))) return rc;
+        h1 = out_hw(h1, *m.convs[gi]); w1 = out_hw(w1, *m.convs[gi]);
+        ++gi;
+        last = t2; last_idx = gi++;
+      }
+      const void* identity = x;
+      if (has_ds) {  // BN(conv1x1(identity)) (Res18.mlir:297-311)
+        if ((rc = run(gi, x, ds, h, w, nullptr, 0))) return rc;
+        ++gi;
+        identity = ds;
+      }
+      // last conv of the block: BN, + identity, ReLU (Res18.mlir:180-203)
+      if ((rc = run(last_idx, last, y, h1, w1, identity, 1))) return rc;
+      xi = (xi + 4) % 5;
+      h = h1; w = w1;
+    }
+  }
+  // global average pool (Res18.mlir:606-614) and FC (:617-628)
+  LAUNCH(launch_avgpool_nhwc(m.act[xi].p, m.pooled.p, adt, N, h * w, m.spec.fc_in, st));
+  rc = conv_run(m.fc.get(), m.pooled.p, m.logits32.p, N, 1, 1, nullptr, (const float*)m.fc_bias.p,
+                nullptr, 0, kF32, 1000, st);
+  if (rc) return rc;
+  if (m.io_dt != kF32)
+    LAUNCH(launch_convert(m.logits32.p, kF32, m.logits_io.p, m.io_dt, (size_t)N * 1000, st));
+  return NNCV_B200_OK;
+}
+
+int check_src(const nncv_memref4* src, int* N, int* H, int* W) {
+  if (!src || !src->aligned) return fail(NNCV_B200_EINVAL, "src descriptor or its pointer is null");
+  const intptr_t n = src->sizes[0], c = src->sizes[1], h = src->sizes[2], w = src->sizes[3];
+  if (n <= 0 || c != 3 || h <= 0 || w <= 0 || n > 65536 || h > 16384 || w > 16384)
+    return fail(NNCV_B200_EINVAL, "src must be [N,3,H,W], got [%ld,%ld,%ld,%ld]", (long)n, (long)c, (long)h, (long)w);
+  // dense NCHW.  The reference's example writes the row stride as H (examples/Res18/main.cpp:87-93),
+  // which equals W only for square images; accept exactly that spelling too.
+  const bool row_ok = src->strides[2] == w || (h == w && src->strides[2] == h);
+  if (src->strides[3] != 1 || !row_ok || src->strides[1] != h * w || src->strides[0] != c * h * w)
+    return fail(NNCV_B200_EINVAL, "src must be dense NCHW (strides %ld,%ld,%ld,%ld)", (long)src->strides[0],
+                (long)src->strides[1], (long)src->strides[2], (long)src->strides[3]);
+  *N = (int)n; *H = (int)h; *W = (int)w;
+  return NNCV_B200_OK;
+}
+
+int check_dst(nncv_memref2* dst, int N, size_t ele_width, bool* allocated_here) {
+  *allocated_here = false;
+  if (!dst) return fail(NNCV_B200_EINVAL, "dst descriptor is null");
+  if (!dst->aligned) {
+    // MLIR convention: the callee allocates the result memref.
+    void* p = malloc((size_t)N * 1000 * ele_width);
+    if (!p) return fail(NNCV_B200_ENOMEM, "malloc of the result buffer failed");
+    dst->allocated = dst->aligned = p;
+    dst->offset = 0;
+    dst->sizes[0] = N; dst->sizes[1] = 1000;
+    dst->strides[0] = 1000; dst->strides[1] = 1;
+    *allocated_here = true;
+    return NNCV_B200_OK;
+  }
+  if (dst->sizes[0] != N || dst->sizes[1] != 1000)
+    return fail(NNCV_B200_EINVAL, "dst must be [%d,1000], got [%ld,%ld]", N, (long)dst->sizes[0], (long)dst->sizes[1]);
+  if (dst->strides[1] != 1 || dst->strides[0] < 1000)
+    return fail(NNCV_B200_EINVAL, "dst rows must be contiguous (strides %ld,%ld)", (long)dst->strides[0], (long)dst->strides[1]);
+  return NNCV_B200_OK;
+}
+
+int forward_impl(nncv_memref2* dst, nncv_memref4* src, void* params, cudaStream_t user_stream,
+                 bool device_only) {
+  int rc = device_init();
+  if (rc) return rc;
+  if (!g_model) {
+    // Lazy plan from the blob descriptor: element count selects the network; the element type of
+    // a bare descriptor is float (the only type the reference's -split-params writes,
+    // SplitParamsFlatArray.cpp:144-147).
+    auto* pd = static_cast<nncv_memref1*>(params);
+    if (!pd || !pd->aligned) return fail(NNCV_B200_ENOMODEL, "no model loaded and params is null");
+    const size_t n = (size_t)pd->sizes[0];
+    int depth = 0;
+    if (n == build_spec(18).total) depth = 18;
+    else if (n == build_spec(50).total) depth = 50;
+    else return fail(NNCV_B200_ENOMODEL, "params hold %zu elements: neither resnet18 nor resnet50", n);
+    rc = model_build(depth, (const char*)pd->aligned + pd->offset * 4, n, 4, nullptr);
+    if (rc) return rc;
+  } else if (params) {
+    auto* pd = static_cast<nncv_memref1*>(params);
+    if ((size_t)pd->sizes[0] != g_model->spec.total)
+      return fail(NNCV_B200_EINVAL, "params hold %ld elements, the loaded model has %zu", (long)pd->sizes[0],
+                  g_model->spec.total);
+  }
+  Model& m = *g_model;
+  int N, H, W;
+  if ((rc = check_src(src, &N, &H, &W))) return rc;
+  bool allocated_here = false;
+  if ((rc = check_dst(dst, N, m.ele_width, &allocated_here))) return rc;
+  const size_t ew = m.ele_width;
+  const char* sp = (const char*)src->aligned + src->offset * (intptr_t)ew;
+  char* dp = (char*)dst->aligned + dst->offset * (intptr_t)ew;
+  const bool src_dev = is_device_ptr(sp), dst_dev = is_device_ptr(dp);
+  if (device_only && (!src_dev || !dst_dev))
+    return fail(NNCV_B200_EINVAL, "nncv_b200_forward_device needs device-resident src and dst");
+  cudaStream_t st = device_only && user_stream ? user_stream : g_dev.stream;
+  if ((rc = ensure_workspace(m, N, H, W))) return rc;
+  const void* src_d = sp;
+  if (!src_dev) {
+    CU(cudaMemcpyAsync(m.in_stage.p, sp, (size_t)N * 3 * H * W * ew, cudaMemcpyHostToDevice, st));
+    src_d = m.in_stage.p;
+  }
+  if ((rc = model_forward_device(m, src_d, N, H, W, st))) return rc;
+  const void* logits = m.io_dt == kF32 ? m.logits32.p : m.logits_io.p;
+  CU(cudaMemcpy2DAsync(dp, (size_t)dst->strides[0] * ew, logits, 1000 * ew, 1000 * ew, (size_t)N,
+                       dst_dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, st));
+  if (device_only) return ok();
+  CU(cudaStreamSynchronize(st));
+  if ((rc = check_kernel_status())) return rc;
+  return ok();
+}
+
+int depth_from_name(const char* net) {
+  if (!net) return 0;
+  if (!strcmp(net, "resnet18")) return 18;
+  if (!strcmp(net, "resnet50")) return 50;
+  return 0;
+}
+
+}  // namespace
+
+// =====================================================================================
+// container reader / writer
+// =====================================================================================
+struct nncv_flat_array {
+  nncv_memref_magic_head head;
+  std::vector<nncv_memref_indexer> idx;
+  std::vector<char> data;
+  std::vector<size_t> offs;  // byte offset of each tensor inside `data`
+  nncv_memref1 wrapped;
+};
+
+namespace {
+size_t indexer_elems(const nncv_memref_indexer& i) {
+  size_t n = 1;
+  for (size_t d = 0; d < i.dims && d < 8; ++d) n *= i.shape[d];
+  return n;
+}
+}  // namespace
+
+extern "C" {
+
+nncv_flat_array* nncv_flat_array_read(const char* path) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (!path) { fail(NNCV_B200_EINVAL, "path is null"); return nullptr; }
+  std::ifstream f(path, std::ifstream::binary);
+  if (!f.good()) { fail(NNCV_B200_EIO, "cannot open %s", path); return nullptr; }
+  f.seekg(0, std::ios::end);
+  const size_t fsize = (size_t)f.tellg();
+  f.seekg(0);
+  auto a = std::make_unique<nncv_flat_array>();
+  if (fsize < sizeof(a->head) || !f.read((char*)&a->head, sizeof(a->head))) {
+    fail(NNCV_B200_EIO, "%s: shorter than the magic head", path);
+    return nullptr;
+  }
+  if (a->head.magicNumber != 0x42) { fail(NNCV_B200_EIO, "%s: bad magic number", path); return nullptr; }
+  const size_t n = a->head.numMemRefIndex, start = a->head.memRefIndexStartOffset;
+  if (start < sizeof(a->head) || start > fsize || n > (fsize - start) / sizeof(nncv_memref_indexer)) {
+    fail(NNCV_B200_EIO, "%s: indexer table runs past the end of the file", path);
+    return nullptr;
+  }
+  f.seekg((std::streamoff)start);
+  a->idx.resize(n);
+  if (n && !f.read((char*)a->idx.data(), (std::streamsize)(n * sizeof(nncv_memref_indexer)))) {
+    fail(NNCV_B200_EIO, "%s: truncated indexer table", path);
+    return nullptr;
+  }
+  size_t total = 0, elems = 0;
+  const size_t budget = fsize - start - n * sizeof(nncv_memref_indexer);
+  for (auto& i : a->idx) {
+    if (i.dims > 8 || (i.eleWidth != 2 && i.eleWidth != 4) || i.eleWidth != a->idx[0].eleWidth) {
+      fail(NNCV_B200_EIO, "%s: unsupported indexer (dims %zu, eleWidth %zu)", path, i.dims, i.eleWidth);
+      return nullptr;
+    }
+    const size_t e = indexer_elems(i);
+    if (e > budget || total + e * i.eleWidth > budget) {
+      fail(NNCV_B200_EIO, "%s: tensor data runs past the end of the file", path);
+      return nullptr;
+    }
+    a->offs.push_back(total);
+    total += e * i.eleWidth;
+    elems += e;
+  }
+  a->data.resize(total);
+  if (total && !f.read(a->data.data(), (std::streamsize)total)) {
+    fail(NNCV_B200_EIO, "%s: truncated tensor data", path);
+    return nullptr;
+  }
+  a->wrapped.allocated = a->wrapped.aligned = a->data.data();
+  a->wrapped.offset = 0;
+  a->wrapped.sizes[0] = (intptr_t)elems;
+  a->wrapped.strides[0] = 1;
+  ok();
+  return a.release();
+}
+
+void nncv_flat_array_free(nncv_flat_array* a) { delete a; }
+size_t nncv_flat_array_count(const nncv_flat_array* a) { return a ? a->idx.size() : 0; }
+const nncv_memref_indexer* nncv_flat_array_indexer(const nncv_flat_array* a, size_t i) {
+  return (a && i < a->idx.size()) ? &a->idx[i] : nullptr;
+}
+const void* nncv_flat_array_data(const nncv_flat_array* a, size_t i) {
+  return (a && i < a->idx.size()) ? a->data.data() + a->offs[i] : nullptr;
+}
+nncv_memref1* nncv_flat_array_wrapped(nncv_flat_array* a) { return a ? &a->wrapped : nullptr; }
+
+int nncv_flat_array_write(const char* path, size_t n, const nncv_memref_indexer* indexers,
+                          const void* const* data) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (!path || (n && (!indexers || !data))) return fail(NNCV_B200_EINVAL, "null argument");
+  std::ofstream out(path, std::ofstream::binary);
+  if (!out.good()) return fail(NNCV_B200_EIO, "cannot create %s", path);
+  nncv_memref_magic_head head;
+  head.magicNumber = 0x42;
+  head.memRefIndexStartOffset = sizeof(head);
+  head.numMemRefIndex = n;
+  out.write((const char*)&head, sizeof(head));
+  size_t off = sizeof(head) + n * sizeof(nncv_memref_indexer);
+  for (size_t i = 0; i < n; ++i) {
+    nncv_memref_indexer idx = indexers[i];
+    if (idx.dims > 8) return fail(NNCV_B200_EINVAL, "tensor %zu has rank %zu > 8", i, idx.dims);
+    idx.dataOffset = off;
+    out.write((const char*)&idx, sizeof(idx));
+    off += indexer_elems(idx) * idx.eleWidth;
+  }
+  for (size_t i = 0; i < n; ++i)
+    out.write((const char*)data[i], (std::streamsize)(indexer_elems(indexers[i]) * indexers[i].eleWidth));
+  out.close();
+  if (!out.good()) return fail(NNCV_B200_EIO, "write to %s failed", path);
+  return ok();
+}
+
+// =====================================================================================
+// model API
+// =====================================================================================
+int nncv_b200_load(const char* net, const char* model_bin_path, const nncv_b200_opts* opts) {
+  const int depth = depth_from_name(net);
+  if (!depth) { std::lock_guard<std::mutex> lk(g_mutex); return fail(NNCV_B200_EINVAL, "net must be \"resnet18\" or \"resnet50\""); }
+  nncv_flat_array* a = nncv_flat_array_read(model_bin_path);
+  if (!a) return g_status;
+  std::lock_guard<std::mutex> lk(g_mutex);
+  std::unique_ptr<nncv_flat_array> hold(a);
+  const NetSpec spec = build_spec(depth);
+  // shape check against the documented tensor order
+  const size_t expect = 2 + 5 * spec.groups.size();
+  if (a->idx.size() != expect)
+    return fail(NNCV_B200_EINVAL, "%s holds %zu tensors, %s needs %zu", model_bin_path, a->idx.size(), net, expect);
+  size_t t = 2;
+  for (int i = (int)spec.groups.size() - 1; i >= 0; --i, t += 5) {
+    const Group& g = spec.groups[i];
+    const nncv_memref_indexer& w = a->idx[t + 4];
+    if (w.dims != 4 || (int)w.shape[0] != g.cout || (int)w.shape[1] != g.cin || (int)w.shape[2] != g.k ||
+        (int)w.shape[3] != g.k)
+      return fail(NNCV_B200_EINVAL, "tensor %zu (%s) is not the %dx%dx%dx%d conv weight the plan expects",
+                  t + 4, w.name, g.cout, g.cin, g.k, g.k);
+    for (int j = 0; j < 4; ++j)
+      if (indexer_elems(a->idx[t + j]) != (size_t)g.cout)
+        return fail(NNCV_B200_EINVAL, "tensor %zu (%s) should hold %d batch-norm values", t + j, a->idx[t + j].name, g.cout);
+  }
+  const size_t ew = a->idx[0].eleWidth;
+  g_model.reset();
+  return model_build(depth, a->data.data(), (size_t)a->wrapped.sizes[0], ew, opts);
+}
+
+int nncv_b200_load_blob(const char* net, const void* blob, size_t n_elements, size_t ele_width,
+                        const nncv_b200_opts* opts) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  const int depth = depth_from_name(net);
+  if (!depth) return fail(NNCV_B200_EINVAL, "net must be \"resnet18\" or \"resnet50\"");
+  if (!blob) return fail(NNCV_B200_EINVAL, "blob is null");
+  g_model.reset();
+  return model_build(depth, blob, n_elements, ele_width, opts);
+}
+
+int nncv_b200_unload(void) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (g_dev.ready) cudaDeviceSynchronize();
+  g_model.reset();
+  return ok();
+}
+
+void _mlir_ciface_forward(nncv_memref2* dst, nncv_memref4* src, void* params) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  forward_impl(dst, src, params, nullptr, false);
+}
+
+int nncv_b200_forward_device(nncv_memref2* dst, nncv_memref4* src, void* cuda_stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (!g_model) return fail(NNCV_B200_ENOMODEL, "no model loaded");
+  return forward_impl(dst, src, nullptr, (cudaStream_t)cuda_stream, true);
+}
+
+int nncv_b200_last_status(void) { return g_status; }
+const char* nncv_b200_last_error(void) { return g_msg; }
+long long nncv_b200_launch_count(void) { return g_launches; }
+
+// =====================================================================================
+// single kernels
+// =====================================================================================
+int nncv_b200_matmul(const void* A, const void* B, void* C, int M, int N, int K, int ab_dtype,
+                     int c_dtype, const float* bias, int relu, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!A || !B || !C || M <= 0 || N <= 0 || K <= 0) return fail(NNCV_B200_EINVAL, "matmul: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (ab_dtype == NNCV_B200_F32) {
+    if (c_dtype != NNCV_B200_F32 || K % 4 != 0) return fail(NNCV_B200_EINVAL, "fp32 matmul needs fp32 C and K %% 4 == 0");
+    if ((rc = ensure_scratch((size_t)N * K * sizeof(float)))) return rc;
+    LAUNCH(launch_repack_weights_f32(B, kF32, 1, N, 0, N, K, K, 1, (float*)g_dev.scratch, st));
+    SimtConvArgs a;
+    a.in = (const float*)A; a.w = (const float*)g_dev.scratch; a.shift = bias; a.out = (float*)C;
+    a.N = M; a.H = a.W = a.OH = a.OW = 1; a.C = K; a.Kout = N; a.ldo = N; a.relu = relu;
+    LAUNCH(launch_conv_simt_f32(a, st));
+    return ok();
+  }
+  if (ab_dtype != NNCV_B200_F16 && ab_dtype != NNCV_B200_BF16) return fail(NNCV_B200_EINVAL, "matmul: bad ab_dtype");
+  if (c_dtype != NNCV_B200_F32 && c_dtype != ab_dtype) return fail(NNCV_B200_EINVAL, "matmul: c_dtype must be F32 or ab_dtype");
+  if (K % 8 != 0) return fail(NNCV_B200_EINVAL, "matmul: the tcgen05 path needs K %% 8 == 0");
+  const int bn = igemm_pick_bn(M, N);
+  if ((rc = ensure_scratch(packed_weight_bytes(N, K, 1, 1, bn)))) return rc;
+  LAUNCH(launch_pack_weights(B, (DType)ab_dtype, 1, N, 0, N, K, K, 1, bn, (DType)ab_dtype, g_dev.scratch, st));
+  IgemmArgs a;
+  a.in = A; a.wpack = g_dev.scratch; a.shift = bias; a.out = C;
+  a.N = M; a.H = a.W = a.OH = a.OW = 1; a.C = K; a.Kout = N; a.ldo = N; a.bn = bn;
+  a.ab = (DType)ab_dtype; a.out_dtype = (DType)c_dtype; a.relu = relu; a.error_flag = g_dev.error_flag;
+  LAUNCH(launch_conv_igemm(a, st));
+  return ok();
+}
+
+nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout, int C, int R,
+                                      int S, int stride, int pad, int dtype, int algo) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (device_init()) return nullptr;
+  if (!weights || Kout <= 0 || C <= 0 || R <= 0 || S <= 0 || stride <= 0 || pad < 0 || w_dtype < 0 ||
+      w_dtype > 2 || dtype < 0 || dtype > 2) {
+    fail(NNCV_B200_EINVAL, "conv_create: bad argument");
+    return nullptr;
+  }
+  if (algo != 0) {
+    fail(NNCV_B200_EINVAL, "conv_create: algo %d is not available", algo);
+    return nullptr;
+  }
+  auto c = std::make_unique<nncv_b200_conv>();
+  c->Kout = Kout; c->C = C; c->R = R; c->S = S; c->stride = stride; c->pad = pad;
+  c->dtype = (DType)dtype; c->algo = algo;
+  c->Cpad = dtype == NNCV_B200_F32 ? (C + 3) / 4 * 4 : (C + 7) / 8 * 8;
+  const size_t bytes = (size_t)Kout * C * R * S * dtype_size((DType)w_dtype);
+  if (c->raw_owned.reserve(bytes)) return nullptr;
+  if (cudaMemcpy(c->raw_owned.p, weights, bytes, cudaMemcpyDefault) != cudaSuccess) {
+    fail(NNCV_B200_ECUDA, "conv_create: copying the weights failed");
+    return nullptr;
+  }
+  c->raw = c->raw_owned.p; c->raw_dt = (DType)w_dtype;
+  c->sn = (long long)C * R * S; c->sc = (long long)R * S; c->stap = 1;
+  ok();
+  return c.release();
+}
+
+void nncv_b200_conv_destroy(nncv_b200_conv* c) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (c && g_dev.ready) cudaDeviceSynchronize();
+  delete c;
+}
+
+int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int H, int W,
+                       const float* scale, const float* shift, const void* residual, int relu,
+                       void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (!c || !in || !out) return fail(NNCV_B200_EINVAL, "conv_run: null argument");
+  int rc = conv_run(c, in, out, N, H, W, scale, shift, residual, relu, c->dtype, c->Kout, (cudaStream_t)stream);
+  return rc ? rc : ok();
+}
+
+int nncv_b200_maxpool_nhwc(const void* in, void* out, int dtype, int N, int H, int W, int C,
+                           int k, int stride, int pad, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!in || !out || N <= 0 || k <= 0 || stride <= 0 || dtype < 0 || dtype > 2) return fail(NNCV_B200_EINVAL, "maxpool: bad argument");
+  LAUNCH(launch_maxpool_nhwc(in, out, (DType)dtype, N, H, W, C, k, stride, pad, (cudaStream_t)stream));
+  return ok();
+}
+
+int nncv_b200_avgpool_nhwc(const void* in, void* out, int dtype, int N, int HW, int C, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!in || !out || N <= 0 || HW <= 0 || dtype < 0 || dtype > 2) return fail(NNCV_B200_EINVAL, "avgpool: bad argument");
+  LAUNCH(launch_avgpool_nhwc(in, out, (DType)dtype, N, HW, C, (cudaStream_t)stream));
+  return ok();
+}
+
+int nncv_b200_nchw_to_nhwc(const void* in, int in_dtype, void* out, int out_dtype, int N, int C,
+                           int H, int W, int Cpad, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!in || !out || N <= 0 || C <= 0 || Cpad < C) return fail(NNCV_B200_EINVAL, "nchw_to_nhwc: bad argument");
+  LAUNCH(launch_nchw_to_nhwc(in, (DType)in_dtype, out, (DType)out_dtype, N, C, H, W, Cpad, (cudaStream_t)stream));
+  return ok();
+}
+
+int nncv_b200_bn_fold(const void* gamma, const void* beta, const void* mean, const void* var,
+                      int dtype, int C, float* scale, float* shift, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!gamma || !beta || !mean || !var || !scale || !shift || C <= 0) return fail(NNCV_B200_EINVAL, "bn_fold: bad argument");
+  LAUNCH(launch_bn_fold(gamma, beta, mean, var, (DType)dtype, C, scale, shift, (cudaStream_t)stream));
+  return ok();
+}
+
+}  // extern "C"

@@ -1,0 +1,349 @@
+// CUDA-core kernels of the forward pass: the fp32-accurate convolution / GEMM, and the
+// memory-bound helpers (layout conversion, max-pool, global average pool, batch-norm folding).
+//
+// Reference semantics (nncv tree): tests/Nets/Res18.mlir:125 (conv), :127-137 (batch-norm,
+// folded here into per-channel scale/shift), :138-143 (ReLU with unordered compare, NaN passes),
+// :144-151 (max-pool over a -inf padded map), :606-614 (sum-pool / HW), :193-197 (residual add).
+// All activations are NHWC; every helper moves 16 bytes per access.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cfloat>
+
+#include "kernels.h"
+
+namespace nncv_b200 {
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ------------------------------------------------------------------ fp32 conv ------------
+// Implicit GEMM on CUDA cores: 64 x 64 output tile, k step 16, 256 threads, 4 x 4 per thread.
+constexpr int kTM = 64, kTN = 64, kTK = 16;
+
+struct SimtParams {
+  const float* in;
+  const float* w;
+  const float* scale;
+  const float* shift;
+  const float* residual;
+  float* out;
+  long long ldo;
+  int M, H, W, C, OH, OW, Kout, R, S, stride, pad, Kred;
+  int relu;
+};
+
+__global__ void __launch_bounds__(256) conv_simt_f32_kernel(const SimtParams p) {
+  __shared__ float As[kTK][kTM + 4];
+  __shared__ float Bs[kTK][kTN + 4];
+  const int t = threadIdx.x;
+  const int lrow = t >> 2;        // 0..63: tile row (A) / tile column (B) this thread loads
+  const int lk = (t & 3) * 4;     // k offset of its float4
+  const long long m = (long long)blockIdx.x * kTM + lrow;
+  const bool mvalid = m < p.M;
+  int iy0 = 0, ix0 = 0;
+  const float* img = p.in;
+  if (mvalid) {
+    const int ohw = p.OH * p.OW;
+    const int n_img = (int)(m / ohw);
+    const int rem = (int)(m - (long long)n_img * ohw);
+    const int oy = rem / p.OW, ox = rem - oy * p.OW;
+    iy0 = oy * p.stride - p.pad;
+    ix0 = ox * p.stride - p.pad;
+    img = p.in + (size_t)n_img * p.H * p.W * p.C;
+  }
+  const int nb = blockIdx.y * kTN + lrow;
+  const bool nvalid = nb < p.Kout;
+  const int ty = t >> 4, tx = t & 15;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < p.Kred; k0 += kTK) {
+    const int kidx = k0 + lk;
+    float4 av = make_float4(0.f, 0.f, 0.f, 0.f), bv = av;
+    if (kidx < p.Kred) {
+      const int tap = kidx / p.C, c0 = kidx - tap * p.C;
+      const int r = tap / p.S, s = tap - r * p.S;
+      const int iy = iy0 + r, ix = ix0 + s;
+      if (mvalid && (unsigned)iy < (unsigned)p.H && (unsigned)ix < (unsigned)p.W)
+        av = __ldg(reinterpret_cast<const float4*>(img + ((size_t)iy * p.W + ix) * p.C + c0));
+      if (nvalid) bv = __ldg(reinterpret_cast<const float4*>(p.w + (size_t)nb * p.Kred + kidx));
+    }
+    As[lk][lrow] = av.x; As[lk + 1][lrow] = av.y; As[lk + 2][lrow] = av.z; As[lk + 3][lrow] = av.w;
+    Bs[lk][lrow] = bv.x; Bs[lk + 1][lrow] = bv.y; Bs[lk + 2][lrow] = bv.z; Bs[lk + 3][lrow] = bv.w;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kTK; ++k) {
+      const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+      const float aa[4] = {a.x, a.y, a.z, a.w}, bb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(aa[i], bb[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long mo = (long long)blockIdx.x * kTM + ty * 4 + i;
+    if (mo >= p.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = blockIdx.y * kTN + tx * 4 + j;
+      if (n >= p.Kout) continue;
+      float v = acc[i][j];
+      if (p.scale) v *= __ldg(p.scale + n);
+      if (p.shift) v += __ldg(p.shift + n);
+      if (p.residual) v += p.residual[(size_t)mo * p.ldo + n];
+      if (p.relu) v = !(v <= 0.0f) ? v : 0.0f;
+      p.out[(size_t)mo * p.ldo + n] = v;
+    }
+  }
+}
+
+template <typename SrcT>
+__global__ void repack_weights_f32_kernel(const SrcT* __restrict__ src, long long sn, long long sc,
+                                          long long stap, int Kout, int C, int Cpad, int taps,
+                                          float* __restrict__ dst) {
+  const long long total = (long long)Kout * taps * Cpad;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % Cpad);
+    long long t = i / Cpad;
+    const int tap = (int)(t % taps);
+    const int n = (int)(t / taps);
+    dst[i] = c < C ? to_f<SrcT>(src[n * sn + c * sc + tap * stap]) : 0.0f;
+  }
+}
+
+// ------------------------------------------------------------------ layout ---------------
+// NCHW -> NHWC with the channel count padded to Cpad (zeros); one thread per pixel.
+template <typename SrcT, typename DstT>
+__global__ void nchw_to_nhwc_kernel(const SrcT* __restrict__ src, DstT* __restrict__ dst, int N,
+                                    int C, long long HW, int Cpad) {
+  const long long total = (long long)N * HW;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long n = i / HW, px = i - n * HW;
+    const SrcT* s = src + (size_t)n * C * HW + px;
+    DstT* d = dst + (size_t)i * Cpad;
+    if (sizeof(DstT) == 2 && Cpad == 8) {
+      alignas(16) DstT v[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) v[c] = from_f<DstT>(c < C ? to_f<SrcT>(s[(size_t)c * HW]) : 0.0f);
+      *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(v);
+    } else if (sizeof(DstT) == 4 && Cpad == 4) {
+      alignas(16) DstT v[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) v[c] = from_f<DstT>(c < C ? to_f<SrcT>(s[(size_t)c * HW]) : 0.0f);
+      *reinterpret_cast<uint4*>(d) = *reinterpret_cast<const uint4*>(v);
+    } else {
+      for (int c = 0; c < Cpad; ++c) d[c] = from_f<DstT>(c < C ? to_f<SrcT>(s[(size_t)c * HW]) : 0.0f);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ pooling --------------
+// Max-pool over a -inf padded map; one thread per (output pixel, 16-byte channel vector).
+template <typename T>
+__global__ void maxpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int H,
+                                    int W, int C, int OH, int OW, int k, int stride, int pad) {
+  constexpr int V = 16 / sizeof(T);
+  const int cv = C / V;
+  const long long total = (long long)N * OH * OW * cv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % cv) * V;
+    long long t = i / cv;
+    const int ox = (int)(t % OW);
+    t /= OW;
+    const int oy = (int)(t % OH);
+    const int n = (int)(t / OH);
+    float m[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) m[e] = -INFINITY;
+    for (int r = 0; r < k; ++r) {
+      const int iy = oy * stride - pad + r;
+      if ((unsigned)iy >= (unsigned)H) continue;
+      for (int s = 0; s < k; ++s) {
+        const int ix = ox * stride - pad + s;
+        if ((unsigned)ix >= (unsigned)W) continue;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + (((size_t)n * H + iy) * W + ix) * C + c));
+        const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const float f = to_f<T>(v[e]);
+          m[e] = (m[e] < f || f != f) ? f : m[e];  // maximumf: NaN propagates
+        }
+      }
+    }
+    alignas(16) T o[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) o[e] = from_f<T>(m[e]);
+    *reinterpret_cast<uint4*>(dst + (((size_t)n * OH + oy) * OW + ox) * C + c) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+// Global average pool: sum in fp32 over HW then divide by HW; one thread per channel vector.
+template <typename T>
+__global__ void avgpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int HW,
+                                    int C) {
+  constexpr int V = 16 / sizeof(T);
+  const int cv = C / V;
+  const long long total = (long long)N * cv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % cv) * V;
+    const int n = (int)(i / cv);
+    float s[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) s[e] = 0.0f;
+    for (int px = 0; px < HW; ++px) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + ((size_t)n * HW + px) * C + c));
+      const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int e = 0; e < V; ++e) s[e] += to_f<T>(v[e]);
+    }
+    alignas(16) T o[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) o[e] = from_f<T>(s[e] / (float)HW);
+    *reinterpret_cast<uint4*>(dst + (size_t)n * C + c) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+template <typename T>
+__global__ void bn_fold_kernel(const T* gamma, const T* beta, const T* mean, const T* var, int C,
+                               float* scale, float* shift) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float eps = (float)1e-5;  // arith.truncf of the f64 constant (Res18.mlir:113,129)
+  const float rs = 1.0f / sqrtf(to_f<T>(var[c]) + eps);
+  const float sc = to_f<T>(gamma[c]) * rs;
+  scale[c] = sc;
+  shift[c] = to_f<T>(beta[c]) - to_f<T>(mean[c]) * sc;
+}
+
+template <typename S, typename D>
+__global__ void convert_kernel(const S* __restrict__ src, D* __restrict__ dst, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    dst[i] = from_f<D>(to_f<S>(src[i]));
+}
+
+inline int grid_for(long long total, int threads) {
+  long long b = (total + threads - 1) / threads;
+  const long long cap = 148LL * 32;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+template <typename F>
+cudaError_t by_dtype(DType t, F&& f) {
+  switch (t) {
+    case kF32: return f(float{});
+    case kF16: return f(__half{});
+    case kBF16: return f(__nv_bfloat16{});
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+cudaError_t launch_conv_simt_f32(const SimtConvArgs& a, cudaStream_t stream) {
+  if (a.C % 4 != 0) return cudaErrorInvalidValue;
+  SimtParams p;
+  p.in = a.in; p.w = a.w; p.scale = a.scale; p.shift = a.shift; p.residual = a.residual; p.out = a.out;
+  p.ldo = a.ldo;
+  const long long M = (long long)a.N * a.OH * a.OW;
+  if (M <= 0 || M > 0x7fffffffLL) return cudaErrorInvalidValue;
+  p.M = (int)M; p.H = a.H; p.W = a.W; p.C = a.C; p.OH = a.OH; p.OW = a.OW; p.Kout = a.Kout;
+  p.R = a.R; p.S = a.S; p.stride = a.stride; p.pad = a.pad; p.Kred = a.R * a.S * a.C; p.relu = a.relu;
+  dim3 grid((unsigned)((M + kTM - 1) / kTM), (unsigned)((a.Kout + kTN - 1) / kTN));
+  conv_simt_f32_kernel<<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_repack_weights_f32(const void* src, DType src_dt, long long sn, long long sc,
+                                      long long stap, int Kout, int C, int Cpad, int taps,
+                                      float* dst, cudaStream_t stream) {
+  const long long total = (long long)Kout * taps * Cpad;
+  return by_dtype(src_dt, [&](auto tag) {
+    using S = decltype(tag);
+    repack_weights_f32_kernel<S><<<grid_for(total, 256), 256, 0, stream>>>(
+        static_cast<const S*>(src), sn, sc, stap, Kout, C, Cpad, taps, dst);
+    return cudaGetLastError();
+  });
+}
+
+cudaError_t launch_nchw_to_nhwc(const void* src, DType src_dt, void* dst, DType dst_dt, int N,
+                                int C, int H, int W, int Cpad, cudaStream_t stream) {
+  const long long HW = (long long)H * W;
+  return by_dtype(src_dt, [&](auto stag) {
+    using S = decltype(stag);
+    return by_dtype(dst_dt, [&](auto dtag) {
+      using D = decltype(dtag);
+      nchw_to_nhwc_kernel<S, D><<<grid_for((long long)N * HW, 256), 256, 0, stream>>>(
+          static_cast<const S*>(src), static_cast<D*>(dst), N, C, HW, Cpad);
+      return cudaGetLastError();
+    });
+  });
+}
+
+cudaError_t launch_maxpool_nhwc(const void* src, void* dst, DType dt, int N, int H, int W, int C,
+                                int k, int stride, int pad, cudaStream_t stream) {
+  const int OH = (H + 2 * pad - k) / stride + 1, OW = (W + 2 * pad - k) / stride + 1;
+  return by_dtype(dt, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int V = 16 / sizeof(T);
+    if (C % V != 0) return cudaErrorInvalidValue;
+    const long long total = (long long)N * OH * OW * (C / V);
+    maxpool_nhwc_kernel<T><<<grid_for(total, 256), 256, 0, stream>>>(
+        static_cast<const T*>(src), static_cast<T*>(dst), N, H, W, C, OH, OW, k, stride, pad);
+    return cudaGetLastError();
+  });
+}
+
+cudaError_t launch_avgpool_nhwc(const void* src, void* dst, DType dt, int N, int HW, int C,
+                                cudaStream_t stream) {
+  return by_dtype(dt, [&](auto tag) {
+    using T = decltype(tag);
+    constexpr int V = 16 / sizeof(T);
+    if (C % V != 0) return cudaErrorInvalidValue;
+    const long long total = (long long)N * (C / V);
+    avgpool_nhwc_kernel<T><<<grid_for(total, 128), 128, 0, stream>>>(
+        static_cast<const T*>(src), static_cast<T*>(dst), N, HW, C);
+    return cudaGetLastError();
+  });
+}
+
+cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean,
+                           const void* var, DType dt, int C, float* scale, float* shift,
+                           cudaStream_t stream) {
+  return by_dtype(dt, [&](auto tag) {
+    using T = decltype(tag);
+    bn_fold_kernel<T><<<(C + 127) / 128, 128, 0, stream>>>(
+        static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<const T*>(mean),
+        static_cast<const T*>(var), C, scale, shift);
+    return cudaGetLastError();
+  });
+}
+
+cudaError_t launch_convert(const void* src, DType src_dt, void* dst, DType dst_dt, size_t n,
+                           cudaStream_t stream) {
+  return by_dtype(src_dt, [&](auto stag) {
+    using S = decltype(stag);
+    return by_dtype(dst_dt, [&](auto dtag) {
+      using D = decltype(dtag);
+      convert_kernel<S, D><<<grid_for((long long)n, 256), 256, 0, stream>>>(
+          static_cast<const S*>(src), static_cast<D*>(dst), n);
+      return cudaGetLastError();
+    });
+  });
+}
+
+}  // namespace nncv_b200

@@ -1,0 +1,176 @@
+"""GPU parity of the single kernels against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+from oracle import binding as ob  # noqa: E402
+from nncv_b200._lib import BF16, F16, F32, check, lib  # noqa: E402
+import gpu_util as G  # noqa: E402
+
+TOL_16 = 2e-3   # fp16/bf16 operands, fp32 accumulate, vs the fp64-accumulated oracle on the same rounded inputs
+TOL_32 = 1e-5
+
+
+def _rng(seed):
+    return np.random.default_rng(seed)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 64, 64), (256, 128, 256), (512, 512, 512), (100, 1000, 72),
+                                   (1, 8, 8), (300, 200, 1024), (1024, 1024, 1024)])
+@pytest.mark.parametrize("ab", [F16, BF16])
+def test_matmul_tcgen05(m, n, k, ab):
+    r = _rng(m * 7 + n * 3 + k)
+    a = r.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = r.uniform(-1, 1, (k, n)).astype(np.float32)
+    c, ar, br = G.matmul(a, b, ab, F32)
+    ref = ob.matmul(ar, br, acc64=True)
+    assert np.isfinite(c).all()
+    assert G.rel_l2(c, ref) <= 1e-5  # same rounded inputs, fp32 accumulate: only summation order differs
+
+
+@pytest.mark.parametrize("c_dt", ["same", "f32"])
+def test_matmul_bias_relu(c_dt):
+    r = _rng(5)
+    m, n, k = 384, 320, 192
+    a = r.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = r.uniform(-1, 1, (k, n)).astype(np.float32)
+    bias = r.standard_normal(n).astype(np.float32)
+    c, ar, br = G.matmul(a, b, F16, F16 if c_dt == "same" else F32, bias, True)
+    ref = ob.matmul(ar, br, bias, True, acc64=True)
+    assert (c >= 0).all()
+    assert G.rel_l2(c, ref) <= (TOL_16 if c_dt == "same" else 1e-5)
+
+
+def test_matmul_f32_simt():
+    r = _rng(6)
+    m, n, k = 200, 136, 260
+    a = r.uniform(-1, 1, (m, k)).astype(np.float32)
+    b = r.uniform(-1, 1, (k, n)).astype(np.float32)
+    bias = r.standard_normal(n).astype(np.float32)
+    c, _, _ = G.matmul(a, b, F32, F32, bias, True)
+    assert G.rel_l2(c, ob.matmul(a, b, bias, True, acc64=True)) <= TOL_32
+
+
+CONV_CASES = [
+    # n, c, h, w, k, r, stride, pad
+    (2, 64, 16, 16, 64, 3, 1, 1),
+    (2, 64, 16, 16, 128, 3, 2, 1),
+    (2, 64, 16, 16, 128, 1, 2, 0),
+    (2, 3, 32, 32, 64, 7, 2, 3),
+    (1, 128, 7, 7, 256, 3, 1, 1),
+    (3, 16, 9, 11, 24, 3, 1, 1),     # ragged everything
+    (1, 256, 14, 14, 512, 1, 1, 0),
+    (1, 512, 7, 7, 512, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+@pytest.mark.parametrize("dtype", [F16, BF16, F32])
+def test_conv_epilogue(case, dtype):
+    n, c, h, w, k, r, stride, pad = case
+    g = _rng(sum(case))
+    x = g.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = (g.standard_normal((k, c, r, r)) * np.sqrt(2.0 / (c * r * r))).astype(np.float32)
+    scale = g.uniform(0.5, 1.5, k).astype(np.float32)
+    shift = (g.standard_normal(k) * 0.1).astype(np.float32)
+    oh, ow = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - r) // stride + 1
+    res = g.standard_normal((n, k, oh, ow)).astype(np.float32)
+    conv = G.Conv(wt, stride, pad, dtype)
+    try:
+        y, xr = conv.run(x, scale, shift, res, True)
+    finally:
+        conv.close()
+    if dtype == F32:
+        wr, rr = wt, res
+    else:
+        tdt = G.TORCH_DT[dtype]
+        wr = torch.from_numpy(wt).to(tdt).float().numpy()
+        rr = torch.from_numpy(res).to(tdt).float().numpy()
+    ref = ob.conv2d(xr, wr, stride, pad, acc64=True) * scale[None, :, None, None] + shift[None, :, None, None] + rr
+    ref = np.where(ref > 0, ref, 0)
+    assert y.shape == ref.shape and np.isfinite(y).all()
+    tol = TOL_32 if dtype == F32 else (TOL_16 if dtype == F16 else 8e-3)
+    assert G.rel_l2(y, ref) <= tol
+
+
+@pytest.mark.parametrize("dtype", [F16, F32])
+def test_conv_kat0_split_params(dtype, golden_dir):
+    """tests/SplitParams/data.mlir of the reference: all-ones input -> every output is 15."""
+    from nncv_b200.memref import MemRefFlatArray
+    arr = MemRefFlatArray.read(f"{golden_dir}/kat0_two_params.bin")
+    w2, w1 = arr.tensors[0].data, arr.tensors[1].data
+    x = np.ones((1, 3, 224, 224), np.float32)
+    c1, c2 = G.Conv(w1, 1, 0, dtype), G.Conv(w2, 1, 0, dtype)
+    try:
+        y1, _ = c1.run(x)
+        y2, _ = c2.run(y1)
+    finally:
+        c1.close()
+        c2.close()
+    assert y2.shape == (1, 1, 218, 218)
+    assert (y2 == 15.0).all()
+
+
+def test_conv_winograd_fixture_closed_form():
+    """tests/ConvOptimization/conv2dNchwWinograd.mlir: 1x16x16x4 input, 3x3x4x16 filter splat 0.1:
+    all-ones input and zero init give 0.1 * 36 = 3.6 everywhere."""
+    x = np.ones((1, 4, 16, 16), np.float32)
+    w = np.full((16, 4, 3, 3), 0.1, np.float32)
+    conv = G.Conv(w, 1, 0, F32)
+    try:
+        y, _ = conv.run(x)
+    finally:
+        conv.close()
+    assert y.shape == (1, 16, 14, 14)
+    np.testing.assert_allclose(y, 3.6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("dtype", [F16, F32])
+def test_maxpool(dtype):
+    g = _rng(11)
+    x = g.standard_normal((2, 64, 17, 19)).astype(np.float32)
+    X = G.dev(x.transpose(0, 2, 3, 1), dtype)
+    oh, ow = (17 + 2 - 3) // 2 + 1, (19 + 2 - 3) // 2 + 1
+    Y = torch.empty((2, oh, ow, 64), device="cuda", dtype=G.TORCH_DT[dtype])
+    check(lib().nncv_b200_maxpool_nhwc(G.p(X), G.p(Y), dtype, 2, 17, 19, 64, 3, 2, 1, G.stream_ptr()))
+    torch.cuda.synchronize()
+    ref = ob.maxpool(G.host(X).transpose(0, 3, 1, 2), 3, 2, 1)
+    assert np.array_equal(G.host(Y).transpose(0, 3, 1, 2), ref)   # max is exact
+
+
+@pytest.mark.parametrize("dtype", [F16, F32])
+def test_avgpool(dtype):
+    g = _rng(12)
+    x = g.standard_normal((3, 512, 7, 7)).astype(np.float32)
+    X = G.dev(x.transpose(0, 2, 3, 1), dtype)
+    Y = torch.empty((3, 512), device="cuda", dtype=G.TORCH_DT[dtype])
+    check(lib().nncv_b200_avgpool_nhwc(G.p(X), G.p(Y), dtype, 3, 49, 512, G.stream_ptr()))
+    torch.cuda.synchronize()
+    ref = ob.avgpool_global(G.host(X).transpose(0, 3, 1, 2))
+    assert G.rel_l2(G.host(Y), ref) <= (1e-3 if dtype == F16 else 1e-6)
+
+
+def test_nchw_to_nhwc_and_bn_fold():
+    g = _rng(13)
+    x = g.standard_normal((2, 3, 10, 12)).astype(np.float32)
+    X = G.dev(x, F32)
+    Y = torch.empty((2, 10, 12, 8), device="cuda", dtype=torch.float16)
+    check(lib().nncv_b200_nchw_to_nhwc(G.p(X), F32, G.p(Y), F16, 2, 3, 10, 12, 8, G.stream_ptr()))
+    torch.cuda.synchronize()
+    y = G.host(Y)
+    assert (y[..., 3:] == 0).all()
+    assert np.array_equal(y[..., :3], x.astype(np.float16).astype(np.float32).transpose(0, 2, 3, 1))
+    c = 70
+    gamma, beta = g.uniform(0.5, 1.5, c).astype(np.float32), g.standard_normal(c).astype(np.float32)
+    mean, var = g.standard_normal(c).astype(np.float32), g.uniform(0.5, 1.5, c).astype(np.float32)
+    sc = torch.empty(c, device="cuda")
+    sh = torch.empty(c, device="cuda")
+    t = [G.dev(v, F32) for v in (gamma, beta, mean, var)]
+    check(lib().nncv_b200_bn_fold(G.p(t[0]), G.p(t[1]), G.p(t[2]), G.p(t[3]), F32, c, G.p(sc), G.p(sh), G.stream_ptr()))
+    torch.cuda.synchronize()
+    xs = g.standard_normal((1, c, 4, 4)).astype(np.float32)
+    ref = ob.batchnorm(xs, gamma, beta, mean, var)
+    got = xs * G.host(sc)[None, :, None, None] + G.host(sh)[None, :, None, None]
+    assert G.rel_l2(got, ref) <= 1e-6
