@@ -106,10 +106,28 @@ int nncv_b200_unload(void);
 /* Forward with an explicit CUDA stream and device-resident src/dst; does not synchronise.
  * The same computation as _mlir_ciface_forward without the host copies. */
 int nncv_b200_forward_device(nncv_memref2* dst, nncv_memref4* src, void* cuda_stream);
+/* Makes _mlir_ciface_forward run on the caller's CUDA stream (enable != 0) instead of the
+ * library's own; the call still synchronises that stream before it returns.  No counterpart in
+ * the reference (it has no device). */
+int nncv_b200_set_stream(void* cuda_stream, int enable);
 int nncv_b200_last_status(void);
 const char* nncv_b200_last_error(void);
 /* Number of kernels of this library launched since load (for benchmark accounting). */
 long long nncv_b200_launch_count(void);
+
+/* Per-launch timing with CUDA events on the launching stream (off by default).  The reference
+ * only has wall-clock timers around the whole forward (examples/Res18/main.cpp:95-99). */
+typedef struct {
+  int kind;      /* 0 tcgen05 implicit GEMM, 1 fp32 CUDA-core conv, 2 Winograd, 3 memory-bound helper */
+  int M, N, K;   /* GEMM view of the launch (helpers: elements, channels, 0) */
+  int bn;        /* N tile (kind 0); helper id (kind 3) */
+  double flops;  /* algorithmic: 2*M*N*K with K = C*R*S (direct-convolution count) */
+  double bytes;  /* algorithmic: each operand and result once */
+  float ms;      /* device time of the launch */
+} nncv_b200_prof_rec;
+int nncv_b200_profile(int enable); /* clears the records; enable != 0 starts recording */
+long long nncv_b200_profile_count(void);
+int nncv_b200_profile_get(long long i, nncv_b200_prof_rec* out);
 
 /* ---- container reader / writer: MemRefFlatArray::read/write, DataType.cpp:9-87 ----------
  * read: returns a handle (NULL on error); tensors are addressed by index in file order. */

@@ -18,7 +18,8 @@ LIB_PATH = os.path.join(_HERE, "libnncv_b200.so")
 EXPORTS = [
     "_mlir_ciface_forward", "nncv_b200_load", "nncv_b200_load_blob", "nncv_b200_unload",
     "nncv_b200_forward_device", "nncv_b200_last_status", "nncv_b200_last_error",
-    "nncv_b200_launch_count",
+    "nncv_b200_launch_count", "nncv_b200_set_stream", "nncv_b200_profile", "nncv_b200_profile_count",
+    "nncv_b200_profile_get",
     "nncv_flat_array_read", "nncv_flat_array_free", "nncv_flat_array_count",
     "nncv_flat_array_indexer", "nncv_flat_array_data", "nncv_flat_array_wrapped",
     "nncv_flat_array_write",
@@ -27,6 +28,11 @@ EXPORTS = [
 ]
 
 F32, F16, BF16 = 0, 1, 2
+
+
+class ProfRec(ctypes.Structure):
+    _fields_ = [("kind", c_int), ("M", c_int), ("N", c_int), ("K", c_int), ("bn", c_int),
+                ("flops", ctypes.c_double), ("bytes", ctypes.c_double), ("ms", ctypes.c_float)]
 
 
 class Opts(ctypes.Structure):
@@ -55,6 +61,10 @@ def lib() -> ctypes.CDLL:
     L.nncv_b200_last_status.restype = c_int
     L.nncv_b200_last_error.restype = c_char_p
     L.nncv_b200_launch_count.restype = c_longlong
+    L.nncv_b200_set_stream.argtypes = [c_void_p, c_int]
+    L.nncv_b200_profile.argtypes = [c_int]
+    L.nncv_b200_profile_count.restype = c_longlong
+    L.nncv_b200_profile_get.argtypes = [c_longlong, POINTER(ProfRec)]
     L.nncv_flat_array_read.argtypes = [c_char_p]
     L.nncv_flat_array_read.restype = c_void_p
     L.nncv_flat_array_free.argtypes = [c_void_p]

@@ -68,6 +68,8 @@ struct Device {
   int id = -1;
   cudaStream_t stream = nullptr;
   int* error_flag = nullptr;   // device
+  cudaStream_t user_stream = nullptr;  // stream _mlir_ciface_forward runs on when set
+  bool user_stream_set = false;
   void* scratch = nullptr;     // grow-only scratch (packed B of nncv_b200_matmul)
   size_t scratch_bytes = 0;
 };
@@ -111,6 +113,38 @@ int ensure_scratch(size_t bytes) {
     return fail(NNCV_B200_ENOMEM, "cudaMalloc(%zu) for scratch failed", want);
   g_dev.scratch_bytes = want;
   return NNCV_B200_OK;
+}
+
+// ---- per-launch timing (off by default): CUDA events on the launching stream around each
+// kernel of a forward, so a benchmark can attribute time to kernels without a profiler.
+struct ProfRec {
+  int kind;  // 0 tcgen05 igemm, 1 fp32 CUDA-core conv, 2 winograd, 3 memory-bound helper
+  double flops, bytes;
+  int M, N, K, bn;
+  cudaEvent_t e0, e1;
+  float ms;
+};
+bool g_prof_on = false;
+std::vector<ProfRec> g_prof;
+
+void prof_begin(int kind, double flops, double bytes, int M, int N, int K, int bn, cudaStream_t st) {
+  if (!g_prof_on) return;
+  ProfRec r{kind, flops, bytes, M, N, K, bn, nullptr, nullptr, -1.0f};
+  cudaEventCreate(&r.e0);
+  cudaEventCreate(&r.e1);
+  cudaEventRecord(r.e0, st);
+  g_prof.push_back(r);
+}
+void prof_end(cudaStream_t st) {
+  if (!g_prof_on || g_prof.empty()) return;
+  cudaEventRecord(g_prof.back().e1, st);
+}
+void prof_clear() {
+  for (auto& r : g_prof) {
+    if (r.e0) cudaEventDestroy(r.e0);
+    if (r.e1) cudaEventDestroy(r.e1);
+  }
+  g_prof.clear();
 }
 
 // Reads and clears the device-side status word; call after the stream has been synchronised.
@@ -204,7 +238,13 @@ int conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int H, int W, 
     a.residual = (const float*)residual; a.out = (float*)out;
     a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
     a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.ldo = ldo; a.relu = relu;
+    const double Ms = (double)N * OH * OW;
+    prof_begin(1, 2.0 * Ms * c->Kout * c->C * c->R * c->S,
+               4.0 * ((double)N * H * W * c->C + (double)c->Kout * c->C * c->R * c->S +
+                      Ms * c->Kout * (residual ? 2 : 1)),
+               (int)Ms, c->Kout, c->C * c->R * c->S, 64, st);
     LAUNCH(launch_conv_simt_f32(a, st));
+    prof_end(st);
     return NNCV_B200_OK;
   }
   const long long M = (long long)N * OH * OW;
@@ -217,7 +257,12 @@ int conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int H, int W, 
   a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
   a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.ldo = ldo; a.bn = bn;
   a.ab = c->dtype; a.out_dtype = out_dt; a.relu = relu; a.error_flag = g_dev.error_flag;
+  prof_begin(0, 2.0 * (double)M * c->Kout * c->C * c->R * c->S,
+             2.0 * ((double)N * H * W * c->C + (double)c->Kout * c->C * c->R * c->S +
+                    (double)M * c->Kout * (residual ? 2 : 1)) + (out_dt == kF32 ? 2.0 * M * c->Kout : 0.0),
+             (int)M, c->Kout, c->C * c->R * c->S, bn, st);
   LAUNCH(launch_conv_igemm(a, st));
+  prof_end(st);
   return NNCV_B200_OK;
 }
 
@@ -398,7 +443,10 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
   const DType adt = m.act_dt;
   size_t gi = 0;
   // NCHW -> NHWC (channels padded), io type -> activation type
+  const double aes = (double)dtype_size(adt);
+  prof_begin(3, 0, (double)N * H * W * (3.0 * m.ele_width + m.convs[0]->Cpad * aes), N * H * W, 3, 0, 0, st);
   LAUNCH(launch_nchw_to_nhwc(src_dev, m.io_dt, m.in_nhwc.p, adt, N, 3, H, W, m.convs[0]->Cpad, st));
+  prof_end(st);
   int h = H, w = W;
   auto out_hw = [](int x, const nncv_b200_conv& c) { return (x + 2 * c.pad - c.R) / c.stride + 1; };
   auto run = [&](size_t idx, const void* in, void* out, int ih, int iw, const void* res, int relu) {
@@ -410,7 +458,10 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
   if (rc) return rc;
   h = out_hw(h, *m.convs[gi]); w = out_hw(w, *m.convs[gi]);
   ++gi;
+  prof_begin(3, 0, aes * 64.0 * N * ((double)h * w + (double)((h + 2 - 3) / 2 + 1) * ((w + 2 - 3) / 2 + 1)),
+             N * h * w, 64, 0, 1, st);
   LAUNCH(launch_maxpool_nhwc(m.stem.p, m.act[0].p, adt, N, h, w, 64, 3, 2, 1, st));
+  prof_end(st);
   h = (h + 2 - 3) / 2 + 1; w = (w + 2 - 3) / 2 + 1;
   int xi = 0;  // index of the buffer holding the block input
   const int nb18[4] = {2, 2, 2, 2}, nb50[4] = {3, 4, 6, 3};
@@ -452,7 +503,9 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
     }
   }
   // global average pool (Res18.mlir:606-614) and FC (:617-628)
+  prof_begin(3, 0, aes * m.spec.fc_in * N * (h * w + 1.0), N * h * w, m.spec.fc_in, 0, 2, st);
   LAUNCH(launch_avgpool_nhwc(m.act[xi].p, m.pooled.p, adt, N, h * w, m.spec.fc_in, st));
+  prof_end(st);
   rc = conv_run(m.fc.get(), m.pooled.p, m.logits32.p, N, 1, 1, nullptr, (const float*)m.fc_bias.p,
                 nullptr, 0, kF32, 1000, st);
   if (rc) return rc;
@@ -531,7 +584,7 @@ int forward_impl(nncv_memref2* dst, nncv_memref4* src, void* params, cudaStream_
   const bool src_dev = is_device_ptr(sp), dst_dev = is_device_ptr(dp);
   if (device_only && (!src_dev || !dst_dev))
     return fail(NNCV_B200_EINVAL, "nncv_b200_forward_device needs device-resident src and dst");
-  cudaStream_t st = device_only && user_stream ? user_stream : g_dev.stream;
+  cudaStream_t st = device_only ? user_stream : (g_dev.user_stream_set ? g_dev.user_stream : g_dev.stream);
   if ((rc = ensure_workspace(m, N, H, W))) return rc;
   const void* src_d = sp;
   if (!src_dev) {
@@ -726,6 +779,41 @@ int nncv_b200_forward_device(nncv_memref2* dst, nncv_memref4* src, void* cuda_st
   std::lock_guard<std::mutex> lk(g_mutex);
   if (!g_model) return fail(NNCV_B200_ENOMODEL, "no model loaded");
   return forward_impl(dst, src, nullptr, (cudaStream_t)cuda_stream, true);
+}
+
+int nncv_b200_set_stream(void* cuda_stream, int enable) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  g_dev.user_stream = (cudaStream_t)cuda_stream;
+  g_dev.user_stream_set = enable != 0;
+  return ok();
+}
+
+int nncv_b200_profile(int enable) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (g_dev.ready) cudaDeviceSynchronize();
+  prof_clear();
+  g_prof_on = enable != 0;
+  return ok();
+}
+
+long long nncv_b200_profile_count(void) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  return (long long)g_prof.size();
+}
+
+int nncv_b200_profile_get(long long i, nncv_b200_prof_rec* out) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (!out || i < 0 || i >= (long long)g_prof.size()) return fail(NNCV_B200_EINVAL, "profile_get: bad index");
+  ProfRec& r = g_prof[(size_t)i];
+  if (r.ms < 0) {
+    CU(cudaEventSynchronize(r.e1));
+    CU(cudaEventElapsedTime(&r.ms, r.e0, r.e1));
+  }
+  out->kind = r.kind; out->M = r.M; out->N = r.N; out->K = r.K; out->bn = r.bn;
+  out->flops = r.flops; out->bytes = r.bytes; out->ms = r.ms;
+  return ok();
 }
 
 int nncv_b200_last_status(void) { return g_status; }

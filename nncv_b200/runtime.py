@@ -64,3 +64,23 @@ def forward_device(dst, src, stream: int = 0) -> None:
 
 def launch_count() -> int:
     return int(lib().nncv_b200_launch_count())
+
+
+def set_stream(stream: int, enable: bool = True) -> None:
+    """Run `_mlir_ciface_forward` on the caller's CUDA stream."""
+    check(lib().nncv_b200_set_stream(ctypes.c_void_p(stream), int(enable)))
+
+
+def profile(enable: bool) -> None:
+    check(lib().nncv_b200_profile(int(enable)))
+
+
+def profile_records():
+    """Per-launch records (kind, M, N, K, bn, flops, bytes, ms) since profile(True)."""
+    out = []
+    n = int(lib().nncv_b200_profile_count())
+    for i in range(n):
+        r = _lib.ProfRec()
+        check(lib().nncv_b200_profile_get(i, ctypes.byref(r)))
+        out.append(dict(kind=r.kind, M=r.M, N=r.N, K=r.K, bn=r.bn, flops=r.flops, bytes=r.bytes, ms=r.ms))
+    return out
