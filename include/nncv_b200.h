@@ -154,8 +154,9 @@ int nncv_b200_matmul(const void* A, const void* B, void* C, int M, int N, int K,
  * epilogue, on NHWC activations.  Weights are prepared once into a plan. */
 typedef struct nncv_b200_conv nncv_b200_conv;
 /* weights: host or device [Kout,C,R,S] of w_dtype.  dtype: activation type (F16/BF16 -> tcgen05
- * implicit GEMM, F32 -> CUDA-core).  algo: 0 = implicit GEMM, 1 = Winograd F(2x2,3x3) (3x3
- * stride-1 pad-1 only).  Activation channel count is C rounded up to 8 (F16/BF16) or 4 (F32). */
+ * implicit GEMM, F32 -> CUDA-core).  algo: 0 = implicit GEMM with a gathered A operand (any
+ * shape), 2 = 3x3 stride-1 pad-1 implicit GEMM whose nine taps are shifted views of one
+ * shared-memory halo tile (16-bit types, C and Kout multiples of 64).  Activation channel count is C rounded up to 8 (F16/BF16) or 4 (F32). */
 nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout, int C, int R,
                                       int S, int stride, int pad, int dtype, int algo);
 void nncv_b200_conv_destroy(nncv_b200_conv* c);
@@ -163,6 +164,11 @@ void nncv_b200_conv_destroy(nncv_b200_conv* c);
 int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int H, int W,
                        const float* scale, const float* shift, const void* residual, int relu,
                        void* stream);
+
+/* algo 2 only: force the tile configuration (N tile 64/128/256, sub-tiles per CTA 1/2/4,
+ * weights resident in shared memory or streamed); bn = 0 restores the built-in choice.  A tuning
+ * and test hook with no counterpart in the reference. */
+int nncv_b200_conv_set_tile(nncv_b200_conv* c, int bn, int mt, int resident);
 
 /* tensor.pad(-inf) + linalg.pooling_nchw_max (Res18.mlir:144-151), NHWC. */
 int nncv_b200_maxpool_nhwc(const void* in, void* out, int dtype, int N, int H, int W, int C,

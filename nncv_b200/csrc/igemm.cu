@@ -49,6 +49,7 @@ struct IgemmParams {
   int M, H, W, C, OH, OW, Kout, R, S, stride, pad;
   int k_blocks;
   int relu, out_f32, bf16;
+  Layout il, ol;  // input / output(+residual) layouts
 };
 
 __device__ __forceinline__ void report(int* flag, int code) {
@@ -98,20 +99,23 @@ __global__ void __launch_bounds__(kThreads) conv_igemm_kernel(const IgemmParams 
   if (warp < 4) {
     // ------------------------------------------------------------- A producer ---------
     const int row = threadIdx.x;
-    const long long m = (long long)m_tile * kBM + row;
-    const bool valid = m < p.M;
+    const long long m_log = (long long)m_tile * kBM + row;   // logical output pixel
+    const bool valid = m_log < p.M;
     int iy0 = 0, ix0 = 0;
+    long long m = 0;                                          // output slot
     const uint16_t* img = p.in;
     if (valid) {
       const int ohw = p.OH * p.OW;
-      const int n_img = (int)(m / ohw);
-      const int rem = (int)(m - (long long)n_img * ohw);
+      const int n_img = (int)(m_log / ohw);
+      const int rem = (int)(m_log - (long long)n_img * ohw);
       const int oy = rem / p.OW;
       const int ox = rem - oy * p.OW;
-      iy0 = oy * p.stride - p.pad;
-      ix0 = ox * p.stride - p.pad;
-      img = p.in + (size_t)n_img * p.H * p.W * p.C;
+      iy0 = oy * p.stride - p.pad + p.il.off;
+      ix0 = ox * p.stride - p.pad + p.il.off;
+      img = p.in + (size_t)n_img * p.il.img_rows * p.il.pitch * p.C;
+      m = ((long long)n_img * p.ol.img_rows + oy + p.ol.off) * p.ol.pitch + ox + p.ol.off;
     }
+    const int y_lo = p.il.off, y_hi = p.H + p.il.off, x_lo = p.il.off, x_hi = p.W + p.il.off;
     const uint32_t row_off = (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
     const uint32_t sw = (uint32_t)(row & 7);
     int r = 0, s = 0, c0 = 0;
@@ -128,9 +132,8 @@ __global__ void __launch_bounds__(kThreads) conv_igemm_kernel(const IgemmParams 
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int iy = iy0 + r, ix = ix0 + s;
-        const bool ok = valid && r < p.R && (unsigned)iy < (unsigned)p.H &&
-                        (unsigned)ix < (unsigned)p.W;
-        const uint16_t* src = ok ? img + ((size_t)iy * p.W + ix) * p.C + c0 : p.in;
+        const bool ok = valid && r < p.R && iy >= y_lo && iy < y_hi && ix >= x_lo && ix < x_hi;
+        const uint16_t* src = ok ? img + ((size_t)iy * p.il.pitch + ix) * p.C + c0 : p.in;
         ptx::cp_async_16(dst + (((uint32_t)j ^ sw) << 4), src, ok ? 16u : 0u);
         c0 += 8;
         if (c0 == p.C) {
@@ -424,6 +427,8 @@ cudaError_t launch_conv_igemm(const IgemmArgs& a, cudaStream_t stream) {
   p.H = a.H; p.W = a.W; p.C = a.C; p.OH = a.OH; p.OW = a.OW; p.Kout = a.Kout;
   p.R = a.R; p.S = a.S; p.stride = a.stride; p.pad = a.pad;
   p.k_blocks = igemm_k_blocks(a.C, a.R, a.S);
+  p.il = a.in_l.pitch ? a.in_l : dense_layout(a.H, a.W);
+  p.ol = a.out_l.pitch ? a.out_l : dense_layout(a.OH, a.OW);
   p.relu = a.relu;
   p.out_f32 = a.out_dtype == kF32;
   p.bf16 = a.ab == kBF16;

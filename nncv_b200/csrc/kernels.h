@@ -20,6 +20,17 @@ enum KernelError : int {
   kErrWaitEpilogue = 4,  // epilogue gave up waiting for the accumulator
 };
 
+// Where pixel (n, y, x) of a logical [N,H,W,C] activation lives: slot
+// (n*img_rows + y + off)*pitch + x + off, each slot holding C contiguous channels.
+//   dense NHWC:      img_rows = H,   pitch = W,   off = 0
+//   shared-pad NHWC: img_rows = H+1, pitch = W+1, off = 1 (row 0 / column 0 are zero pads)
+struct Layout {
+  int img_rows, pitch, off;
+};
+inline Layout dense_layout(int H, int W) { return Layout{H, W, 0}; }
+inline Layout sp_layout(int H, int W) { return Layout{H + 1, W + 1, 1}; }
+inline long long layout_slots(Layout l, int N) { return (long long)N * l.img_rows * l.pitch; }
+
 // ---- implicit-GEMM convolution / GEMM on tcgen05 ---------------------------------------
 // Activations NHWC with C a multiple of 8, weights packed by launch_pack_weights().
 struct IgemmArgs {
@@ -31,6 +42,8 @@ struct IgemmArgs {
   void* out = nullptr;             // [M,ldo] out_dtype
   int N = 0, H = 0, W = 0, C = 0, OH = 0, OW = 0, Kout = 0, R = 1, S = 1, stride = 1, pad = 0;
   long long ldo = 0;               // output row pitch in elements (>= Kout)
+  Layout in_l{0, 0, 0};            // zero pitch = dense NHWC
+  Layout out_l{0, 0, 0};           // layout of out and residual
   int bn = 64;                     // N tile the weights were packed for (64, 128 or 256)
   DType ab = kF16;                 // operand type (kF16 or kBF16)
   DType out_dtype = kF16;          // kF16/kBF16 (same as ab) or kF32
@@ -48,6 +61,29 @@ cudaError_t launch_conv_igemm(const IgemmArgs& a, cudaStream_t stream);
 cudaError_t launch_pack_weights(const void* src, DType src_dt, long long sn, long long sc,
                                 long long stap, int Kout, int C, int Cpad, int taps, int bn,
                                 DType dst_dt, void* dst, cudaStream_t stream);
+
+// ---- 3x3 stride-1 pad-1 convolution with shared-memory halo reuse (tcgen05 + TMA) ----------
+// in / out / residual are shared-pad NHWC; C and Kout multiples of 64.
+struct Conv3x3Config {
+  int bn = 64, mt = 1, resident = 0;
+};
+struct Conv3x3Args {
+  const void* in = nullptr;
+  const void* wpack = nullptr;     // packed by launch_pack_weights for N tile `bn`
+  const float* scale = nullptr;
+  const float* shift = nullptr;
+  const void* residual = nullptr;
+  void* out = nullptr;
+  int N = 0, H = 0, W = 0, C = 0, Kout = 0;
+  int bn = 64, mt = 1, resident = 0;
+  DType ab = kF16;
+  int relu = 0;
+  int sm_count = 0;
+  int* error_flag = nullptr;
+};
+bool conv3x3_supported(int C, int Kout, int R, int S, int stride, int pad);
+Conv3x3Config conv3x3_pick(int N, int H, int W, int C, int Kout);
+cudaError_t launch_conv3x3(const Conv3x3Args& a, cudaStream_t stream);
 
 // ---- fp32 SIMT implicit-GEMM convolution (the fp32-accurate path) ------------------------
 struct SimtConvArgs {
@@ -71,9 +107,13 @@ cudaError_t launch_repack_weights_f32(const void* src, DType src_dt, long long s
 cudaError_t launch_nchw_to_nhwc(const void* src, DType src_dt, void* dst, DType dst_dt, int N,
                                 int C, int H, int W, int Cpad, cudaStream_t stream);
 cudaError_t launch_maxpool_nhwc(const void* src, void* dst, DType dt, int N, int H, int W, int C,
-                                int k, int stride, int pad, cudaStream_t stream);
-cudaError_t launch_avgpool_nhwc(const void* src, void* dst, DType dt, int N, int HW, int C,
+                                int k, int stride, int pad, Layout in_l, Layout out_l,
                                 cudaStream_t stream);
+cudaError_t launch_avgpool_nhwc(const void* src, void* dst, DType dt, int N, int H, int W, int C,
+                                Layout in_l, cudaStream_t stream);
+// Copies a [N,H,W,C] activation between layouts; every slot of dst that is a pad becomes zero.
+cudaError_t launch_relayout(const void* src, Layout src_l, void* dst, Layout dst_l, DType dt, int N,
+                            int H, int W, int C, cudaStream_t stream);
 // scale = gamma * rsqrt(var + 1e-5f); shift = beta - mean * scale  (inputs of type dt)
 cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean,
                            const void* var, DType dt, int C, float* scale, float* shift,

@@ -41,6 +41,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Bounded wait that also gives up as soon as another role of the CTA has raised `*abort_flag`
+// (a shared-memory word), so one lost arrival ends the whole CTA within about a second.
+__device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity,
+                                                    volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > (1LL << 31)) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+  return true;
+}
+
 // Bounded wait: gives up after ~2^31 clocks (about a second) and reports false, so a lost
 // arrival turns into an error status instead of a hung GPU.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
@@ -79,6 +95,56 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
           "r"(dst),
       "l"(src), "r"(bytes), "r"(bar)
       : "memory");
+}
+
+// Tiled TMA copies through a CUtensorMap (2-D: c0 = innermost coordinate).  The innermost
+// coordinate times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int c0, int c1,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+          "r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const void* tmap, int c0, int c1, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap),
+               "r"(c0), "r"(c1), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Named barrier that also ANDs a predicate over its participants: every thread gets the same
+// answer, so a group can leave a loop together.
+__device__ __forceinline__ bool named_bar_and(int id, int nthreads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 q, %3, 0;\n"
+      "bar.red.and.pred p, %1, %2, q;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(id), "r"(nthreads), "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
 }
 
 // ---------------------------------------------------------------- tcgen05 -------------
@@ -155,6 +221,12 @@ __device__ __forceinline__ void tmem_ld_wait() {
 //   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4 (unused here)
 //   bits [32,46) stride byte offset >> 4 bits [46,48) descriptor version (1 on sm_100)
 //   bits [61,64) layout type (2 = 128-byte swizzle)
+//   bits [49,52) base offset, left 0: the tensor core applies the 128-byte swizzle to the
+//                ABSOLUTE shared-memory address (chunk bits [4,7) ^= row bits [7,10)), so an operand
+//                may start at any 128-byte row of a buffer whose rows were written with that
+//                same address-based swizzle (TMA with SWIZZLE_128B into a 1024-byte aligned
+//                buffer does) -- measured on B200: every row shift gives exact results with
+//                base offset 0, and wrong ones with (address >> 7) & 7 in the field.
 __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);

@@ -70,6 +70,7 @@ struct Device {
   int* error_flag = nullptr;   // device
   cudaStream_t user_stream = nullptr;  // stream _mlir_ciface_forward runs on when set
   bool user_stream_set = false;
+  int sm_count = 148;
   void* scratch = nullptr;     // grow-only scratch (packed B of nncv_b200_matmul)
   size_t scratch_bytes = 0;
 };
@@ -91,6 +92,7 @@ int device_init() {
     return fail(NNCV_B200_ENODEVICE, "device %d is sm_%d%d; the kernels are built for sm_100a only",
                 dev, prop.major, prop.minor);
   g_dev.id = dev;
+  g_dev.sm_count = prop.multiProcessorCount;
   if (cudaStreamCreateWithFlags(&g_dev.stream, cudaStreamNonBlocking) != cudaSuccess)
     return fail(NNCV_B200_ENODEVICE, "cudaStreamCreate failed");
   if (cudaMalloc(&g_dev.error_flag, sizeof(int)) != cudaSuccess)
@@ -201,6 +203,8 @@ struct nncv_b200_conv {
   std::map<int, std::unique_ptr<DevBuf>> packed;   // tcgen05 path: per N-tile width
   DevBuf w_f32;                                    // fp32 path: [Kout][R*S][Cpad]
   bool w_f32_ready = false;
+  DevBuf sp_in, sp_out, sp_res;                    // standalone algo 2: shared-pad copies
+  Conv3x3Config cfg3{0, 0, 0};                     // algo 2: forced tile configuration (bn 0 = auto)
 };
 
 namespace {
@@ -219,13 +223,16 @@ int conv_prepare(nncv_b200_conv* c, int bn, cudaStream_t st, const void** wpack)
   return NNCV_B200_OK;
 }
 
-int conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int H, int W, const float* scale,
-             const float* shift, const void* residual, int relu, DType out_dt, long long ldo,
-             cudaStream_t st) {
+int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout out_l, int N, int H,
+             int W, const float* scale, const float* shift, const void* residual, int relu,
+             DType out_dt, long long ldo, cudaStream_t st) {
   const int OH = (H + 2 * c->pad - c->R) / c->stride + 1;
   const int OW = (W + 2 * c->pad - c->S) / c->stride + 1;
   if (N <= 0 || OH <= 0 || OW <= 0) return fail(NNCV_B200_EINVAL, "conv: empty output");
+  if (in_l.pitch == 0) in_l = dense_layout(H, W);
+  if (out_l.pitch == 0) out_l = dense_layout(OH, OW);
   if (c->dtype == kF32) {
+    if (in_l.off != 0 || out_l.off != 0) return fail(NNCV_B200_EINVAL, "fp32 conv takes dense NHWC only");
     if (!c->w_f32_ready) {
       int rc = c->w_f32.reserve((size_t)c->Kout * c->R * c->S * c->Cpad * sizeof(float));
       if (rc) return rc;
@@ -248,6 +255,28 @@ int conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int H, int W, 
     return NNCV_B200_OK;
   }
   const long long M = (long long)N * OH * OW;
+  const double flops = 2.0 * (double)M * c->Kout * c->C * c->R * c->S;
+  const double bytes = 2.0 * ((double)N * H * W * c->C + (double)c->Kout * c->C * c->R * c->S +
+                              (double)M * c->Kout * (residual ? 2 : 1)) +
+                       (out_dt == kF32 ? 2.0 * M * c->Kout : 0.0);
+  if (c->algo == 2) {
+    // shifted-view 3x3: shared-pad layouts on both sides
+    if (in_l.off != 1 || out_l.off != 1 || out_dt != c->dtype || ldo != c->Kout)
+      return fail(NNCV_B200_EINVAL, "conv3x3: needs shared-pad NHWC input and output");
+    const Conv3x3Config cfg = c->cfg3.bn ? c->cfg3 : conv3x3_pick(N, H, W, c->Cpad, c->Kout);
+    const void* wpack = nullptr;
+    int rc = conv_prepare(c, cfg.bn, st, &wpack);
+    if (rc) return rc;
+    Conv3x3Args a;
+    a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
+    a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.Kout = c->Kout;
+    a.bn = cfg.bn; a.mt = cfg.mt; a.resident = cfg.resident; a.ab = c->dtype; a.relu = relu;
+    a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
+    prof_begin(2, flops, bytes, (int)M, c->Kout, c->C * 9, cfg.bn * 1000 + cfg.mt * 10 + cfg.resident, st);
+    LAUNCH(launch_conv3x3(a, st));
+    prof_end(st);
+    return NNCV_B200_OK;
+  }
   const int bn = igemm_pick_bn(M, c->Kout);
   const void* wpack = nullptr;
   int rc = conv_prepare(c, bn, st, &wpack);
@@ -256,11 +285,9 @@ int conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int H, int W, 
   a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
   a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
   a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.ldo = ldo; a.bn = bn;
+  a.in_l = in_l; a.out_l = out_l;
   a.ab = c->dtype; a.out_dtype = out_dt; a.relu = relu; a.error_flag = g_dev.error_flag;
-  prof_begin(0, 2.0 * (double)M * c->Kout * c->C * c->R * c->S,
-             2.0 * ((double)N * H * W * c->C + (double)c->Kout * c->C * c->R * c->S +
-                    (double)M * c->Kout * (residual ? 2 : 1)) + (out_dt == kF32 ? 2.0 * M * c->Kout : 0.0),
-             (int)M, c->Kout, c->C * c->R * c->S, bn, st);
+  prof_begin(0, flops, bytes, (int)M, c->Kout, c->C * c->R * c->S, bn, st);
   LAUNCH(launch_conv_igemm(a, st));
   prof_end(st);
   return NNCV_B200_OK;
@@ -344,7 +371,12 @@ struct Model {
   const void* host_blob_id = nullptr;  // pointer identity of the blob the plan was built from
   // per-shape workspace
   int wsN = 0, wsH = 0, wsW = 0;
-  DevBuf in_stage, in_nhwc, stem, act[5], pooled, logits32, logits_io;
+  DevBuf in_stage, in_nhwc, stem, pooled, logits32, logits_io;
+  // One buffer per activation tensor of the forward, handed out in call order.  Buffers are
+  // zeroed when created and never shared between tensors, so the pad slots of shared-pad
+  // tensors stay zero no matter which kernel writes the interior.
+  std::vector<std::unique_ptr<DevBuf>> acts;
+  size_t act_next = 0;
 };
 std::unique_ptr<Model> g_model;
 
@@ -386,6 +418,7 @@ int model_build(int depth, const void* host_blob, size_t n_elements, size_t ele_
     c->Kout = g.cout; c->C = g.cin; c->R = g.k; c->S = g.k; c->stride = g.stride; c->pad = g.pad;
     c->dtype = m->act_dt;
     c->Cpad = m->act_dt == kF32 ? (g.cin + 3) / 4 * 4 : (g.cin + 7) / 8 * 8;
+    if (m->act_dt != kF32 && conv3x3_supported(g.cin, g.cout, g.k, g.k, g.stride, g.pad)) c->algo = 2;
     c->raw = at(g.off_w); c->raw_dt = pdt;
     c->sn = (long long)g.cin * g.k * g.k; c->sc = (long long)g.k * g.k; c->stap = 1;
     m->convs.push_back(std::move(c));
@@ -419,19 +452,35 @@ int ensure_workspace(Model& m, int N, int H, int W) {
   const int h1 = (H + 6 - 7) / 2 + 1, w1 = (W + 6 - 7) / 2 + 1;
   const int h2 = (h1 + 2 - 3) / 2 + 1, w2 = (w1 + 2 - 3) / 2 + 1;
   if (h1 <= 0 || w1 <= 0 || h2 <= 0 || w2 <= 0) return fail(NNCV_B200_EINVAL, "input %dx%d too small", H, W);
-  // largest block activation: the first stage (spatial h2 x w2) with its widest channel count
-  const size_t cmax = m.spec.depth == 18 ? 64 : 256;
-  const size_t act_elems = (size_t)N * h2 * w2 * cmax;
+  if (g_dev.ready) cudaDeviceSynchronize();
+  m.acts.clear();
+  m.act_next = 0;
   int rc = 0;
   if ((rc = m.in_stage.reserve((size_t)N * 3 * H * W * m.ele_width))) return rc;
   if ((rc = m.in_nhwc.reserve((size_t)N * H * W * cpad0 * es))) return rc;
   if ((rc = m.stem.reserve((size_t)N * h1 * w1 * 64 * es))) return rc;
-  for (auto& b : m.act)
-    if ((rc = b.reserve(act_elems * es))) return rc;
   if ((rc = m.pooled.reserve((size_t)N * m.spec.fc_in * es))) return rc;
   if ((rc = m.logits32.reserve((size_t)N * 1000 * sizeof(float)))) return rc;
   if ((rc = m.logits_io.reserve((size_t)N * 1000 * m.ele_width))) return rc;
   m.wsN = N; m.wsH = H; m.wsW = W;
+  return NNCV_B200_OK;
+}
+
+// Next activation buffer of the current forward ([N,h,w,c] in layout l); created and zeroed on
+// the first forward of a shape, reused afterwards.
+int next_act(Model& m, int N, int h, int w, int c, Layout l, cudaStream_t st, void** out) {
+  const size_t bytes = (size_t)layout_slots(l, N) * c * dtype_size(m.act_dt);
+  (void)h; (void)w;
+  if (m.act_next == m.acts.size()) {
+    auto b = std::make_unique<DevBuf>();
+    int rc = b->reserve(bytes);
+    if (rc) return rc;
+    CU(cudaMemsetAsync(b->p, 0, bytes, st));
+    m.acts.push_back(std::move(b));
+  }
+  DevBuf& b = *m.acts[m.act_next++];
+  if (b.bytes < bytes) return fail(NNCV_B200_ECUDA, "activation plan changed under a fixed shape");
+  *out = b.p;
   return NNCV_B200_OK;
 }
 
@@ -440,7 +489,10 @@ int ensure_workspace(Model& m, int N, int H, int W) {
 int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cudaStream_t st) {
   int rc = ensure_workspace(m, N, H, W);
   if (rc) return rc;
+  m.act_next = 0;
   const DType adt = m.act_dt;
+  const bool sp = adt != kF32;  // tensor-core path keeps block activations in shared-pad NHWC
+  auto lay = [&](int h, int w) { return sp ? sp_layout(h, w) : dense_layout(h, w); };
   size_t gi = 0;
   // NCHW -> NHWC (channels padded), io type -> activation type
   const double aes = (double)dtype_size(adt);
@@ -449,65 +501,69 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
   prof_end(st);
   int h = H, w = W;
   auto out_hw = [](int x, const nncv_b200_conv& c) { return (x + 2 * c.pad - c.R) / c.stride + 1; };
-  auto run = [&](size_t idx, const void* in, void* out, int ih, int iw, const void* res, int relu) {
+  auto run = [&](size_t idx, const void* in, Layout il, void* out, Layout ol, int ih, int iw,
+                 const void* res, int relu) {
     nncv_b200_conv& c = *m.convs[idx];
-    return conv_run(&c, in, out, N, ih, iw, m.scale[idx], m.shift[idx], res, relu, adt, c.Kout, st);
+    return conv_run(&c, in, il, out, ol, N, ih, iw, m.scale[idx], m.shift[idx], res, relu, adt, c.Kout, st);
   };
   // stem (Res18.mlir:118-143) and max-pool (:144-151)
-  rc = run(gi, m.in_nhwc.p, m.stem.p, h, w, nullptr, 1);
-  if (rc) return rc;
-  h = out_hw(h, *m.convs[gi]); w = out_hw(w, *m.convs[gi]);
-  ++gi;
-  prof_begin(3, 0, aes * 64.0 * N * ((double)h * w + (double)((h + 2 - 3) / 2 + 1) * ((w + 2 - 3) / 2 + 1)),
-             N * h * w, 64, 0, 1, st);
-  LAUNCH(launch_maxpool_nhwc(m.stem.p, m.act[0].p, adt, N, h, w, 64, 3, 2, 1, st));
-  prof_end(st);
-  h = (h + 2 - 3) / 2 + 1; w = (w + 2 - 3) / 2 + 1;
-  int xi = 0;  // index of the buffer holding the block input
+  {
+    const int oh = out_hw(h, *m.convs[gi]), ow = out_hw(w, *m.convs[gi]);
+    rc = run(gi, m.in_nhwc.p, dense_layout(h, w), m.stem.p, dense_layout(oh, ow), h, w, nullptr, 1);
+    if (rc) return rc;
+    h = oh; w = ow;
+    ++gi;
+  }
+  void* x = nullptr;
+  {
+    const int oh = (h + 2 - 3) / 2 + 1, ow = (w + 2 - 3) / 2 + 1;
+    if ((rc = next_act(m, N, oh, ow, 64, lay(oh, ow), st, &x))) return rc;
+    prof_begin(3, 0, aes * 64.0 * N * ((double)h * w + (double)oh * ow), N * h * w, 64, 0, 1, st);
+    LAUNCH(launch_maxpool_nhwc(m.stem.p, x, adt, N, h, w, 64, 3, 2, 1, dense_layout(h, w), lay(oh, ow), st));
+    prof_end(st);
+    h = oh; w = ow;
+  }
   const int nb18[4] = {2, 2, 2, 2}, nb50[4] = {3, 4, 6, 3};
   const int* nb = m.spec.depth == 18 ? nb18 : nb50;
   for (int l = 0; l < 4; ++l) {
     for (int b = 0; b < nb[l]; ++b) {
       const bool has_ds = m.spec.depth == 18 ? (b == 0 && l > 0) : (b == 0);
-      void* x = m.act[xi].p;
-      void* t1 = m.act[(xi + 1) % 5].p;
-      void* t2 = m.act[(xi + 2) % 5].p;
-      void* ds = m.act[(xi + 3) % 5].p;
-      void* y = m.act[(xi + 4) % 5].p;
-      int h1 = h, w1 = w;
-      const void* last = nullptr;
-      size_t last_idx = 0;
-      if (m.spec.depth == 18) {
-        if ((rc = run(gi, x, t1, h1, w1, nullptr, 1))) return rc;
-        h1 = out_hw(h1, *m.convs[gi]); w1 = out_hw(w1, *m.convs[gi]);
+      int ch = h, cw = w;       // spatial size of the tensor flowing through the block body
+      const void* cur = x;
+      const int body = m.spec.depth == 18 ? 1 : 2;  // convs before the last one
+      for (int k = 0; k < body; ++k) {
+        nncv_b200_conv& c = *m.convs[gi];
+        const int oh = out_hw(ch, c), ow = out_hw(cw, c);
+        void* t = nullptr;
+        if ((rc = next_act(m, N, oh, ow, c.Kout, lay(oh, ow), st, &t))) return rc;
+        if ((rc = run(gi, cur, lay(ch, cw), t, lay(oh, ow), ch, cw, nullptr, 1))) return rc;
+        cur = t; ch = oh; cw = ow;
         ++gi;
-        last = t1; last_idx = gi++;
-      } else {
-        if ((rc = run(gi, x, t1, h1, w1, nullptr, 1))) return rc;
-        ++gi;
-        if ((rc = run(gi, t1, t2, h1, w1, nullptr, 1))) return rc;
-        h1 = out_hw(h1, *m.convs[gi]); w1 = out_hw(w1, *m.convs[gi]);
-        ++gi;
-        last = t2; last_idx = gi++;
       }
+      const size_t last_idx = gi++;
+      nncv_b200_conv& cl = *m.convs[last_idx];
+      const int oh = out_hw(ch, cl), ow = out_hw(cw, cl);
       const void* identity = x;
       if (has_ds) {  // BN(conv1x1(identity)) (Res18.mlir:297-311)
-        if ((rc = run(gi, x, ds, h, w, nullptr, 0))) return rc;
+        void* ds = nullptr;
+        if ((rc = next_act(m, N, oh, ow, cl.Kout, lay(oh, ow), st, &ds))) return rc;
+        if ((rc = run(gi, x, lay(h, w), ds, lay(oh, ow), h, w, nullptr, 0))) return rc;
         ++gi;
         identity = ds;
       }
       // last conv of the block: BN, + identity, ReLU (Res18.mlir:180-203)
-      if ((rc = run(last_idx, last, y, h1, w1, identity, 1))) return rc;
-      xi = (xi + 4) % 5;
-      h = h1; w = w1;
+      void* y = nullptr;
+      if ((rc = next_act(m, N, oh, ow, cl.Kout, lay(oh, ow), st, &y))) return rc;
+      if ((rc = run(last_idx, cur, lay(ch, cw), y, lay(oh, ow), ch, cw, identity, 1))) return rc;
+      x = y; h = oh; w = ow;
     }
   }
   // global average pool (Res18.mlir:606-614) and FC (:617-628)
   prof_begin(3, 0, aes * m.spec.fc_in * N * (h * w + 1.0), N * h * w, m.spec.fc_in, 0, 2, st);
-  LAUNCH(launch_avgpool_nhwc(m.act[xi].p, m.pooled.p, adt, N, h * w, m.spec.fc_in, st));
+  LAUNCH(launch_avgpool_nhwc(x, m.pooled.p, adt, N, h, w, m.spec.fc_in, lay(h, w), st));
   prof_end(st);
-  rc = conv_run(m.fc.get(), m.pooled.p, m.logits32.p, N, 1, 1, nullptr, (const float*)m.fc_bias.p,
-                nullptr, 0, kF32, 1000, st);
+  rc = conv_run(m.fc.get(), m.pooled.p, dense_layout(1, 1), m.logits32.p, dense_layout(1, 1), N, 1, 1, nullptr,
+                (const float*)m.fc_bias.p, nullptr, 0, kF32, 1000, st);
   if (rc) return rc;
   if (m.io_dt != kF32)
     LAUNCH(launch_convert(m.logits32.p, kF32, m.logits_io.p, m.io_dt, (size_t)N * 1000, st));
@@ -863,8 +919,12 @@ nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout
     fail(NNCV_B200_EINVAL, "conv_create: bad argument");
     return nullptr;
   }
-  if (algo != 0) {
+  if (algo != 0 && algo != 2) {
     fail(NNCV_B200_EINVAL, "conv_create: algo %d is not available", algo);
+    return nullptr;
+  }
+  if (algo == 2 && (dtype == NNCV_B200_F32 || !conv3x3_supported(C, Kout, R, S, stride, pad))) {
+    fail(NNCV_B200_EINVAL, "conv_create: algo 2 needs a 16-bit 3x3 stride-1 pad-1 conv with C, Kout %% 64 == 0");
     return nullptr;
   }
   auto c = std::make_unique<nncv_b200_conv>();
@@ -894,8 +954,38 @@ int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int 
                        void* stream) {
   std::lock_guard<std::mutex> lk(g_mutex);
   if (!c || !in || !out) return fail(NNCV_B200_EINVAL, "conv_run: null argument");
-  int rc = conv_run(c, in, out, N, H, W, scale, shift, residual, relu, c->dtype, c->Kout, (cudaStream_t)stream);
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc;
+  if (c->algo == 2) {
+    // The kernel works on shared-pad NHWC; this entry point takes dense NHWC, so convert on both
+    // sides (the network executor keeps its activations in shared-pad form and skips this).
+    const Layout dl = dense_layout(H, W), sl = sp_layout(H, W);
+    const size_t es = dtype_size(c->dtype);
+    const size_t slots = (size_t)layout_slots(sl, N);
+    if ((rc = c->sp_in.reserve(slots * c->Cpad * es))) return rc;
+    if ((rc = c->sp_out.reserve(slots * c->Kout * es))) return rc;
+    LAUNCH(launch_relayout(in, dl, c->sp_in.p, sl, c->dtype, N, H, W, c->Cpad, st));
+    const void* res = nullptr;
+    if (residual) {
+      if ((rc = c->sp_res.reserve(slots * c->Kout * es))) return rc;
+      LAUNCH(launch_relayout(residual, dl, c->sp_res.p, sl, c->dtype, N, H, W, c->Kout, st));
+      res = c->sp_res.p;
+    }
+    rc = conv_run(c, c->sp_in.p, sl, c->sp_out.p, sl, N, H, W, scale, shift, res, relu, c->dtype, c->Kout, st);
+    if (rc) return rc;
+    LAUNCH(launch_relayout(c->sp_out.p, sl, out, dl, c->dtype, N, H, W, c->Kout, st));
+    return ok();
+  }
+  rc = conv_run(c, in, Layout{0, 0, 0}, out, Layout{0, 0, 0}, N, H, W, scale, shift, residual, relu, c->dtype,
+                c->Kout, st);
   return rc ? rc : ok();
+}
+
+int nncv_b200_conv_set_tile(nncv_b200_conv* c, int bn, int mt, int resident) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (!c || c->algo != 2) return fail(NNCV_B200_EINVAL, "conv_set_tile: only for algo 2 plans");
+  c->cfg3 = Conv3x3Config{bn, mt, resident};
+  return ok();
 }
 
 int nncv_b200_maxpool_nhwc(const void* in, void* out, int dtype, int N, int H, int W, int C,
@@ -904,7 +994,8 @@ int nncv_b200_maxpool_nhwc(const void* in, void* out, int dtype, int N, int H, i
   int rc = device_init();
   if (rc) return rc;
   if (!in || !out || N <= 0 || k <= 0 || stride <= 0 || dtype < 0 || dtype > 2) return fail(NNCV_B200_EINVAL, "maxpool: bad argument");
-  LAUNCH(launch_maxpool_nhwc(in, out, (DType)dtype, N, H, W, C, k, stride, pad, (cudaStream_t)stream));
+  LAUNCH(launch_maxpool_nhwc(in, out, (DType)dtype, N, H, W, C, k, stride, pad, Layout{0, 0, 0}, Layout{0, 0, 0},
+                             (cudaStream_t)stream));
   return ok();
 }
 
@@ -913,7 +1004,7 @@ int nncv_b200_avgpool_nhwc(const void* in, void* out, int dtype, int N, int HW, 
   int rc = device_init();
   if (rc) return rc;
   if (!in || !out || N <= 0 || HW <= 0 || dtype < 0 || dtype > 2) return fail(NNCV_B200_EINVAL, "avgpool: bad argument");
-  LAUNCH(launch_avgpool_nhwc(in, out, (DType)dtype, N, HW, C, (cudaStream_t)stream));
+  LAUNCH(launch_avgpool_nhwc(in, out, (DType)dtype, N, 1, HW, C, Layout{0, 0, 0}, (cudaStream_t)stream));
   return ok();
 }
 

@@ -154,7 +154,8 @@ __global__ void nchw_to_nhwc_kernel(const SrcT* __restrict__ src, DstT* __restri
 // Max-pool over a -inf padded map; one thread per (output pixel, 16-byte channel vector).
 template <typename T>
 __global__ void maxpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int H,
-                                    int W, int C, int OH, int OW, int k, int stride, int pad) {
+                                    int W, int C, int OH, int OW, int k, int stride, int pad,
+                                    Layout il, Layout ol) {
   constexpr int V = 16 / sizeof(T);
   const int cv = C / V;
   const long long total = (long long)N * OH * OW * cv;
@@ -175,7 +176,8 @@ __global__ void maxpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ d
       for (int s = 0; s < k; ++s) {
         const int ix = ox * stride - pad + s;
         if ((unsigned)ix >= (unsigned)W) continue;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + (((size_t)n * H + iy) * W + ix) * C + c));
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+            src + (((size_t)n * il.img_rows + iy + il.off) * il.pitch + ix + il.off) * C + c));
         const T* v = reinterpret_cast<const T*>(&raw);
 #pragma unroll
         for (int e = 0; e < V; ++e) {
@@ -187,14 +189,16 @@ __global__ void maxpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ d
     alignas(16) T o[V];
 #pragma unroll
     for (int e = 0; e < V; ++e) o[e] = from_f<T>(m[e]);
-    *reinterpret_cast<uint4*>(dst + (((size_t)n * OH + oy) * OW + ox) * C + c) = *reinterpret_cast<const uint4*>(o);
+    *reinterpret_cast<uint4*>(dst + (((size_t)n * ol.img_rows + oy + ol.off) * ol.pitch + ox + ol.off) * C + c) =
+        *reinterpret_cast<const uint4*>(o);
   }
 }
 
 // Global average pool: sum in fp32 over HW then divide by HW; one thread per channel vector.
 template <typename T>
-__global__ void avgpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int HW,
-                                    int C) {
+__global__ void avgpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int H,
+                                    int W, int C, Layout il) {
+  const int HW = H * W;
   constexpr int V = 16 / sizeof(T);
   const int cv = C / V;
   const long long total = (long long)N * cv;
@@ -206,7 +210,9 @@ __global__ void avgpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ d
 #pragma unroll
     for (int e = 0; e < V; ++e) s[e] = 0.0f;
     for (int px = 0; px < HW; ++px) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src + ((size_t)n * HW + px) * C + c));
+      const int y = px / W, x = px - y * W;
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+          src + (((size_t)n * il.img_rows + y + il.off) * il.pitch + x + il.off) * C + c));
       const T* v = reinterpret_cast<const T*>(&raw);
 #pragma unroll
       for (int e = 0; e < V; ++e) s[e] += to_f<T>(v[e]);
@@ -215,6 +221,26 @@ __global__ void avgpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ d
 #pragma unroll
     for (int e = 0; e < V; ++e) o[e] = from_f<T>(s[e] / (float)HW);
     *reinterpret_cast<uint4*>(dst + (size_t)n * C + c) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+// Layout change, one thread per 16-byte vector of a destination slot; pads are written as zero.
+__global__ void relayout_kernel(const uint4* __restrict__ src, Layout sl, uint4* __restrict__ dst,
+                                Layout dl, int N, int H, int W, int cv) {
+  const long long total = (long long)N * dl.img_rows * dl.pitch * cv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % cv);
+    long long t = i / cv;
+    const int xs = (int)(t % dl.pitch);
+    t /= dl.pitch;
+    const int ys = (int)(t % dl.img_rows);
+    const int n = (int)(t / dl.img_rows);
+    const int y = ys - dl.off, x = xs - dl.off;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (y >= 0 && y < H && x >= 0 && x < W)
+      v = __ldg(src + (((size_t)n * sl.img_rows + y + sl.off) * sl.pitch + x + sl.off) * cv + c);
+    dst[i] = v;
   }
 }
 
@@ -295,30 +321,47 @@ cudaError_t launch_nchw_to_nhwc(const void* src, DType src_dt, void* dst, DType 
 }
 
 cudaError_t launch_maxpool_nhwc(const void* src, void* dst, DType dt, int N, int H, int W, int C,
-                                int k, int stride, int pad, cudaStream_t stream) {
+                                int k, int stride, int pad, Layout in_l, Layout out_l,
+                                cudaStream_t stream) {
   const int OH = (H + 2 * pad - k) / stride + 1, OW = (W + 2 * pad - k) / stride + 1;
+  if (in_l.pitch == 0) in_l = dense_layout(H, W);
+  if (out_l.pitch == 0) out_l = dense_layout(OH, OW);
   return by_dtype(dt, [&](auto tag) {
     using T = decltype(tag);
     constexpr int V = 16 / sizeof(T);
     if (C % V != 0) return cudaErrorInvalidValue;
     const long long total = (long long)N * OH * OW * (C / V);
     maxpool_nhwc_kernel<T><<<grid_for(total, 256), 256, 0, stream>>>(
-        static_cast<const T*>(src), static_cast<T*>(dst), N, H, W, C, OH, OW, k, stride, pad);
+        static_cast<const T*>(src), static_cast<T*>(dst), N, H, W, C, OH, OW, k, stride, pad, in_l,
+        out_l);
     return cudaGetLastError();
   });
 }
 
-cudaError_t launch_avgpool_nhwc(const void* src, void* dst, DType dt, int N, int HW, int C,
-                                cudaStream_t stream) {
+cudaError_t launch_avgpool_nhwc(const void* src, void* dst, DType dt, int N, int H, int W, int C,
+                                Layout in_l, cudaStream_t stream) {
+  if (in_l.pitch == 0) in_l = dense_layout(H, W);
   return by_dtype(dt, [&](auto tag) {
     using T = decltype(tag);
     constexpr int V = 16 / sizeof(T);
     if (C % V != 0) return cudaErrorInvalidValue;
     const long long total = (long long)N * (C / V);
     avgpool_nhwc_kernel<T><<<grid_for(total, 128), 128, 0, stream>>>(
-        static_cast<const T*>(src), static_cast<T*>(dst), N, HW, C);
+        static_cast<const T*>(src), static_cast<T*>(dst), N, H, W, C, in_l);
     return cudaGetLastError();
   });
+}
+
+cudaError_t launch_relayout(const void* src, Layout src_l, void* dst, Layout dst_l, DType dt, int N,
+                            int H, int W, int C, cudaStream_t stream) {
+  const int cv = (int)(C * dtype_size(dt) / 16);
+  if ((size_t)cv * 16 != C * dtype_size(dt)) return cudaErrorInvalidValue;
+  if (src_l.pitch == 0) src_l = dense_layout(H, W);
+  if (dst_l.pitch == 0) dst_l = dense_layout(H, W);
+  const long long total = layout_slots(dst_l, N) * cv;
+  relayout_kernel<<<grid_for(total, 256), 256, 0, stream>>>(
+      static_cast<const uint4*>(src), src_l, static_cast<uint4*>(dst), dst_l, N, H, W, cv);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean,

@@ -95,6 +95,66 @@ def test_conv_epilogue(case, dtype):
     assert G.rel_l2(y, ref) <= tol
 
 
+SV_CASES = [
+    # n, c, h, w, k, (bn, mt, resident) or None for the built-in choice
+    (1, 64, 8, 8, 64, (64, 1, 1)),
+    (2, 64, 56, 56, 64, (64, 2, 1)),
+    (2, 64, 56, 56, 64, None),
+    (2, 128, 28, 28, 128, (64, 1, 1)),
+    (2, 128, 28, 28, 128, (128, 2, 0)),
+    (3, 256, 14, 14, 256, (128, 4, 0)),
+    (3, 256, 14, 14, 256, (256, 2, 0)),
+    (3, 256, 14, 14, 256, (64, 1, 0)),
+    (5, 512, 7, 7, 512, None),
+    (2, 64, 17, 23, 128, None),      # ragged map, Kout != C
+    (1, 192, 5, 3, 64, None),
+]
+
+
+@pytest.mark.parametrize("case", SV_CASES)
+@pytest.mark.parametrize("dtype,res", [(F16, True), (F16, False), (BF16, True)])
+def test_conv3x3_shifted_view(case, dtype, res):
+    """3x3 stride-1 pad-1 kernel whose taps are shifted views of one halo tile (algo 2), every
+    tile configuration, against the fp64-accumulated oracle on the same rounded operands."""
+    n, c, h, w, k, cfg = case
+    g = _rng(n + c + h + w + k)
+    x = g.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = (g.standard_normal((k, c, 3, 3)) * np.sqrt(2.0 / (9 * c))).astype(np.float32)
+    scale = g.uniform(0.5, 1.5, k).astype(np.float32)
+    shift = (g.standard_normal(k) * 0.1).astype(np.float32)
+    rs = g.standard_normal((n, k, h, w)).astype(np.float32) if res else None
+    conv = G.Conv(wt, 1, 1, dtype, algo=2)
+    try:
+        if cfg:
+            check(lib().nncv_b200_conv_set_tile(conv.h, *cfg))
+        y, xr = conv.run(x, scale, shift, rs, True)
+    finally:
+        conv.close()
+    tdt = G.TORCH_DT[dtype]
+    wr = torch.from_numpy(wt).to(tdt).float().numpy()
+    ref = ob.conv2d(xr, wr, 1, 1, acc64=True) * scale[None, :, None, None] + shift[None, :, None, None]
+    if res:
+        ref = ref + torch.from_numpy(rs).to(tdt).float().numpy()
+    ref = np.where(ref > 0, ref, 0)
+    assert np.isfinite(y).all()
+    assert G.rel_l2(y, ref) <= (TOL_16 if dtype == F16 else 8e-3)
+
+
+def test_conv3x3_shifted_view_matches_gather_kernel():
+    """The two tcgen05 kernels agree on the same layer up to the order of the fp32 sums."""
+    g = _rng(77)
+    x = g.standard_normal((4, 128, 28, 28)).astype(np.float32)
+    wt = (g.standard_normal((128, 128, 3, 3)) * np.sqrt(2.0 / (9 * 128))).astype(np.float32)
+    a, b = G.Conv(wt, 1, 1, F16, algo=0), G.Conv(wt, 1, 1, F16, algo=2)
+    try:
+        ya, _ = a.run(x)
+        yb, _ = b.run(x)
+    finally:
+        a.close()
+        b.close()
+    assert G.rel_l2(ya, yb) <= 5e-4
+
+
 @pytest.mark.parametrize("dtype", [F16, F32])
 def test_conv_kat0_split_params(dtype, golden_dir):
     """tests/SplitParams/data.mlir of the reference: all-ones input -> every output is 15."""
