@@ -15,7 +15,7 @@
 // for every slot; slots that are pads are computed too (4-23 % extra MMA work, depending on W)
 // and stored as zeros, which keeps the output in the same layout with its pads clean.
 //
-// Kernel (persistent, 6 warps):
+// Kernel (persistent, 10 warps):
 //   warp 0  one thread: TMA loads.  Per (tile, 64-channel block) ONE tiled copy brings rows
 //           [q0-P-1, q0+MT*128+P+1) x 64 channels into shared memory (128-byte swizzle; rows
 //           before slot 0 / past the end are zero-filled by TMA).  Weights are pre-packed
@@ -25,9 +25,9 @@
 //           (r*P+s)*128 bytes into the halo tile: the 128-byte swizzle is a function of the
 //           absolute shared-memory address, so a view shifted by whole rows reads consistently.
 //           MT accumulators of 128 x BN fp32 live in TMEM, double-buffered when they fit.
-//   warps 2-5  epilogue: tcgen05.ld, scale/shift (+ residual) (+ ReLU), zero the pad slots,
-//           convert, write a swizzled 128 x 64 slab in shared memory, TMA store.  The residual
-//           slab is fetched by TMA into the same staging buffer one slab ahead.
+//   warps 2-9  epilogue (two warps per TMEM lane quadrant, 32 columns each): tcgen05.ld, scale/shift (+ residual) (+ ReLU), zero the pad slots,
+//           convert, write a swizzled 128 x 64 slab in shared memory, TMA store.  Each thread
+//           fetches the residual of its own row one slab ahead, straight into registers.
 // Every wait is bounded and abortable; a timed-out wait sets the device status word.
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -44,16 +44,35 @@ namespace nncv_b200 {
 
 namespace {
 
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kEpiWarps = 8;               // two warps per TMEM lane quadrant, 32 columns each
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;  // warp 0 TMA, warp 1 MMA, warps 2.. epilogue
 constexpr int kSlabBytes = 128 * 128;  // 128 rows x 64 fp16
+constexpr int kResPrefetch = 5;  // slabs between the L2 prefetch of a residual row and its use
 constexpr int kMaxInStages = 4;
 constexpr int kMaxWStages = 8;
 
+// Optional clock64() trace of CTA 0 (built only with -DNNCV_B200_TRACE; a tuning aid).
+#ifdef NNCV_B200_TRACE
+unsigned long long* g_c3_trace = nullptr;  // device buffer [3 roles][32 items][8 stamps]
+#define C3_TRACE(role, item, k)                                                          \
+  do {                                                                                   \
+    if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && (item) < 32)                     \
+      p.trace[((role) * 32 + (item)) * 8 + (k)] = (unsigned long long)clock64();          \
+  } while (0)
+#else
+#define C3_TRACE(role, item, k) \
+  do {                          \
+  } while (0)
+#endif
+
 struct C3Params {
+  unsigned long long* trace;
   const uint8_t* wpack;
   const float* scale;
   const float* shift;
+  const uint16_t* residual;  // shared-pad [T, Kout] or null
+  int Kout;
   int* error_flag;
   int T;          // total slots
   int P;          // row pitch in slots (W + 1)
@@ -70,8 +89,8 @@ struct C3Params {
 
 template <int BN, int MT, bool RESIDENT>
 __global__ void __launch_bounds__(kThreads, 1)
-conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_res,
-               const __grid_constant__ CUtensorMap tm_out, const C3Params p) {
+conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_out,
+               const C3Params p) {
   constexpr int AB = (2 * MT * BN <= 512) ? 2 : 1;  // accumulator buffers in TMEM
   constexpr int ACC_COLS = AB * MT * BN;
   constexpr int WTILE = BN * 128;
@@ -91,8 +110,7 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
   const uint32_t in_full = bars, in_empty = bars + 8 * kMaxInStages;
   const uint32_t w_full = in_empty + 8 * kMaxInStages, w_empty = w_full + 8 * kMaxWStages;
   const uint32_t acc_full = w_empty + 8 * kMaxWStages, acc_empty = acc_full + 16;
-  const uint32_t res_full = acc_empty + 16;
-  const uint32_t tmem_slot = res_full + 16;
+  const uint32_t tmem_slot = acc_empty + 16;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -110,12 +128,10 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(acc_full + 8 * i, 1);
       ptx::mbar_init(acc_empty + 8 * i, kEpiThreads);
-      ptx::mbar_init(res_full + 8 * i, 1);
     }
     ptx::mbar_fence_init();
     ptx::prefetch_tensormap(&tm_in);
     ptx::prefetch_tensormap(&tm_out);
-    if (p.has_res) ptx::prefetch_tensormap(&tm_res);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, ACC_COLS);
@@ -161,7 +177,9 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         for (int cb = 0; cb < p.CB && okw; ++cb) {
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
           const uint32_t par = ((in_cnt / (uint32_t)p.in_stages) & 1u) ^ 1u;
+          C3_TRACE(0, i, 0);
           if (!ptx::mbar_wait_abortable(in_empty + 8 * st, par, abort_flag)) { okw = false; break; }
+          C3_TRACE(0, i, 1);
           ptx::mbar_arrive_expect_tx(in_full + 8 * st, (uint32_t)in_stage_bytes);
           for (int b = 0; b < p.in_boxes; ++b)
             ptx::tma_load_2d(sIn + st * in_stage_bytes + (uint32_t)b * p.box_rows * 128, &tm_in, cb * 64,
@@ -194,12 +212,15 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         int m_item, n_tile;
         if (!item_of(i, m_item, n_tile)) break;
         const uint32_t ab = acc_cnt % AB;
+        C3_TRACE(1, i, 0);
         if (!ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt / AB) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
+        C3_TRACE(1, i, 1);
         ptx::tc_fence_after();
         const uint32_t d_base = tmem_base + ab * (MT * BN);
         for (int cb = 0; cb < p.CB && okw; ++cb) {
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
           if (!ptx::mbar_wait_abortable(in_full + 8 * st, (in_cnt / (uint32_t)p.in_stages) & 1u, abort_flag)) { okw = false; break; }
+          if (cb == 0) C3_TRACE(1, i, 2);
           ptx::tc_fence_after();
           const uint32_t a_stage = sIn + st * in_stage_bytes;
           for (int tap = 0; tap < 9; ++tap) {
@@ -214,14 +235,18 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
               w_addr = sW + ws * WTILE;
             }
             const int r = tap / 3, s = tap - 3 * r;
-            const uint32_t a_tap = a_stage + (uint32_t)(r * p.P + s) * 128u;
+            // descriptors differ only in the address bits of the low word: one add per MMA
+            const uint32_t a_lo = ptx::smem_desc_k128_lo(a_stage + (uint32_t)(r * p.P + s) * 128u);
+            const uint32_t b_lo = ptx::smem_desc_k128_lo(w_addr);
+            const uint32_t first = (cb | tap) != 0 ? 1u : 0u;
 #pragma unroll
             for (int t = 0; t < MT; ++t) {
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4) {
-                ptx::umma_f16(d_base + t * BN, ptx::smem_desc_k128(a_tap + t * (128 * 128) + k4 * 32),
-                              ptx::smem_desc_k128(w_addr + k4 * 32), idesc,
-                              (cb | tap | k4) != 0 ? 1u : 0u);
+                ptx::umma_f16(d_base + t * BN,
+                              ptx::desc_from_halves(a_lo + (uint32_t)(t * (128 * 128) + k4 * 32) / 16u, ptx::kSmemDescK128Hi),
+                              ptx::desc_from_halves(b_lo + (uint32_t)(k4 * 32) / 16u, ptx::kSmemDescK128Hi), idesc,
+                              k4 == 0 ? first : 1u);
               }
             }
             if (!RESIDENT) {
@@ -232,6 +257,7 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
           ptx::tc_commit(in_empty + 8 * st);
           ++in_cnt;
         }
+        C3_TRACE(1, i, 3);
         ptx::tc_commit(acc_full + 8 * ab);
         ++acc_cnt;
       }
@@ -240,6 +266,7 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
   } else {
     // ------------------------------------------------------------------ epilogue --------
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;     // which 32 of the slab's 64 columns this warp handles
     const int row = quad * 32 + lane;     // row of the 128-row sub-tile
     const bool elected = threadIdx.x == 64;
     const uint32_t sw = (uint32_t)(row & 7);
@@ -253,11 +280,23 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       ncol = n_tile * BN + sl * 64;
       return true;
     };
-    if (elected && p.has_res) {
+    // residual of the first slab (later slabs are fetched one slab ahead inside the loop)
+    uint32_t res_cur[2][8];
+    bool have_cur = false;
+    if (p.has_res) {
       int q_tile, ncol;
-      if (slab_of(0, q_tile, ncol)) {
-        ptx::mbar_arrive_expect_tx(res_full, kSlabBytes);
-        ptx::tma_load_2d(sStage, &tm_res, ncol, q_tile, res_full);
+      if (slab_of(0, q_tile, ncol) && q_tile + row < p.T) {
+        have_cur = true;
+        const uint16_t* rp = p.residual + ((size_t)(q_tile + row) * p.Kout + ncol + half * 32);
+        ptx::ldg_256(rp, res_cur[0]);
+        ptx::ldg_256(rp + 16, res_cur[1]);
+      }
+    }
+    if (p.has_res) {
+      for (int j = 1; j < kResPrefetch; ++j) {
+        int qf, nf;
+        if (slab_of(j, qf, nf) && qf + row < p.T)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + ((size_t)(qf + row) * p.Kout + nf + half * 32)));
       }
     }
     uint32_t acc_cnt = 0;
@@ -269,94 +308,120 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       const int t = rem / SLABS, sl = rem - t * SLABS;
       const uint32_t sb = (uint32_t)j & 1u;
       const uint32_t ab = acc_cnt % AB;
-      bool got = true;
-      if (rem == 0) got = ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt / AB) & 1u, abort_flag);
-      if (got && p.has_res)
-        got = ptx::mbar_wait_abortable(res_full + 8 * sb, ((uint32_t)j >> 1) & 1u, abort_flag);
-      // all 128 epilogue threads take the same exit: nobody is left alone at a named barrier
-      if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; break; }
-      ptx::tc_fence_after();
+      if (elected) C3_TRACE(2, j, 0);
+      // Everything that does not depend on the accumulator is issued before the waits: pad test,
+      // per-channel scale/shift, and (below) the residual of the NEXT slab.
       const int q = q_tile + row;
       bool valid = q < p.T;
       if (valid) {
         const int yrow = q / p.P;
         valid = (q - yrow * p.P != 0) && (yrow % p.Himg != 0);
       }
+      const int n0 = ncol + half * 32;
+      float4 sc[8], sh[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sc[i] = p.scale ? __ldg(reinterpret_cast<const float4*>(p.scale + n0) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+        sh[i] = p.shift ? __ldg(reinterpret_cast<const float4*>(p.shift + n0) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      bool got = true;
+      if (rem == 0) got = ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt / AB) & 1u, abort_flag);
+      if (elected) C3_TRACE(2, j, 1);
+      // all epilogue threads take the same exit: nobody is left alone at a named barrier
+      if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; break; }
+      if (elected) C3_TRACE(2, j, 2);
+      ptx::tc_fence_after();
       const uint32_t srow = sStage + sb * kSlabBytes + (uint32_t)row * 128u;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + ab * (MT * BN) + t * BN + sl * 64;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t acc[32];
-        __syncwarp();
-        ptx::tmem_ld_32x32(t_addr + half * 32, acc);
-        ptx::tmem_ld_wait();
-        const int n0 = ncol + half * 32;
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          float4 sc = make_float4(1.f, 1.f, 1.f, 1.f), sh = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (p.scale) sc = __ldg(reinterpret_cast<const float4*>(p.scale + n0 + i));
-          if (p.shift) sh = __ldg(reinterpret_cast<const float4*>(p.shift + n0 + i));
-          v[i] = fmaf(__uint_as_float(acc[i]), sc.x, sh.x);
-          v[i + 1] = fmaf(__uint_as_float(acc[i + 1]), sc.y, sh.y);
-          v[i + 2] = fmaf(__uint_as_float(acc[i + 2]), sc.z, sh.z);
-          v[i + 3] = fmaf(__uint_as_float(acc[i + 3]), sc.w, sh.w);
-        }
-#pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-          const uint32_t chunk = (uint32_t)(half * 4 + c4);
-          const uint32_t addr = srow + ((chunk ^ sw) << 4);
-          if (p.has_res) {
-            uint4 rv;
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(rv.x), "=r"(rv.y), "=r"(rv.z), "=r"(rv.w) : "r"(addr));
-            const uint32_t w4[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              float2 f;
-              if (p.bf16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[h]));
-              else f = __half22float2(*reinterpret_cast<const __half2*>(&w4[h]));
-              v[c4 * 8 + h * 2] += f.x;
-              v[c4 * 8 + h * 2 + 1] += f.y;
-            }
+      uint32_t acc[32];
+      __syncwarp();
+      ptx::tmem_ld_32x32(t_addr + half * 32, acc);
+      // residual of the next slab: in flight while this slab is converted and stored
+      uint32_t res_next[2][8];
+      bool have_next = false;
+      if (p.has_res) {
+        int qn, nn;
+        if (slab_of(j + 1, qn, nn)) {
+          const int qr = qn + row;
+          if (qr < p.T) {
+            have_next = true;
+            const uint16_t* rp = p.residual + ((size_t)qr * p.Kout + nn + half * 32);
+            ptx::ldg_256(rp, res_next[0]);
+            ptx::ldg_256(rp + 16, res_next[1]);
           }
-          uint32_t o[4];
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            float a = v[c4 * 8 + h * 2], b = v[c4 * 8 + h * 2 + 1];
-            if (p.relu) {
-              a = !(a <= 0.0f) ? a : 0.0f;
-              b = !(b <= 0.0f) ? b : 0.0f;
-            }
-            if (!valid) a = b = 0.0f;
-            if (p.bf16) {
-              __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
-              o[h] = *reinterpret_cast<uint32_t*>(&x);
-            } else {
-              __half2 x = __floats2half2_rn(a, b);
-              o[h] = *reinterpret_cast<uint32_t*>(&x);
-            }
-          }
-          asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
         }
       }
-      if (rem == SPI - 1) {  // last read of this accumulator buffer
+      __syncwarp();
+      if (p.has_res) {  // and pull the residual rows of a later slab from HBM into L2
+        int qf, nf;
+        if (slab_of(j + kResPrefetch, qf, nf) && qf + row < p.T)
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + ((size_t)(qf + row) * p.Kout + nf + half * 32)));
+      }
+      ptx::tmem_ld_wait();
+      if (rem == SPI - 1) {  // the accumulator is in registers: hand the TMEM buffer back
         ptx::tc_fence_before();
         ptx::mbar_arrive(acc_empty + 8 * ab);
         ++acc_cnt;
       }
+      if (elected) C3_TRACE(2, j, 3);
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[4 * i] = fmaf(__uint_as_float(acc[4 * i]), sc[i].x, sh[i].x);
+        v[4 * i + 1] = fmaf(__uint_as_float(acc[4 * i + 1]), sc[i].y, sh[i].y);
+        v[4 * i + 2] = fmaf(__uint_as_float(acc[4 * i + 2]), sc[i].z, sh[i].z);
+        v[4 * i + 3] = fmaf(__uint_as_float(acc[4 * i + 3]), sc[i].w, sh[i].w);
+      }
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const uint32_t chunk = (uint32_t)(half * 4 + c4);
+        const uint32_t addr = srow + ((chunk ^ sw) << 4);
+        if (p.has_res && have_cur) {
+          const uint32_t w4[4] = {res_cur[c4 >> 1][(c4 & 1) * 4], res_cur[c4 >> 1][(c4 & 1) * 4 + 1],
+                                  res_cur[c4 >> 1][(c4 & 1) * 4 + 2], res_cur[c4 >> 1][(c4 & 1) * 4 + 3]};
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            float2 f;
+            if (p.bf16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[h]));
+            else f = __half22float2(*reinterpret_cast<const __half2*>(&w4[h]));
+            v[c4 * 8 + h * 2] += f.x;
+            v[c4 * 8 + h * 2 + 1] += f.y;
+          }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const float a = v[c4 * 8 + h * 2], b = v[c4 * 8 + h * 2 + 1];
+          uint32_t packed;
+          if (p.bf16) {
+            __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
+            if (p.relu) x = __hmax2_nan(x, __floats2bfloat162_rn(0.f, 0.f));
+            packed = *reinterpret_cast<uint32_t*>(&x);
+          } else {
+            __half2 x = __floats2half2_rn(a, b);
+            if (p.relu) x = __hmax2_nan(x, __floats2half2_rn(0.f, 0.f));  // NaN passes, like cmpf ugt
+            packed = *reinterpret_cast<uint32_t*>(&x);
+          }
+          o[h] = valid ? packed : 0u;
+        }
+        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+      }
+      if (p.has_res) {
+        have_cur = have_next;
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) res_cur[c4 >> 3][c4 & 7] = res_next[c4 >> 3][c4 & 7];
+      }
+      if (elected) C3_TRACE(2, j, 4);
       ptx::fence_proxy_async_smem();
       ptx::named_bar_sync(1, kEpiThreads);
+      if (elected) C3_TRACE(2, j, 5);
       if (elected) {
         ptx::tma_store_2d(&tm_out, ncol, q_tile, sStage + sb * kSlabBytes);
         ptx::bulk_commit();
         ptx::bulk_wait_read<1>();  // the store that last read the other buffer has finished
-        int qn, nn;
-        if (p.has_res && slab_of(j + 1, qn, nn)) {
-          ptx::mbar_arrive_expect_tx(res_full + 8 * (sb ^ 1u), kSlabBytes);
-          ptx::tma_load_2d(sStage + (sb ^ 1u) * kSlabBytes, &tm_res, nn, qn, res_full + 8 * (sb ^ 1u));
-        }
       }
-      if (!p.has_res) ptx::named_bar_sync(2, kEpiThreads);  // the other buffer is free for everyone
+      if (elected) C3_TRACE(2, j, 6);
+      ptx::named_bar_sync(2, kEpiThreads);  // the other staging buffer is free for everyone
     }
     if (elected) ptx::bulk_wait<0>();
     if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitEpilogue);
@@ -404,8 +469,14 @@ constexpr size_t kSmemLimit = 227 * 1024;
 template <int BN, int MT, bool RESIDENT>
 cudaError_t launch_cfg(const Conv3x3Args& a, cudaStream_t stream) {
   C3Params p;
+#ifdef NNCV_B200_TRACE
+  p.trace = g_c3_trace;
+#else
+  p.trace = nullptr;
+#endif
   p.wpack = static_cast<const uint8_t*>(a.wpack);
   p.scale = a.scale; p.shift = a.shift; p.error_flag = a.error_flag;
+  p.residual = static_cast<const uint16_t*>(a.residual); p.Kout = a.Kout;
   p.P = a.W + 1; p.Himg = a.H + 1;
   const long long T = (long long)a.N * p.Himg * p.P;
   if (T <= 0 || T > 0x7fffff00LL) return cudaErrorInvalidValue;
@@ -446,10 +517,9 @@ cudaError_t launch_cfg(const Conv3x3Args& a, cudaStream_t stream) {
   const size_t smem = fixed + wbytes + (size_t)p.in_stages * in_stage;
   p.relu = a.relu; p.has_res = a.residual != nullptr; p.bf16 = a.ab == kBF16;
 
-  CUtensorMap tm_in, tm_res, tm_out;
+  CUtensorMap tm_in, tm_out;
   if (!make_map(&tm_in, a.in, T, a.C, p.box_rows, p.bf16) ||
-      !make_map(&tm_out, a.out, T, a.Kout, 128, p.bf16) ||
-      !make_map(&tm_res, a.residual ? a.residual : a.out, T, a.Kout, 128, p.bf16))
+      !make_map(&tm_out, a.out, T, a.Kout, 128, p.bf16))
     return cudaErrorInvalidValue;
 
   auto kern = conv3x3_kernel<BN, MT, RESIDENT>;
@@ -466,31 +536,36 @@ cudaError_t launch_cfg(const Conv3x3Args& a, cudaStream_t stream) {
     const int items = p.m_items * p.n_tiles;
     grid = dim3(items < sms ? items : sms, 1);
   }
-  kern<<<grid, kThreads, smem, stream>>>(tm_in, tm_res, tm_out, p);
+  kern<<<grid, kThreads, smem, stream>>>(tm_in, tm_out, p);
   return cudaGetLastError();
 }
 
 }  // namespace
 
+#ifdef NNCV_B200_TRACE
+extern "C" void nncv_b200_debug_set_trace(unsigned long long* dev_buf) { g_c3_trace = dev_buf; }
+#endif
+
 bool conv3x3_supported(int C, int Kout, int R, int S, int stride, int pad) {
   return R == 3 && S == 3 && stride == 1 && pad == 1 && C % 64 == 0 && Kout % 64 == 0 && C >= 64;
 }
 
-// Tile configuration.  Small channel counts keep all weights of a 64-wide Kout tile resident in
-// shared memory; large ones stream weights and amortise each weight tile over MT sub-tiles.
-Conv3x3Config conv3x3_pick(int N, int H, int W, int C, int Kout) {
+// Tile configuration, from timing every variant on the four ResNet-18 layer shapes at batch 256.
+// With 64 input channels all nine weight tiles of a 64-wide Kout tile stay resident in shared
+// memory; wider layers stream weights and favour the widest N tile (fewer passes over the input,
+// and tcgen05.mma runs closer to its peak rate as N grows).
+Conv3x3Config conv3x3_pick(int N, int H, int W, int C, int Kout, int has_res) {
   Conv3x3Config c;
-  const size_t resident64 = (size_t)9 * (C / 64) * 64 * 128;
-  if (resident64 <= 150 * 1024) {
-    c.bn = 64;
-    c.resident = 1;
-    c.mt = C <= 64 ? 2 : 1;
-  } else {
-    c.resident = 0;
-    c.bn = Kout % 128 == 0 ? 128 : 64;
-    c.mt = 2;
-  }
   (void)N; (void)H; (void)W;
+  if (C <= 64) {
+    c.bn = 64; c.resident = 1; c.mt = has_res ? 1 : 2;
+  } else if (C <= 128 || Kout % 256 != 0) {
+    c.resident = 0; c.bn = Kout % 128 == 0 ? 128 : 64; c.mt = 2;
+  } else if (C <= 256) {
+    c.resident = 0; c.bn = 256; c.mt = 1;
+  } else {
+    c.resident = 0; c.bn = 256; c.mt = 2;
+  }
   return c;
 }
 

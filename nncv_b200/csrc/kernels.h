@@ -82,7 +82,7 @@ struct Conv3x3Args {
   int* error_flag = nullptr;
 };
 bool conv3x3_supported(int C, int Kout, int R, int S, int stride, int pad);
-Conv3x3Config conv3x3_pick(int N, int H, int W, int C, int Kout);
+Conv3x3Config conv3x3_pick(int N, int H, int W, int C, int Kout, int has_res);
 cudaError_t launch_conv3x3(const Conv3x3Args& a, cudaStream_t stream);
 
 // ---- fp32 SIMT implicit-GEMM convolution (the fp32-accurate path) ------------------------

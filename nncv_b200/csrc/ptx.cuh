@@ -87,6 +87,13 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// 32-byte read-only global load (address 32-byte aligned).
+__device__ __forceinline__ void ldg_256(const void* p, uint32_t (&r)[8]) {
+  asm volatile("ld.global.nc.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "l"(p));
+}
+
 // Untiled bulk copy global->shared; both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
                                          uint32_t bar) {
@@ -234,6 +241,18 @@ __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr) {
   d |= (uint64_t)(1024 >> 4) << 32;
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// The same descriptor split in two 32-bit halves, so that an issue loop only adds byte offsets
+// (>> 4) to the low word: hi is constant, lo = smem_desc_k128_lo(address).
+__device__ __forceinline__ uint32_t smem_desc_k128_lo(uint32_t smem_addr) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+}
+constexpr uint32_t kSmemDescK128Hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint64_t desc_from_halves(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
   return d;
 }
 

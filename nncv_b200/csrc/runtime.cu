@@ -263,7 +263,7 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
     // shifted-view 3x3: shared-pad layouts on both sides
     if (in_l.off != 1 || out_l.off != 1 || out_dt != c->dtype || ldo != c->Kout)
       return fail(NNCV_B200_EINVAL, "conv3x3: needs shared-pad NHWC input and output");
-    const Conv3x3Config cfg = c->cfg3.bn ? c->cfg3 : conv3x3_pick(N, H, W, c->Cpad, c->Kout);
+    const Conv3x3Config cfg = c->cfg3.bn ? c->cfg3 : conv3x3_pick(N, H, W, c->Cpad, c->Kout, residual != nullptr);
     const void* wpack = nullptr;
     int rc = conv_prepare(c, cfg.bn, st, &wpack);
     if (rc) return rc;
