@@ -118,7 +118,8 @@ long long nncv_b200_launch_count(void);
 /* Per-launch timing with CUDA events on the launching stream (off by default).  The reference
  * only has wall-clock timers around the whole forward (examples/Res18/main.cpp:95-99). */
 typedef struct {
-  int kind;      /* 0 tcgen05 implicit GEMM, 1 fp32 CUDA-core conv, 2 Winograd, 3 memory-bound helper */
+  int kind;      /* 0 tcgen05 implicit GEMM (gathered A), 1 fp32 CUDA-core conv, 2 tcgen05 3x3 shifted-view
+                    conv, 3 memory-bound helper, 4 fused stem conv + max-pool */
   int M, N, K;   /* GEMM view of the launch (helpers: elements, channels, 0) */
   int bn;        /* N tile (kind 0); helper id (kind 3) */
   double flops;  /* algorithmic: 2*M*N*K with K = C*R*S (direct-convolution count) */
@@ -169,6 +170,14 @@ int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int 
  * weights resident in shared memory or streamed); bn = 0 restores the built-in choice.  A tuning
  * and test hook with no counterpart in the reference. */
 int nncv_b200_conv_set_tile(nncv_b200_conv* c, int bn, int mt, int resident);
+
+/* The ResNet stem in one kernel (tests/Nets/Res18.mlir:118-151): tensor.pad 3 + 7x7 stride-2
+ * conv 3 -> 64 + per-channel scale/shift (folded batch-norm) + ReLU + tensor.pad(-inf) 1 +
+ * 3x3 stride-2 max-pool.  in: NCHW [N,3,H,W] of in_dtype; weights: device [64,3,7,7] of w_dtype;
+ * out: dense NHWC [N,PH,PW,64] of dtype (F16/BF16).  Uses the library's scratch buffer. */
+int nncv_b200_stem_pool(const void* in_nchw, int in_dtype, const void* weights, int w_dtype,
+                        const float* scale, const float* shift, void* out_nhwc, int dtype, int N, int H,
+                        int W, void* stream);
 
 /* tensor.pad(-inf) + linalg.pooling_nchw_max (Res18.mlir:144-151), NHWC. */
 int nncv_b200_maxpool_nhwc(const void* in, void* out, int dtype, int N, int H, int W, int C,

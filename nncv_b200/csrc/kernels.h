@@ -85,6 +85,27 @@ bool conv3x3_supported(int C, int Kout, int R, int S, int stride, int pad);
 Conv3x3Config conv3x3_pick(int N, int H, int W, int C, int Kout, int has_res);
 cudaError_t launch_conv3x3(const Conv3x3Args& a, cudaStream_t stream);
 
+// ---- ResNet stem: 7x7 s2 p3 conv (3 -> 64) + scale/shift + ReLU + 3x3 s2 p1 max-pool, fused ---
+struct StemArgs {
+  const void* in_rows = nullptr;   // rows written by launch_nchw_to_stem_rows
+  const void* wpack = nullptr;     // written by launch_pack_stem_weights
+  const float* scale = nullptr;
+  const float* shift = nullptr;
+  void* out = nullptr;             // pooled [N, PH, PW, 64]
+  Layout out_l{0, 0, 0};
+  int N = 0, H = 0, W = 0;
+  DType ab = kF16;
+  int sm_count = 0;
+  int* error_flag = nullptr;
+};
+int stem_row_pixels(int W);
+size_t stem_rows_bytes(int N, int H, int W);
+size_t stem_wpack_bytes();
+cudaError_t launch_nchw_to_stem_rows(const void* src, DType src_dt, void* dst, DType dst_dt, int N, int H,
+                                     int W, cudaStream_t stream);
+cudaError_t launch_pack_stem_weights(const void* w, DType w_dt, void* dst, DType dst_dt, cudaStream_t stream);
+cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream);
+
 // ---- fp32 SIMT implicit-GEMM convolution (the fp32-accurate path) ------------------------
 struct SimtConvArgs {
   const float* in = nullptr;        // [N,H,W,C] fp32, C % 4 == 0

@@ -372,6 +372,8 @@ struct Model {
   // per-shape workspace
   int wsN = 0, wsH = 0, wsW = 0;
   DevBuf in_stage, in_nhwc, stem, pooled, logits32, logits_io;
+  DevBuf stem_rows, stem_w;  // fused stem (16-bit path): reformatted input rows, packed weights
+  bool fused_stem = false;
   // One buffer per activation tensor of the forward, handed out in call order.  Buffers are
   // zeroed when created and never shared between tensors, so the pad slots of shared-pad
   // tensors stay zero no matter which kernel writes the interior.
@@ -428,6 +430,12 @@ int model_build(int depth, const void* host_blob, size_t n_elements, size_t ele_
                           g.cout, fp, fp + g.cout, st));
     fp += 2 * g.cout;
   }
+  if (m->act_dt != kF32) {
+    rc = m->stem_w.reserve(stem_wpack_bytes());
+    if (rc) return rc;
+    LAUNCH(launch_pack_stem_weights(at(m->spec.groups[0].off_w), pdt, m->stem_w.p, m->act_dt, st));
+    m->fused_stem = true;
+  }
   // FC: weight [1000, fc_in] is already "[Kout][C]" (the forward's transpose generic,
   // Res18.mlir:617-620, is absorbed by reading it K-major); bias in fp32.
   m->fc = std::make_unique<nncv_b200_conv>();
@@ -457,8 +465,12 @@ int ensure_workspace(Model& m, int N, int H, int W) {
   m.act_next = 0;
   int rc = 0;
   if ((rc = m.in_stage.reserve((size_t)N * 3 * H * W * m.ele_width))) return rc;
-  if ((rc = m.in_nhwc.reserve((size_t)N * H * W * cpad0 * es))) return rc;
-  if ((rc = m.stem.reserve((size_t)N * h1 * w1 * 64 * es))) return rc;
+  if (m.fused_stem) {
+    if ((rc = m.stem_rows.reserve(stem_rows_bytes(N, H, W)))) return rc;
+  } else {
+    if ((rc = m.in_nhwc.reserve((size_t)N * H * W * cpad0 * es))) return rc;
+    if ((rc = m.stem.reserve((size_t)N * h1 * w1 * 64 * es))) return rc;
+  }
   if ((rc = m.pooled.reserve((size_t)N * m.spec.fc_in * es))) return rc;
   if ((rc = m.logits32.reserve((size_t)N * 1000 * sizeof(float)))) return rc;
   if ((rc = m.logits_io.reserve((size_t)N * 1000 * m.ele_width))) return rc;
@@ -494,11 +506,7 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
   const bool sp = adt != kF32;  // tensor-core path keeps block activations in shared-pad NHWC
   auto lay = [&](int h, int w) { return sp ? sp_layout(h, w) : dense_layout(h, w); };
   size_t gi = 0;
-  // NCHW -> NHWC (channels padded), io type -> activation type
   const double aes = (double)dtype_size(adt);
-  prof_begin(3, 0, (double)N * H * W * (3.0 * m.ele_width + m.convs[0]->Cpad * aes), N * H * W, 3, 0, 0, st);
-  LAUNCH(launch_nchw_to_nhwc(src_dev, m.io_dt, m.in_nhwc.p, adt, N, 3, H, W, m.convs[0]->Cpad, st));
-  prof_end(st);
   int h = H, w = W;
   auto out_hw = [](int x, const nncv_b200_conv& c) { return (x + 2 * c.pad - c.R) / c.stride + 1; };
   auto run = [&](size_t idx, const void* in, Layout il, void* out, Layout ol, int ih, int iw,
@@ -506,22 +514,46 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
     nncv_b200_conv& c = *m.convs[idx];
     return conv_run(&c, in, il, out, ol, N, ih, iw, m.scale[idx], m.shift[idx], res, relu, adt, c.Kout, st);
   };
-  // stem (Res18.mlir:118-143) and max-pool (:144-151)
-  {
-    const int oh = out_hw(h, *m.convs[gi]), ow = out_hw(w, *m.convs[gi]);
-    rc = run(gi, m.in_nhwc.p, dense_layout(h, w), m.stem.p, dense_layout(oh, ow), h, w, nullptr, 1);
-    if (rc) return rc;
-    h = oh; w = ow;
-    ++gi;
-  }
   void* x = nullptr;
-  {
-    const int oh = (h + 2 - 3) / 2 + 1, ow = (w + 2 - 3) / 2 + 1;
-    if ((rc = next_act(m, N, oh, ow, 64, lay(oh, ow), st, &x))) return rc;
-    prof_begin(3, 0, aes * 64.0 * N * ((double)h * w + (double)oh * ow), N * h * w, 64, 0, 1, st);
-    LAUNCH(launch_maxpool_nhwc(m.stem.p, x, adt, N, h, w, 64, 3, 2, 1, dense_layout(h, w), lay(oh, ow), st));
+  if (m.fused_stem) {
+    // stem conv + BN + ReLU + max-pool in one kernel (Res18.mlir:118-151)
+    const int oh = out_hw(h, *m.convs[0]), ow = out_hw(w, *m.convs[0]);
+    const int ph = (oh + 2 - 3) / 2 + 1, pw = (ow + 2 - 3) / 2 + 1;
+    prof_begin(3, 0, (double)N * H * (3.0 * W * m.ele_width + stem_row_pixels(W) * 8.0), N * H * W, 3, 0, 3, st);
+    LAUNCH(launch_nchw_to_stem_rows(src_dev, m.io_dt, m.stem_rows.p, adt, N, H, W, st));
     prof_end(st);
-    h = oh; w = ow;
+    if ((rc = next_act(m, N, ph, pw, 64, lay(ph, pw), st, &x))) return rc;
+    StemArgs a;
+    a.in_rows = m.stem_rows.p; a.wpack = m.stem_w.p; a.scale = m.scale[0]; a.shift = m.shift[0];
+    a.out = x; a.out_l = lay(ph, pw); a.N = N; a.H = H; a.W = W; a.ab = adt;
+    a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
+    prof_begin(4, 2.0 * N * oh * ow * 64.0 * 147.0,
+               (double)N * H * stem_row_pixels(W) * 8.0 + 2.0 * N * ph * pw * 64.0, N * oh * ow, 64, 147, 64, st);
+    LAUNCH(launch_stem_pool(a, st));
+    prof_end(st);
+    h = ph; w = pw;
+    gi = 1;
+  } else {
+    // NCHW -> NHWC (channels padded), io type -> activation type
+    prof_begin(3, 0, (double)N * H * W * (3.0 * m.ele_width + m.convs[0]->Cpad * aes), N * H * W, 3, 0, 0, st);
+    LAUNCH(launch_nchw_to_nhwc(src_dev, m.io_dt, m.in_nhwc.p, adt, N, 3, H, W, m.convs[0]->Cpad, st));
+    prof_end(st);
+    // stem (Res18.mlir:118-143) and max-pool (:144-151)
+    {
+      const int oh = out_hw(h, *m.convs[gi]), ow = out_hw(w, *m.convs[gi]);
+      rc = run(gi, m.in_nhwc.p, dense_layout(h, w), m.stem.p, dense_layout(oh, ow), h, w, nullptr, 1);
+      if (rc) return rc;
+      h = oh; w = ow;
+      ++gi;
+    }
+    {
+      const int oh = (h + 2 - 3) / 2 + 1, ow = (w + 2 - 3) / 2 + 1;
+      if ((rc = next_act(m, N, oh, ow, 64, lay(oh, ow), st, &x))) return rc;
+      prof_begin(3, 0, aes * 64.0 * N * ((double)h * w + (double)oh * ow), N * h * w, 64, 0, 1, st);
+      LAUNCH(launch_maxpool_nhwc(m.stem.p, x, adt, N, h, w, 64, 3, 2, 1, dense_layout(h, w), lay(oh, ow), st));
+      prof_end(st);
+      h = oh; w = ow;
+    }
   }
   const int nb18[4] = {2, 2, 2, 2}, nb50[4] = {3, 4, 6, 3};
   const int* nb = m.spec.depth == 18 ? nb18 : nb50;
@@ -985,6 +1017,27 @@ int nncv_b200_conv_set_tile(nncv_b200_conv* c, int bn, int mt, int resident) {
   std::lock_guard<std::mutex> lk(g_mutex);
   if (!c || c->algo != 2) return fail(NNCV_B200_EINVAL, "conv_set_tile: only for algo 2 plans");
   c->cfg3 = Conv3x3Config{bn, mt, resident};
+  return ok();
+}
+
+int nncv_b200_stem_pool(const void* in_nchw, int in_dtype, const void* weights, int w_dtype,
+                        const float* scale, const float* shift, void* out_nhwc, int dtype, int N, int H,
+                        int W, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!in_nchw || !weights || !out_nhwc || N <= 0 || H < 7 || W < 7 || (dtype != NNCV_B200_F16 && dtype != NNCV_B200_BF16))
+    return fail(NNCV_B200_EINVAL, "stem_pool: bad argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t rows = (stem_rows_bytes(N, H, W) + 255) & ~(size_t)255;
+  if ((rc = ensure_scratch(rows + stem_wpack_bytes()))) return rc;
+  char* sp = (char*)g_dev.scratch;
+  LAUNCH(launch_nchw_to_stem_rows(in_nchw, (DType)in_dtype, sp, (DType)dtype, N, H, W, st));
+  LAUNCH(launch_pack_stem_weights(weights, (DType)w_dtype, sp + rows, (DType)dtype, st));
+  StemArgs a;
+  a.in_rows = sp; a.wpack = sp + rows; a.scale = scale; a.shift = shift; a.out = out_nhwc;
+  a.N = N; a.H = H; a.W = W; a.ab = (DType)dtype; a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
+  LAUNCH(launch_stem_pool(a, st));
   return ok();
 }
 

@@ -1,0 +1,448 @@
+// ResNet stem for sm_100a: 7x7 stride-2 pad-3 convolution (3 -> 64 channels) + folded batch-norm
+// + ReLU + 3x3 stride-2 pad-1 max-pool in ONE kernel, on tcgen05 tensor cores.
+//
+// Reference semantics (nncv tree): tests/Nets/Res18.mlir:118-151 (tensor.pad 3, conv_2d_nchw_fchw
+// with strides 2, the batch-norm and ReLU generics, tensor.pad -inf 1, pooling_nchw_max 3x3
+// strides 2).  nncv tiles this conv with an extra {1,1} tile for strided ops
+// (src/nncv/compiler/Conversion/CodeGen/LlvmCpu/ModernTile.cpp:201-209).
+//
+// Input format: the NCHW image is first rewritten (nchw_to_stem_rows) as fp16 rows of
+// 4-channel pixels with 4 zero pixels on the left and >= 4 on the right:
+//     row(n, y) = [0 0 0 0 | p(0) ... p(W-1) | 0 0 0 0 ...],   p = (c0, c1, c2, 0),  8 bytes each.
+// With this layout the A operand of the implicit GEMM needs no im2col at all.  tcgen05.mma's
+// un-swizzled K-major operand layout addresses element (row i, 16-byte chunk j) at
+//     start + (i % 8) * 16 + (i / 8) * SBO + j * LBO .
+// Choosing SBO = 128 and LBO = 16 makes that  start + 16 * (i + j):  row i (output column x0+i)
+// reads the 16-byte chunks i, i+1, i+2, i+3 of the input row, i.e. the pixel pairs
+// 2x-4 .. 2x+3 -- exactly the 7 taps (plus one zero-weight tap in front) of a stride-2 window.
+// The rows of the operand overlap in memory; the tensor core only does address arithmetic.
+// One filter row is therefore K = 32 (two MMAs of K = 16), a conv output row of up to 128
+// pixels is 14 MMAs of 128 x 64 x 16, and every input row is brought into shared memory once
+// (bulk async copy into a ring) and reused by the seven filter rows of four output rows.
+//
+// Roles (10 warps, persistent over (image, band of pooled rows) items):
+//   warp 0   bulk-copies input rows into the ring; weights (28 KB) are resident.
+//   warp 1   issues the MMAs of one conv row into one of four TMEM accumulators.
+//   warps 2-9  read the accumulator, apply scale/shift, write the fp16 conv row into a 4-row
+//            ring in shared memory; after every second row they max-pool (3x3 window, -inf
+//            padding, so out-of-range taps are skipped), apply ReLU (it commutes with max)
+//            and store the pooled row, 16 bytes per thread, fully coalesced.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace nncv_b200 {
+
+namespace {
+
+constexpr int kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;
+constexpr int kRingSlots = 16;      // input rows resident in shared memory
+constexpr int kAccBufs = 4;         // TMEM accumulators of 64 columns
+constexpr int kConvRing = 4;        // fp16 conv rows kept for pooling
+constexpr int kWBytes = 7 * 4096;   // packed weights: 7 filter rows x [64 x 32] fp16
+
+struct StemParams {
+  const uint8_t* in_rows;   // [N][H][RW] pixels of 8 bytes
+  const uint8_t* wpack;     // kWBytes
+  const float* scale;
+  const float* shift;
+  uint16_t* out;            // pooled [N, PH, PW, 64] in layout ol
+  int* error_flag;
+  Layout ol;
+  int N, H, W, OH, OW, PH, PW;
+  int row_bytes;            // RW * 8
+  int slot_bytes;           // ring slot size (>= row_bytes, covers the junk rows of the last tile)
+  int x_tiles;              // ceil(OW / 128)
+  int bands, band_rows;     // pooled rows per item
+  int bf16;
+};
+
+// Un-swizzled K-major descriptor: LBO = byte step between 16-byte chunks along K, SBO = byte
+// step between 8-row groups along M/N.
+__device__ __forceinline__ uint64_t desc_noswz(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  const uint32_t lo = ((addr & 0x3FFFFu) >> 4) | ((lbo >> 4) << 16);
+  const uint32_t hi = (sbo >> 4) | (1u << 14);
+  return ptx::desc_from_halves(lo, hi);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_abort;
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 127u) & ~127u;
+  const int crow_bytes = p.x_tiles * 128 * 128;            // one fp16 conv row, 128 B per pixel
+  const uint32_t sW = base;
+  const uint32_t sRing = sW + kWBytes;
+  const uint32_t sConv = sRing + (uint32_t)kRingSlots * p.slot_bytes + 256;
+  const uint32_t bars = (sConv + (uint32_t)kConvRing * crow_bytes + 7u) & ~7u;
+  const uint32_t full = bars, empty = bars + 8 * kRingSlots;
+  const uint32_t acc_full = empty + 8 * kRingSlots, acc_empty = acc_full + 8 * kAccBufs;
+  const uint32_t w_full = acc_empty + 8 * kAccBufs;
+  const uint32_t tmem_slot = w_full + 8;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kRingSlots; ++i) {
+      ptx::mbar_init(full + 8 * i, 1);
+      ptx::mbar_init(empty + 8 * i, 1);
+    }
+    for (int i = 0; i < kAccBufs; ++i) {
+      ptx::mbar_init(acc_full + 8 * i, 1);
+      ptx::mbar_init(acc_empty + 8 * i, kEpiThreads);
+    }
+    ptx::mbar_init(w_full, 1);
+    ptx::mbar_fence_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, kAccBufs * 64);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
+  volatile int* abort_flag = &s_abort;
+
+  const int total_items = p.N * p.bands;
+  // item -> image, conv rows [y0, y1], input rows [ir0, ir1]
+  auto item_of = [&](int i, int& n, int& p0, int& p1, int& y0, int& y1, int& ir0, int& ir1) {
+    const int w = (int)blockIdx.x + i * (int)gridDim.x;
+    if (w >= total_items) return false;
+    n = w / p.bands;
+    const int b = w - n * p.bands;
+    p0 = b * p.band_rows;
+    p1 = min(p.PH, p0 + p.band_rows);
+    y0 = max(0, 2 * p0 - 1);
+    y1 = min(p.OH - 1, 2 * p1 - 1);
+    ir0 = max(0, 2 * y0 - 3);
+    ir1 = min(p.H - 1, 2 * y1 + 3);
+    return true;
+  };
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- input rows -------
+    if (lane == 0) {
+      ptx::mbar_arrive_expect_tx(w_full, kWBytes);
+      ptx::bulk_g2s(sW, p.wpack, kWBytes, w_full);
+      uint32_t seq = 0;
+      bool okw = true;
+      for (int i = 0; okw; ++i) {
+        int n, p0, p1, y0, y1, ir0, ir1;
+        if (!item_of(i, n, p0, p1, y0, y1, ir0, ir1)) break;
+        const uint8_t* img = p.in_rows + (size_t)n * p.H * p.row_bytes;
+        for (int ir = ir0; ir <= ir1; ++ir, ++seq) {
+          const uint32_t slot = seq % kRingSlots;
+          if (!ptx::mbar_wait_abortable(empty + 8 * slot, ((seq / kRingSlots) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
+          ptx::mbar_arrive_expect_tx(full + 8 * slot, (uint32_t)p.row_bytes);
+          ptx::bulk_g2s(sRing + slot * p.slot_bytes, img + (size_t)ir * p.row_bytes, (uint32_t)p.row_bytes, full + 8 * slot);
+        }
+      }
+      if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitProducer);
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer -------
+    if (lane == 0) {
+      const uint32_t idesc = ptx::umma_idesc(128, 64, p.bf16 ? 1 : 0);
+      bool okw = ptx::mbar_wait_abortable(w_full, 0, abort_flag);
+      uint32_t seq_base = 0, acc_cnt = 0;
+      for (int i = 0; okw; ++i) {
+        int n, p0, p1, y0, y1, ir0, ir1;
+        if (!item_of(i, n, p0, p1, y0, y1, ir0, ir1)) break;
+        int waited_upto = ir0;     // input rows [ir0, waited_upto) are known to be in the ring
+        int released_upto = ir0;   // input rows [ir0, released_upto) were handed back
+        for (int y = y0; y <= y1 && okw; ++y) {
+          const int need = min(ir1, 2 * y + 3);
+          for (; waited_upto <= need; ++waited_upto) {
+            const uint32_t s = seq_base + (uint32_t)(waited_upto - ir0);
+            if (!ptx::mbar_wait_abortable(full + 8 * (s % kRingSlots), (s / kRingSlots) & 1u, abort_flag)) { okw = false; break; }
+          }
+          if (!okw) break;
+          ptx::tc_fence_after();
+          for (int xt = 0; xt < p.x_tiles && okw; ++xt) {
+            const uint32_t ab = acc_cnt % kAccBufs;
+            if (!ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt / kAccBufs) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
+            ptx::tc_fence_after();
+            uint32_t accumulate = 0;
+            for (int r = 0; r < 7; ++r) {
+              const int ir = 2 * y + r - 3;
+              if (ir < 0 || ir >= p.H) continue;   // zero padding rows contribute nothing
+              const uint32_t s = seq_base + (uint32_t)(ir - ir0);
+              const uint32_t a_addr = sRing + (s % kRingSlots) * p.slot_bytes + (uint32_t)xt * 2048u;
+              const uint32_t b_addr = sW + (uint32_t)r * 4096u;
+#pragma unroll
+              for (int k2 = 0; k2 < 2; ++k2) {
+                ptx::umma_f16(tmem_base + ab * 64, desc_noswz(a_addr + k2 * 32, 16, 128),
+                              desc_noswz(b_addr + k2 * 2048, 1024, 128), idesc, accumulate);
+                accumulate = 1;
+              }
+            }
+            ptx::tc_commit(acc_full + 8 * ab);
+            ++acc_cnt;
+          }
+          // input rows no later conv row of this item needs go back to the producer
+          const int new_upto = (y == y1) ? ir1 + 1 : min(ir1 + 1, 2 * y - 1);
+          for (; released_upto < new_upto; ++released_upto) {
+            const uint32_t s = seq_base + (uint32_t)(released_upto - ir0);
+            ptx::tc_commit(empty + 8 * (s % kRingSlots));
+          }
+        }
+        seq_base += (uint32_t)(ir1 - ir0 + 1);
+      }
+      if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitMma);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue ---------
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;          // output column within the x tile
+    const int et = threadIdx.x - 64;           // 0..255
+    float4 sc[8], sh[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      sc[i] = p.scale ? __ldg(reinterpret_cast<const float4*>(p.scale + half * 32) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+      sh[i] = p.shift ? __ldg(reinterpret_cast<const float4*>(p.shift + half * 32) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    uint32_t acc_cnt = 0;
+    bool okw = true;
+    for (int i = 0; okw; ++i) {
+      int n, p0, p1, y0, y1, ir0, ir1;
+      if (!item_of(i, n, p0, p1, y0, y1, ir0, ir1)) break;
+      int next_pool = p0;
+      for (int y = y0; y <= y1 && okw; ++y) {
+        const uint32_t crow = sConv + (uint32_t)(y % kConvRing) * crow_bytes;
+        for (int xt = 0; xt < p.x_tiles; ++xt) {
+          const uint32_t ab = acc_cnt % kAccBufs;
+          const bool got = ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt / kAccBufs) & 1u, abort_flag);
+          if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; break; }
+          ptx::tc_fence_after();
+          uint32_t acc[32];
+          __syncwarp();
+          ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + ab * 64 + half * 32, acc);
+          ptx::tmem_ld_wait();
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(acc_empty + 8 * ab);
+          ++acc_cnt;
+          const int x = xt * 128 + row;
+          const uint32_t prow = crow + (uint32_t)x * 128u;
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint32_t o[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const int e = c4 * 8 + h * 2;
+              const float4 s4 = sc[e >> 2], b4 = sh[e >> 2];
+              const float sa = (e & 2) ? s4.z : s4.x, sb = (e & 2) ? s4.w : s4.y;
+              const float ba = (e & 2) ? b4.z : b4.x, bb = (e & 2) ? b4.w : b4.y;
+              const float a = fmaf(__uint_as_float(acc[e]), sa, ba);
+              const float b = fmaf(__uint_as_float(acc[e + 1]), sb, bb);
+              if (p.bf16) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+                o[h] = *reinterpret_cast<uint32_t*>(&v);
+              } else {
+                __half2 v = __floats2half2_rn(a, b);
+                o[h] = *reinterpret_cast<uint32_t*>(&v);
+              }
+            }
+            const uint32_t chunk = (uint32_t)(half * 4 + c4);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + ((chunk ^ (uint32_t)(x & 7)) << 4)),
+                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                         : "memory");
+          }
+        }
+        if (!okw) break;
+        ptx::named_bar_sync(1, kEpiThreads);   // conv row y is complete in shared memory
+        // pooled rows whose last conv row is y
+        while (next_pool < p1 && min(2 * next_pool + 1, p.OH - 1) <= y) {
+          const int pr = next_pool++;
+          const int ya = max(0, 2 * pr - 1), yb = min(p.OH - 1, 2 * pr + 1);
+          uint16_t* orow = p.out + ((size_t)((size_t)n * p.ol.img_rows + pr + p.ol.off) * p.ol.pitch + p.ol.off) * 64;
+          for (int u = et; u < p.PW * 8; u += kEpiThreads) {
+            const int px = u >> 3, c = u & 7;
+            const int xa = max(0, 2 * px - 1), xb = min(p.OW - 1, 2 * px + 1);
+            uint32_t m[4];
+            bool first = true;
+            for (int yy = ya; yy <= yb; ++yy) {
+              const uint32_t cr = sConv + (uint32_t)(yy % kConvRing) * crow_bytes;
+              for (int xx = xa; xx <= xb; ++xx) {
+                uint32_t v[4];
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+                             : "r"(cr + (uint32_t)xx * 128u + (((uint32_t)c ^ (uint32_t)(xx & 7)) << 4)));
+                if (first) {
+#pragma unroll
+                  for (int h = 0; h < 4; ++h) m[h] = v[h];
+                  first = false;
+                } else {
+#pragma unroll
+                  for (int h = 0; h < 4; ++h) {
+                    if (p.bf16) {
+                      __nv_bfloat162 r = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&m[h]), *reinterpret_cast<__nv_bfloat162*>(&v[h]));
+                      m[h] = *reinterpret_cast<uint32_t*>(&r);
+                    } else {
+                      __half2 r = __hmax2_nan(*reinterpret_cast<__half2*>(&m[h]), *reinterpret_cast<__half2*>(&v[h]));
+                      m[h] = *reinterpret_cast<uint32_t*>(&r);
+                    }
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {   // ReLU after the max (NaN passes)
+              if (p.bf16) {
+                __nv_bfloat162 r = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&m[h]), __floats2bfloat162_rn(0.f, 0.f));
+                m[h] = *reinterpret_cast<uint32_t*>(&r);
+              } else {
+                __half2 r = __hmax2_nan(*reinterpret_cast<__half2*>(&m[h]), __floats2half2_rn(0.f, 0.f));
+                m[h] = *reinterpret_cast<uint32_t*>(&r);
+              }
+            }
+            *reinterpret_cast<uint4*>(orow + (size_t)px * 64 + c * 8) = make_uint4(m[0], m[1], m[2], m[3]);
+          }
+        }
+      }
+      // the next item starts writing the conv ring only after everyone has finished pooling
+      ptx::named_bar_sync(2, kEpiThreads);
+    }
+    if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitEpilogue);
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tmem_dealloc(tmem_base, kAccBufs * 64);
+  }
+}
+
+// NCHW (any dtype) -> fp16/bf16 rows of 4-channel pixels with 4 zero pixels in front; one thread
+// per output pixel slot (8-byte store), the tail of every row is zero.
+template <typename SrcT, typename DstT>
+__global__ void nchw_to_stem_rows_kernel(const SrcT* __restrict__ src, DstT* __restrict__ dst, int N,
+                                         int H, int W, int RW) {
+  const long long total = (long long)N * H * RW;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int xs = (int)(i % RW);
+    const long long t = i / RW;
+    const int y = (int)(t % H);
+    const int n = (int)(t / H);
+    const int x = xs - 4;
+    alignas(8) DstT v[4];
+    if (x >= 0 && x < W) {
+      const SrcT* s = src + ((size_t)n * 3 * H + y) * W + x;
+      v[0] = (DstT)(float)s[0];
+      v[1] = (DstT)(float)s[(size_t)H * W];
+      v[2] = (DstT)(float)s[(size_t)2 * H * W];
+      v[3] = (DstT)0.0f;
+    } else {
+      v[0] = v[1] = v[2] = v[3] = (DstT)0.0f;
+    }
+    *reinterpret_cast<uint2*>(dst + i * 4) = *reinterpret_cast<const uint2*>(v);
+  }
+}
+
+// W[64][3][7][7] -> per filter row r a [64 x 32] K-major un-swizzled tile: element (n, k) at
+// (k / 8) * 1024 + (n / 8) * 128 + (n % 8) * 16 + (k % 8) * 2; k = 4 * tap + channel, tap 0 is the
+// zero-weight pixel in front of the window, channel 3 is the zero padding channel.
+template <typename SrcT, typename DstT>
+__global__ void pack_stem_weights_kernel(const SrcT* __restrict__ w, DstT* __restrict__ dst) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 7 * 64 * 32) return;
+  const int k = i % 32, n = (i / 32) % 64, r = i / (32 * 64);
+  const int tap = k / 4, ch = k % 4;
+  float v = 0.0f;
+  if (tap >= 1 && ch < 3) v = (float)w[((n * 3 + ch) * 7 + r) * 7 + (tap - 1)];
+  const size_t off = (size_t)r * 4096 + (size_t)(k / 8) * 1024 + (size_t)(n / 8) * 128 + (size_t)(n % 8) * 16 + (size_t)(k % 8) * 2;
+  *reinterpret_cast<DstT*>(reinterpret_cast<uint8_t*>(dst) + off) = (DstT)v;
+}
+
+template <typename F>
+cudaError_t by_dt(DType t, F&& f) {
+  switch (t) {
+    case kF32: return f(float{});
+    case kF16: return f(__half{});
+    case kBF16: return f(__nv_bfloat16{});
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+int stem_row_pixels(int W) { return (4 + W + 4 + 1) & ~1; }
+size_t stem_rows_bytes(int N, int H, int W) { return (size_t)N * H * stem_row_pixels(W) * 8; }
+size_t stem_wpack_bytes() { return kWBytes; }
+
+cudaError_t launch_nchw_to_stem_rows(const void* src, DType src_dt, void* dst, DType dst_dt, int N, int H,
+                                     int W, cudaStream_t stream) {
+  const int RW = stem_row_pixels(W);
+  const long long total = (long long)N * H * RW;
+  long long blocks = (total + 255) / 256;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  if (dst_dt == kF32) return cudaErrorInvalidValue;
+  return by_dt(src_dt, [&](auto st) {
+    using S = decltype(st);
+    if (dst_dt == kBF16)
+      nchw_to_stem_rows_kernel<S, __nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+          static_cast<const S*>(src), static_cast<__nv_bfloat16*>(dst), N, H, W, RW);
+    else
+      nchw_to_stem_rows_kernel<S, __half><<<(int)blocks, 256, 0, stream>>>(
+          static_cast<const S*>(src), static_cast<__half*>(dst), N, H, W, RW);
+    return cudaGetLastError();
+  });
+}
+
+cudaError_t launch_pack_stem_weights(const void* w, DType w_dt, void* dst, DType dst_dt, cudaStream_t stream) {
+  if (dst_dt == kF32) return cudaErrorInvalidValue;
+  return by_dt(w_dt, [&](auto st) {
+    using S = decltype(st);
+    if (dst_dt == kBF16)
+      pack_stem_weights_kernel<S, __nv_bfloat16><<<(7 * 64 * 32 + 255) / 256, 256, 0, stream>>>(
+          static_cast<const S*>(w), static_cast<__nv_bfloat16*>(dst));
+    else
+      pack_stem_weights_kernel<S, __half><<<(7 * 64 * 32 + 255) / 256, 256, 0, stream>>>(
+          static_cast<const S*>(w), static_cast<__half*>(dst));
+    return cudaGetLastError();
+  });
+}
+
+cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream) {
+  if (a.ab == kF32 || a.N <= 0 || a.H < 7 || a.W < 7) return cudaErrorInvalidValue;
+  StemParams p;
+  p.in_rows = static_cast<const uint8_t*>(a.in_rows);
+  p.wpack = static_cast<const uint8_t*>(a.wpack);
+  p.scale = a.scale; p.shift = a.shift;
+  p.out = static_cast<uint16_t*>(a.out);
+  p.error_flag = a.error_flag;
+  p.N = a.N; p.H = a.H; p.W = a.W;
+  p.OH = (a.H + 6 - 7) / 2 + 1; p.OW = (a.W + 6 - 7) / 2 + 1;
+  p.PH = (p.OH + 2 - 3) / 2 + 1; p.PW = (p.OW + 2 - 3) / 2 + 1;
+  p.ol = a.out_l.pitch ? a.out_l : dense_layout(p.PH, p.PW);
+  p.row_bytes = stem_row_pixels(a.W) * 8;
+  p.x_tiles = (p.OW + 127) / 128;
+  // the last x tile's junk rows read up to chunk (x_tiles*128 - 1) + 3 of the slot
+  int slot = p.x_tiles * 2048 + 64;
+  if (slot < p.row_bytes) slot = p.row_bytes;
+  p.slot_bytes = (slot + 15) & ~15;
+  p.bf16 = a.ab == kBF16;
+  const int sms = a.sm_count > 0 ? a.sm_count : 148;
+  // bands: enough items to fill the SMs several times over, at least 4 pooled rows each
+  int band_rows = p.PH;
+  while (band_rows > 4 && (long long)a.N * ((p.PH + band_rows - 1) / band_rows) < 6LL * sms) band_rows = (band_rows + 1) / 2;
+  p.band_rows = band_rows;
+  p.bands = (p.PH + band_rows - 1) / band_rows;
+  const size_t smem = 128 + kWBytes + (size_t)kRingSlots * p.slot_bytes + 256 +
+                      (size_t)kConvRing * p.x_tiles * 128 * 128 + 8 + 8 * (2 * kRingSlots + 2 * kAccBufs + 1) + 16;
+  if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
+  cudaError_t e = cudaFuncSetAttribute(stem_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const int items = a.N * p.bands;
+  stem_pool_kernel<<<items < sms ? items : sms, kThreads, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+}  // namespace nncv_b200

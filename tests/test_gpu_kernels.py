@@ -187,6 +187,36 @@ def test_conv_winograd_fixture_closed_form():
     np.testing.assert_allclose(y, 3.6, rtol=1e-6)
 
 
+@pytest.mark.parametrize("shape", [(2, 32, 32), (2, 224, 224), (1, 37, 53), (1, 64, 300), (3, 256, 256), (1, 7, 7)])
+@pytest.mark.parametrize("dtype,in_dt", [(F16, F32), (F16, F16), (BF16, F32)])
+def test_stem_pool_fused(shape, dtype, in_dt):
+    """7x7 s2 conv + scale/shift + ReLU + 3x3 s2 max-pool in one kernel vs the oracle's
+    conv -> batch-norm-style affine -> ReLU -> max-pool chain (Res18.mlir:118-151)."""
+    n, h, w = shape
+    g = _rng(n * 1000 + h + w)
+    x = g.standard_normal((n, 3, h, w)).astype(np.float32)
+    wt = (g.standard_normal((64, 3, 7, 7)) * np.sqrt(2.0 / 147)).astype(np.float32)
+    scale = g.uniform(0.5, 1.5, 64).astype(np.float32)
+    shift = (g.standard_normal(64) * 0.1).astype(np.float32)
+    X = G.dev(x, in_dt)
+    Wd = G.dev(wt, F32)
+    sc, sh = G.dev(scale, F32), G.dev(shift, F32)
+    oh, ow = (h + 6 - 7) // 2 + 1, (w + 6 - 7) // 2 + 1
+    ph, pw = (oh + 2 - 3) // 2 + 1, (ow + 2 - 3) // 2 + 1
+    Y = torch.full((n, ph, pw, 64), float("nan"), device="cuda", dtype=G.TORCH_DT[dtype])
+    check(lib().nncv_b200_stem_pool(G.p(X), in_dt, G.p(Wd), F32, G.p(sc), G.p(sh), G.p(Y), dtype, n, h, w,
+                                    G.stream_ptr()))
+    torch.cuda.synchronize()
+    tdt = G.TORCH_DT[dtype]
+    xr = torch.from_numpy(x).to(G.TORCH_DT[in_dt]).to(tdt).float().numpy()
+    wr = torch.from_numpy(wt).to(tdt).float().numpy()
+    conv = ob.conv2d(xr, wr, 2, 3, acc64=True) * scale[None, :, None, None] + shift[None, :, None, None]
+    ref = ob.maxpool(ob.relu(conv), 3, 2, 1)
+    y = G.host(Y).transpose(0, 3, 1, 2)
+    assert y.shape == ref.shape and np.isfinite(y).all()
+    assert G.rel_l2(y, ref) <= (TOL_16 if dtype == F16 else 8e-3)
+
+
 @pytest.mark.parametrize("dtype", [F16, F32])
 def test_maxpool(dtype):
     g = _rng(11)
