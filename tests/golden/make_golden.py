@@ -4,7 +4,7 @@ read only the files this script wrote):
 
     python tests/golden/make_golden.py
 
-  res18_constants.json   shapes of the constants of tests/Nets/Res18.mlir:12-109, in order
+  res18_constants.json   shapes of the constants of tests/Nets/Res18.mlir:12-110, in order
   kat0_two_params.bin    the SplitParams known-answer weights (tests/SplitParams/getParams.py:15-29)
                          written by the REFERENCE's own MemRefFlatArray::write (oracle/_ref)
   res18_fp32_n1_256.npz  logits of ResNet-18 fp32, N=1, 3x256x256 U[0,1) seed 0, from the oracle
@@ -36,7 +36,7 @@ def constants():
     shapes = []
     with open(os.path.join(REF, "tests/Nets/Res18.mlir")) as f:
         for i, line in enumerate(f, 1):
-            if 12 <= i <= 109:
+            if 12 <= i <= 110:
                 m = re.search(r"(%cst(?:_\d+)?) = arith.constant dense_resource<__elided__> : tensor<([0-9x]+)xf32>", line)
                 assert m, line
                 shapes.append([m.group(1), [int(v) for v in m.group(2).split("x")]])

@@ -1,0 +1,57 @@
+"""The C-ABI library loads and exports exactly what include/nncv_b200.h declares; without a GPU every
+compute entry point fails loudly (there is no CPU fallback)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from nncv_b200 import _lib
+from nncv_b200 import runtime as rt
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "nncv_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{}]*\)\s*;", text)
+    return sorted(set(n for n in names if n.startswith(("nncv_", "_mlir_ciface_"))))
+
+
+def test_header_and_library_agree():
+    declared = declared_functions()
+    assert "_mlir_ciface_forward" in declared and "nncv_b200_load" in declared
+    L = _lib.lib()
+    missing = [n for n in declared if not hasattr(L, n)]
+    assert not missing, f"declared in the header but not exported: {missing}"
+    assert sorted(_lib.EXPORTS) == declared, "nncv_b200/_lib.py EXPORTS is out of step with the header"
+
+
+def test_library_does_not_link_the_oracle():
+    out = os.popen(f"ldd {_lib.LIB_PATH}").read()
+    assert "oracle" not in out and "nncv_rt_ref" not in out
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")
+def test_no_gpu_means_loud_failure_not_cpu_fallback():
+    L = _lib.lib()
+    a = np.zeros((8, 8), np.float16)
+    rc = L.nncv_b200_matmul(a.ctypes.data, a.ctypes.data, a.ctypes.data, 8, 8, 8, _lib.F16, _lib.F16, None, 0, None)
+    assert rc == 3 and b"no CPU fallback" in L.nncv_b200_last_error()   # NNCV_B200_ENODEVICE
+    with pytest.raises(_lib.NncvError) as e:
+        rt.load_blob("resnet18", np.zeros(11699112, np.float32))
+    assert e.value.code == 3
+    out = np.full((1, 1000), 5.0, np.float32)
+    with pytest.raises(_lib.NncvError):
+        rt.forward(out, np.zeros((1, 3, 64, 64), np.float32), np.zeros(11699112, np.float32))
+    assert (out == 5.0).all()
+
+
+def test_missing_library_raises(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libnncv_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        _lib.lib()
