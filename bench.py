@@ -243,11 +243,11 @@ def run_ours(args):
 
     if rank == 0:
         tf_peak, tf_sus, hbm_peak, which = peaks()
-        conv = [r for r in prof if r["kind"] in (0, 2, 4)]
+        conv = [r for r in prof if r["kind"] in (0, 2, 4, 5)]
         conv_ms = sum(r["ms"] for r in conv)
         conv_fl = sum(r["flops"] for r in conv)
         n_conv = len(conv)
-        other_ms = sum(r["ms"] for r in prof if r["kind"] not in (0, 2, 4))
+        other_ms = sum(r["ms"] for r in prof if r["kind"] not in (0, 2, 4, 5))
         achieved = conv_fl / (conv_ms * 1e-3) / 1e12 if conv_ms > 0 else None
         traffic = None
         try:

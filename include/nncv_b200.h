@@ -119,7 +119,8 @@ long long nncv_b200_launch_count(void);
  * only has wall-clock timers around the whole forward (examples/Res18/main.cpp:95-99). */
 typedef struct {
   int kind;      /* 0 tcgen05 implicit GEMM (gathered A), 1 fp32 CUDA-core conv, 2 tcgen05 3x3 shifted-view
-                    conv, 3 memory-bound helper, 4 fused stem conv + max-pool */
+                    conv, 3 memory-bound helper, 4 fused stem conv + max-pool, 5 tcgen05 implicit GEMM
+                    (TMA-fed A) */
   int M, N, K;   /* GEMM view of the launch (helpers: elements, channels, 0) */
   int bn;        /* N tile (kind 0); helper id (kind 3) */
   double flops;  /* algorithmic: 2*M*N*K with K = C*R*S (direct-convolution count) */
@@ -155,8 +156,9 @@ int nncv_b200_matmul(const void* A, const void* B, void* C, int M, int N, int K,
  * epilogue, on NHWC activations.  Weights are prepared once into a plan. */
 typedef struct nncv_b200_conv nncv_b200_conv;
 /* weights: host or device [Kout,C,R,S] of w_dtype.  dtype: activation type (F16/BF16 -> tcgen05
- * implicit GEMM, F32 -> CUDA-core).  algo: 0 = implicit GEMM with a gathered A operand (any
- * shape), 2 = 3x3 stride-1 pad-1 implicit GEMM whose nine taps are shifted views of one
+ * implicit GEMM, F32 -> CUDA-core).  algo: 0 = implicit GEMM, A operand fetched by strided TMA
+ * copies when C %% 64 == 0 and by a cp.async gather otherwise (any shape), 3 = always the gather
+ * kernel, 2 = 3x3 stride-1 pad-1 implicit GEMM whose nine taps are shifted views of one
  * shared-memory halo tile (16-bit types, C and Kout multiples of 64).  Activation channel count is C rounded up to 8 (F16/BF16) or 4 (F32). */
 nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout, int C, int R,
                                       int S, int stride, int pad, int dtype, int algo);
@@ -166,8 +168,8 @@ int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int 
                        const float* scale, const float* shift, const void* residual, int relu,
                        void* stream);
 
-/* algo 2 only: force the tile configuration (N tile 64/128/256, sub-tiles per CTA 1/2/4,
- * weights resident in shared memory or streamed); bn = 0 restores the built-in choice.  A tuning
+/* Force the tile configuration (N tile 64/128/256; algo 2: sub-tiles per CTA 1/2/4; weights
+ * resident in shared memory or streamed); bn = 0 restores the built-in choice.  A tuning
  * and test hook with no counterpart in the reference. */
 int nncv_b200_conv_set_tile(nncv_b200_conv* c, int bn, int mt, int resident);
 

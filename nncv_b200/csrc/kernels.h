@@ -85,6 +85,27 @@ bool conv3x3_supported(int C, int Kout, int R, int S, int stride, int pad);
 Conv3x3Config conv3x3_pick(int N, int H, int W, int C, int Kout, int has_res);
 cudaError_t launch_conv3x3(const Conv3x3Args& a, cudaStream_t stream);
 
+// ---- TMA-fed persistent implicit GEMM (1x1 / strided convs, GEMM): C % 64 == 0 -----------------
+struct TconvArgs {
+  const void* in = nullptr;        // activation in layout in_l, or A[M,K] as {1, M, 0}
+  const void* wpack = nullptr;     // packed by launch_pack_weights for N tile `bn`
+  const float* scale = nullptr;
+  const float* shift = nullptr;
+  const void* residual = nullptr;  // layout out_l, 16-bit
+  void* out = nullptr;             // layout out_l, row pitch == Kout
+  int N = 0, H = 0, W = 0, C = 0, OH = 0, OW = 0, Kout = 0, R = 1, S = 1, stride = 1, pad = 0;
+  Layout in_l{0, 0, 0}, out_l{0, 0, 0};
+  int bn = 64, resident = 0;
+  DType ab = kF16, out_dtype = kF16;
+  int relu = 0;
+  int sm_count = 0;
+  int* error_flag = nullptr;
+};
+bool tconv_supported(int C, int Kout, DType out_dt, long long ldo);
+void tconv_tile(int N, int OH, int OW, int* tw, int* th, int* tn);
+void tconv_pick(long long m_items, int C, int Kout, int taps, int* bn, int* resident);
+cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream);
+
 // ---- ResNet stem: 7x7 s2 p3 conv (3 -> 64) + scale/shift + ReLU + 3x3 s2 p1 max-pool, fused ---
 struct StemArgs {
   const void* in_rows = nullptr;   // rows written by launch_nchw_to_stem_rows

@@ -126,6 +126,7 @@ struct ProfRec {
   cudaEvent_t e0, e1;
   float ms;
 };
+bool g_force_gather = false;  // tuning/test hook: route algo-0 convs through the gather kernel
 bool g_prof_on = false;
 std::vector<ProfRec> g_prof;
 
@@ -204,6 +205,7 @@ struct nncv_b200_conv {
   DevBuf w_f32;                                    // fp32 path: [Kout][R*S][Cpad]
   bool w_f32_ready = false;
   DevBuf sp_in, sp_out, sp_res;                    // standalone algo 2: shared-pad copies
+  bool force_gather = false;                       // algo 3: the cp.async gather kernel even where TMA would do
   Conv3x3Config cfg3{0, 0, 0};                     // algo 2: forced tile configuration (bn 0 = auto)
 };
 
@@ -274,6 +276,28 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
     a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
     prof_begin(2, flops, bytes, (int)M, c->Kout, c->C * 9, cfg.bn * 1000 + cfg.mt * 10 + cfg.resident, st);
     LAUNCH(launch_conv3x3(a, st));
+    prof_end(st);
+    return NNCV_B200_OK;
+  }
+  if (c->algo == 0 && !g_force_gather && !c->force_gather && tconv_supported(c->Cpad, c->Kout, out_dt, ldo) &&
+      (out_dt == kF32 ? 32 : 64) <= c->Kout) {
+    // TMA-fed persistent kernel: no thread-side gather
+    int tw, th, tn, bn, resident;
+    tconv_tile(N, OH, OW, &tw, &th, &tn);
+    const long long m_items = (long long)((OW + tw - 1) / tw) * ((OH + th - 1) / th) * ((N + tn - 1) / tn);
+    tconv_pick(m_items, c->Cpad, c->Kout, c->R * c->S, &bn, &resident);
+    if (c->cfg3.bn) { bn = c->cfg3.bn; resident = c->cfg3.resident; }
+    const void* wpack = nullptr;
+    int rc = conv_prepare(c, bn, st, &wpack);
+    if (rc) return rc;
+    TconvArgs a;
+    a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
+    a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
+    a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.in_l = in_l; a.out_l = out_l;
+    a.bn = bn; a.resident = resident; a.ab = c->dtype; a.out_dtype = out_dt; a.relu = relu;
+    a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
+    prof_begin(5, flops, bytes, (int)M, c->Kout, c->C * c->R * c->S, bn * 10 + resident, st);
+    LAUNCH(launch_tconv(a, st));
     prof_end(st);
     return NNCV_B200_OK;
   }
@@ -931,6 +955,20 @@ int nncv_b200_matmul(const void* A, const void* B, void* C, int M, int N, int K,
   if (ab_dtype != NNCV_B200_F16 && ab_dtype != NNCV_B200_BF16) return fail(NNCV_B200_EINVAL, "matmul: bad ab_dtype");
   if (c_dtype != NNCV_B200_F32 && c_dtype != ab_dtype) return fail(NNCV_B200_EINVAL, "matmul: c_dtype must be F32 or ab_dtype");
   if (K % 8 != 0) return fail(NNCV_B200_EINVAL, "matmul: the tcgen05 path needs K %% 8 == 0");
+  if (K % 64 == 0 && tconv_supported(K, N, (DType)c_dtype, N) && N >= 64) {
+    int bn, resident;
+    tconv_pick((M + 127) / 128, K, N, 1, &bn, &resident);
+    if ((rc = ensure_scratch(packed_weight_bytes(N, K, 1, 1, bn)))) return rc;
+    LAUNCH(launch_pack_weights(B, (DType)ab_dtype, 1, N, 0, N, K, K, 1, bn, (DType)ab_dtype, g_dev.scratch, st));
+    TconvArgs a;
+    a.in = A; a.wpack = g_dev.scratch; a.shift = bias; a.out = C;
+    a.N = 1; a.H = 1; a.W = M; a.OH = 1; a.OW = M; a.C = K; a.Kout = N;
+    a.in_l = Layout{1, M, 0}; a.out_l = Layout{1, M, 0};
+    a.bn = bn; a.resident = resident; a.ab = (DType)ab_dtype; a.out_dtype = (DType)c_dtype; a.relu = relu;
+    a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
+    LAUNCH(launch_tconv(a, st));
+    return ok();
+  }
   const int bn = igemm_pick_bn(M, N);
   if ((rc = ensure_scratch(packed_weight_bytes(N, K, 1, 1, bn)))) return rc;
   LAUNCH(launch_pack_weights(B, (DType)ab_dtype, 1, N, 0, N, K, K, 1, bn, (DType)ab_dtype, g_dev.scratch, st));
@@ -951,7 +989,7 @@ nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout
     fail(NNCV_B200_EINVAL, "conv_create: bad argument");
     return nullptr;
   }
-  if (algo != 0 && algo != 2) {
+  if (algo != 0 && algo != 2 && algo != 3) {
     fail(NNCV_B200_EINVAL, "conv_create: algo %d is not available", algo);
     return nullptr;
   }
@@ -961,7 +999,7 @@ nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout
   }
   auto c = std::make_unique<nncv_b200_conv>();
   c->Kout = Kout; c->C = C; c->R = R; c->S = S; c->stride = stride; c->pad = pad;
-  c->dtype = (DType)dtype; c->algo = algo;
+  c->dtype = (DType)dtype; c->algo = algo == 3 ? 0 : algo; c->force_gather = algo == 3;
   c->Cpad = dtype == NNCV_B200_F32 ? (C + 3) / 4 * 4 : (C + 7) / 8 * 8;
   const size_t bytes = (size_t)Kout * C * R * S * dtype_size((DType)w_dtype);
   if (c->raw_owned.reserve(bytes)) return nullptr;
@@ -1015,7 +1053,7 @@ int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int 
 
 int nncv_b200_conv_set_tile(nncv_b200_conv* c, int bn, int mt, int resident) {
   std::lock_guard<std::mutex> lk(g_mutex);
-  if (!c || c->algo != 2) return fail(NNCV_B200_EINVAL, "conv_set_tile: only for algo 2 plans");
+  if (!c) return fail(NNCV_B200_EINVAL, "conv_set_tile: null plan");
   c->cfg3 = Conv3x3Config{bn, mt, resident};
   return ok();
 }

@@ -1,0 +1,504 @@
+// TMA-fed persistent implicit-GEMM convolution / GEMM for sm_100a (tcgen05 + TMEM).
+//
+// Covers the convolutions whose taps cannot share one halo tile -- 1x1 and 3x3 with stride 2
+// (tests/Nets/Res18.mlir: the convs on %padded_107/111/115 and the 1x1 downsample convs on
+// %cst_62/38/14), ResNet-50's 1x1 convs -- and plain linalg.matmul / the FC layer
+// (Res18.mlir:617-628, tests/MatMulOptimization/MatMulNv.mlir:6-9).  nncv lowers strided convs
+// with an extra {1,1} tile to near-scalar loops (ModernTile.cpp:201-209) and aims matmul at
+// 16x16x16 wmma tiles (ModernTileGpu.cpp:427-525, PrepareModernVecGpu.cpp:43-48).
+//
+// GEMM view: D[pixels, Kout] = A[pixels, R*S*C] * W[Kout, R*S*C]^T.  The M tile is a block of
+// tn images x th rows x tw columns of OUTPUT pixels (tn*th*tw = 128).  For every (tap, 64-channel
+// block) ONE 4-D tiled TMA copy with element strides (1, stride, stride, 1) fetches exactly the
+// input pixels that tile needs -- x = stride*ox + s - pad, y = stride*oy + r - pad -- as 128 rows
+// of 128 bytes in the swizzled K-major layout tcgen05.mma reads; out-of-range pixels (padding,
+// ragged tiles) arrive as zeros.  No thread touches the A operand.  A plain [M,K] matrix is the
+// degenerate case tw = 128, th = tn = 1.
+// Weights are the packed [Kout tile][k-block] images of launch_pack_weights(): resident in shared
+// memory for the whole kernel when they fit, otherwise streamed with the A stage.
+// Roles: warp 0 TMA producer, warp 1 MMA issuer (accumulator double-buffered in TMEM), warps 2-9
+// epilogue (scale/shift, residual, ReLU, 128-byte-row slab in shared memory, 4-D TMA store, which
+// clips ragged tiles and keeps the pads of shared-pad tensors untouched).
+// Every wait is bounded and abortable; a timed-out wait sets the device status word.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace nncv_b200 {
+
+namespace {
+
+constexpr int kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;
+constexpr int kABytes = 128 * 128;
+constexpr int kSlabBytes = 128 * 128;
+constexpr int kMaxStages = 8;
+
+struct TcParams {
+  const uint8_t* wpack;
+  const float* scale;
+  const float* shift;
+  const uint8_t* residual;   // same layout / type as out, or null
+  int* error_flag;
+  int Kout, CB, taps, S, stride, pad;
+  int in_off;                // layout offset of the input (0 dense, 1 shared-pad)
+  int out_off;
+  int OH, OW, NB;            // logical output extent
+  int out_pitch, out_rows;   // output layout: slots per row, rows per image
+  int tw, th, tn;            // M tile shape
+  int tiles_x, tiles_y, tiles_n, n_tiles, m_items;
+  int stages;                // A (+ streamed weight) ring depth
+  int relu, bf16, out_f32;
+};
+
+template <int BN, bool RESIDENT>
+__global__ void __launch_bounds__(kThreads, 1)
+tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_out,
+             const TcParams p) {
+  constexpr int WTILE = BN * 128;
+  constexpr int ACC_COLS = 2 * BN;   // two accumulator buffers
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_abort;
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const int KB = p.taps * p.CB;
+  const int stage_bytes = RESIDENT ? kABytes : kABytes + WTILE;
+  const uint32_t sRing = base;
+  const uint32_t sW = sRing + (uint32_t)p.stages * stage_bytes;       // resident weights
+  const uint32_t sStage = sW + (RESIDENT ? (uint32_t)KB * WTILE : 0u);
+  const uint32_t bars = sStage + 2 * kSlabBytes;
+  const uint32_t full = bars, empty = bars + 8 * kMaxStages;
+  const uint32_t acc_full = empty + 8 * kMaxStages, acc_empty = acc_full + 16;
+  const uint32_t w_full = acc_empty + 16;
+  const uint32_t tmem_slot = w_full + 8;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kMaxStages; ++i) {
+      ptx::mbar_init(full + 8 * i, 1);
+      ptx::mbar_init(empty + 8 * i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(acc_full + 8 * i, 1);
+      ptx::mbar_init(acc_empty + 8 * i, kEpiThreads);
+    }
+    ptx::mbar_init(w_full, 1);
+    ptx::mbar_fence_init();
+    ptx::prefetch_tensormap(&tm_in);
+    ptx::prefetch_tensormap(&tm_out);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, ACC_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
+  volatile int* abort_flag = &s_abort;
+
+  // Resident weights pin a CTA to one Kout tile (blockIdx.y); otherwise the CTA strides over
+  // (pixel tile, Kout tile) pairs with the Kout tiles of a pixel tile adjacent.
+  const int total_items = RESIDENT ? p.m_items : p.m_items * p.n_tiles;
+  auto item_of = [&](int i, int& n0, int& oy0, int& ox0, int& n_tile) {
+    const int w = (int)blockIdx.x + i * (int)gridDim.x;
+    if (w >= total_items) return false;
+    int m_item;
+    if (RESIDENT) {
+      m_item = w;
+      n_tile = (int)blockIdx.y;
+    } else {
+      m_item = w / p.n_tiles;
+      n_tile = w - m_item * p.n_tiles;
+    }
+    const int tx = m_item % p.tiles_x;
+    const int t2 = m_item / p.tiles_x;
+    const int ty = t2 % p.tiles_y;
+    n0 = (t2 / p.tiles_y) * p.tn;
+    oy0 = ty * p.th;
+    ox0 = tx * p.tw;
+    return true;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer ----
+    if (lane == 0) {
+      if (RESIDENT) {
+        const uint8_t* src = p.wpack + (size_t)blockIdx.y * KB * WTILE;
+        ptx::mbar_arrive_expect_tx(w_full, (uint32_t)KB * WTILE);
+        for (int i = 0; i < KB; ++i) ptx::bulk_g2s(sW + (uint32_t)i * WTILE, src + (size_t)i * WTILE, WTILE, w_full);
+      }
+      uint32_t cnt = 0;
+      bool okw = true;
+      for (int i = 0; okw; ++i) {
+        int n0, oy0, ox0, n_tile;
+        if (!item_of(i, n0, oy0, ox0, n_tile)) break;
+        const int xb = p.stride * ox0 - p.pad + p.in_off, yb = p.stride * oy0 - p.pad + p.in_off;
+        for (int tap = 0; tap < p.taps && okw; ++tap) {
+          const int r = tap / p.S, s = tap - r * p.S;
+          for (int cb = 0; cb < p.CB; ++cb, ++cnt) {
+            const uint32_t st = cnt % (uint32_t)p.stages;
+            if (!ptx::mbar_wait_abortable(empty + 8 * st, ((cnt / (uint32_t)p.stages) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
+            ptx::mbar_arrive_expect_tx(full + 8 * st, (uint32_t)stage_bytes);
+            const uint32_t dst = sRing + st * stage_bytes;
+            ptx::tma_load_4d(dst, &tm_in, cb * 64, xb + s, yb + r, n0, full + 8 * st);
+            if (!RESIDENT)
+              ptx::bulk_g2s(dst + kABytes, p.wpack + ((size_t)n_tile * KB + (size_t)tap * p.CB + cb) * WTILE, WTILE,
+                            full + 8 * st);
+          }
+        }
+      }
+      if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitProducer);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer ------
+    if (lane == 0) {
+      const uint32_t idesc = ptx::umma_idesc(128, BN, p.bf16 ? 1 : 0);
+      bool okw = true;
+      if (RESIDENT) okw = ptx::mbar_wait_abortable(w_full, 0, abort_flag);
+      uint32_t cnt = 0, acc_cnt = 0;
+      for (int i = 0; okw; ++i) {
+        int n0, oy0, ox0, n_tile;
+        if (!item_of(i, n0, oy0, ox0, n_tile)) break;
+        const uint32_t ab = acc_cnt & 1u;
+        if (!ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt >> 1) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t d = tmem_base + ab * BN;
+        for (int kb = 0; kb < KB; ++kb, ++cnt) {
+          const uint32_t st = cnt % (uint32_t)p.stages;
+          if (!ptx::mbar_wait_abortable(full + 8 * st, (cnt / (uint32_t)p.stages) & 1u, abort_flag)) { okw = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a_addr = sRing + st * stage_bytes;
+          const uint32_t a_lo = ptx::smem_desc_k128_lo(a_addr);
+          const uint32_t b_lo = ptx::smem_desc_k128_lo(RESIDENT ? sW + (uint32_t)kb * WTILE : a_addr + kABytes);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            ptx::umma_f16(d, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
+                          ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi), idesc, (kb | k4) != 0 ? 1u : 0u);
+          ptx::tc_commit(empty + 8 * st);
+        }
+        if (!okw) break;
+        ptx::tc_commit(acc_full + 8 * ab);
+        ++acc_cnt;
+      }
+      if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitMma);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue --------
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int row = quad * 32 + lane;
+    const bool elected = threadIdx.x == 64;
+    const uint32_t sw = (uint32_t)(row & 7);
+    const int slab_cols = p.out_f32 ? 32 : 64;      // 128-byte rows either way
+    const int slabs = BN / slab_cols;
+    const int esz = p.out_f32 ? 4 : 2;
+    // row of the tile -> pixel inside the tile
+    const int tj = row % p.tw, ti = (row / p.tw) % p.th, tnn = row / (p.tw * p.th);
+    uint32_t acc_cnt = 0;
+    int jglob = 0;   // slab counter for the two staging buffers
+    bool okw = true;
+    for (int i = 0; okw; ++i) {
+      int n0, oy0, ox0, n_tile;
+      if (!item_of(i, n0, oy0, ox0, n_tile)) break;
+      const uint32_t ab = acc_cnt & 1u;
+      const int nimg = n0 + tnn, oy = oy0 + ti, ox = ox0 + tj;
+      const bool valid = nimg < p.NB && oy < p.OH && ox < p.OW;
+      const size_t pix = ((size_t)nimg * p.out_rows + oy + p.out_off) * p.out_pitch + ox + p.out_off;
+      const bool got = ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt >> 1) & 1u, abort_flag);
+      if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; break; }
+      ptx::tc_fence_after();
+      for (int sl = 0; sl < slabs; ++sl, ++jglob) {
+        const uint32_t sb = (uint32_t)jglob & 1u;
+        const int ncol = n_tile * BN + sl * slab_cols;     // first column of the slab
+        // this warp's 32 accumulator columns inside the slab: 16-bit output -> columns
+        // [half*32, +32) of a 64-column slab; fp32 output -> both halves share a 32-column
+        // slab, so each warp takes 16 columns twice... keep it simple: for fp32 only half 0 works
+        // on columns [0,32) and half 1 idles through the barriers.
+        const bool active = p.out_f32 ? (half == 0) : true;
+        const int c0 = p.out_f32 ? 0 : half * 32;
+        const int n_first = ncol + c0;
+        uint32_t acc[32];
+        __syncwarp();
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + ab * BN + (uint32_t)(sl * slab_cols + c0), acc);
+        uint32_t res[2][8];
+        const bool use_res = p.residual != nullptr && valid && active && n_first + 32 <= p.Kout;
+        if (use_res) {
+          const uint8_t* rp = p.residual + (pix * (size_t)p.Kout + n_first) * 2;
+          ptx::ldg_256(rp, res[0]);
+          ptx::ldg_256(rp + 32, res[1]);
+        }
+        __syncwarp();
+        ptx::tmem_ld_wait();
+        if (sl == slabs - 1) {
+          ptx::tc_fence_before();
+          ptx::mbar_arrive(acc_empty + 8 * ab);
+        }
+        if (active) {
+          float v[32];
+          if (n_first + 32 <= p.Kout) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              float4 sc = make_float4(1.f, 1.f, 1.f, 1.f), sh = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (p.scale) sc = __ldg(reinterpret_cast<const float4*>(p.scale + n_first + e));
+              if (p.shift) sh = __ldg(reinterpret_cast<const float4*>(p.shift + n_first + e));
+              v[e] = fmaf(__uint_as_float(acc[e]), sc.x, sh.x);
+              v[e + 1] = fmaf(__uint_as_float(acc[e + 1]), sc.y, sh.y);
+              v[e + 2] = fmaf(__uint_as_float(acc[e + 2]), sc.z, sh.z);
+              v[e + 3] = fmaf(__uint_as_float(acc[e + 3]), sc.w, sh.w);
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int n = n_first + e;
+              float x = __uint_as_float(acc[e]);
+              if (n < p.Kout) {
+                if (p.scale) x *= __ldg(p.scale + n);
+                if (p.shift) x += __ldg(p.shift + n);
+              }
+              v[e] = x;
+            }
+          }
+          if (use_res) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const uint32_t w = res[e >> 3][e & 7];
+              float2 f;
+              if (p.bf16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+              else f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+              v[2 * e] += f.x;
+              v[2 * e + 1] += f.y;
+            }
+          }
+          const uint32_t srow = sStage + sb * kSlabBytes + (uint32_t)row * 128u;
+          if (p.out_f32) {
+#pragma unroll
+            for (int c4 = 0; c4 < 8; ++c4) {
+              float o[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                const float a = v[c4 * 4 + h];
+                o[h] = p.relu ? (!(a <= 0.0f) ? a : 0.0f) : a;
+              }
+              asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(srow + (((uint32_t)c4 ^ sw) << 4)), "f"(o[0]),
+                           "f"(o[1]), "f"(o[2]), "f"(o[3])
+                           : "memory");
+            }
+          } else {
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              uint32_t o[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                const float a = v[c4 * 8 + h * 2], b = v[c4 * 8 + h * 2 + 1];
+                if (p.bf16) {
+                  __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
+                  if (p.relu) x = __hmax2_nan(x, __floats2bfloat162_rn(0.f, 0.f));
+                  o[h] = *reinterpret_cast<uint32_t*>(&x);
+                } else {
+                  __half2 x = __floats2half2_rn(a, b);
+                  if (p.relu) x = __hmax2_nan(x, __floats2half2_rn(0.f, 0.f));
+                  o[h] = *reinterpret_cast<uint32_t*>(&x);
+                }
+              }
+              const uint32_t chunk = (uint32_t)(half * 4 + c4);
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(srow + ((chunk ^ sw) << 4)), "r"(o[0]), "r"(o[1]),
+                           "r"(o[2]), "r"(o[3])
+                           : "memory");
+            }
+          }
+        }
+        ptx::fence_proxy_async_smem();
+        ptx::named_bar_sync(1, kEpiThreads);
+        if (elected) {
+          if (ncol < p.Kout)
+            ptx::tma_store_4d(&tm_out, ncol, ox0 + p.out_off, oy0 + p.out_off, n0, sStage + sb * kSlabBytes);
+          ptx::bulk_commit();
+          ptx::bulk_wait_read<1>();
+        }
+        ptx::named_bar_sync(2, kEpiThreads);
+      }
+      ++acc_cnt;
+      (void)esz;
+    }
+    if (elected) ptx::bulk_wait<0>();
+    if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitEpilogue);
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tmem_dealloc(tmem_base, ACC_COLS);
+  }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  });
+  return fn;
+}
+
+// 4-D map over an activation [NB][rows][pitch][C] (C innermost), box (box_c, bx, by, bn) with
+// traversal strides (1, sx, sy, 1); 128-byte swizzle; out-of-range elements read as zero.
+bool make_map4(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esz, int C, long long pitch,
+               long long rows, long long NB, int box_c, int bx, int by, int bn, int sx, int sy) {
+  auto enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t gdim[4] = {(cuuint64_t)C, (cuuint64_t)pitch, (cuuint64_t)rows, (cuuint64_t)NB};
+  cuuint64_t gstr[3] = {(cuuint64_t)C * esz, (cuuint64_t)pitch * C * esz, (cuuint64_t)rows * pitch * C * esz};
+  cuuint32_t box[4] = {(cuuint32_t)box_c, (cuuint32_t)bx, (cuuint32_t)by, (cuuint32_t)bn};
+  cuuint32_t estr[4] = {1, (cuuint32_t)sx, (cuuint32_t)sy, 1};
+  return enc(m, dt, 4, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+         CUDA_SUCCESS;
+}
+
+constexpr size_t kSmemLimit = 227 * 1024;
+
+template <int BN, bool RESIDENT>
+cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
+  const size_t wtile = (size_t)BN * 128;
+  const int KB = p.taps * p.CB;
+  const size_t fixed = 1024 + 2 * kSlabBytes + 512;
+  const size_t stage = RESIDENT ? kABytes : kABytes + wtile;
+  const size_t wres = RESIDENT ? (size_t)KB * wtile : 0;
+  if (fixed + wres + 2 * stage > kSmemLimit) return cudaErrorInvalidConfiguration;
+  size_t st = (kSmemLimit - fixed - wres) / stage;
+  if (st > kMaxStages) st = kMaxStages;
+  p.stages = (int)st;
+  const size_t smem = fixed + wres + st * stage;
+
+  const Layout il = a.in_l, ol = a.out_l;
+  const auto dt = p.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUtensorMap tm_in, tm_out;
+  if (!make_map4(&tm_in, a.in, dt, 2, a.C, il.pitch, il.img_rows, a.N, 64, p.tw * p.stride, p.th * p.stride, p.tn,
+                 p.stride, p.stride))
+    return cudaErrorInvalidValue;
+  const bool f32 = p.out_f32 != 0;
+  if (!make_map4(&tm_out, a.out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : dt, f32 ? 4 : 2, a.Kout, ol.pitch, ol.img_rows,
+                 a.N, f32 ? 32 : 64, p.tw, p.th, p.tn, 1, 1))
+    return cudaErrorInvalidValue;
+  auto kern = tconv_kernel<BN, RESIDENT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const int sms = a.sm_count > 0 ? a.sm_count : 148;
+  dim3 grid;
+  if (RESIDENT) {
+    int gx = sms / p.n_tiles;
+    if (gx < 1) gx = 1;
+    if (gx > p.m_items) gx = p.m_items;
+    grid = dim3(gx, p.n_tiles);
+  } else {
+    const long long items = (long long)p.m_items * p.n_tiles;
+    grid = dim3((unsigned)(items < sms ? items : sms), 1);
+  }
+  kern<<<grid, kThreads, smem, stream>>>(tm_in, tm_out, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool tconv_supported(int C, int Kout, DType out_dt, long long ldo) {
+  // channels in blocks of 64; the output row pitch must be 16-byte aligned for the tensor map
+  return C % 64 == 0 && C >= 64 && ldo == Kout && (Kout * (out_dt == kF32 ? 4 : 2)) % 16 == 0;
+}
+
+// M-tile shape: tw covers the output row in as few pieces as possible.
+void tconv_tile(int N, int OH, int OW, int* tw, int* th, int* tn) {
+  int w = 128;
+  if (OW <= 8) w = 8;
+  else if (OW <= 16) w = 16;
+  else if (OW <= 32) w = 32;
+  else if (OW <= 64) w = 64;
+  else if (OW < 112) w = 128;
+  else {
+    // pick the divisor-friendly width among 32/64/128 with the least ragged waste
+    int best = 128, waste = (OW + 127) / 128 * 128 - OW;
+    for (int c : {64, 32}) {
+      const int ws = (OW + c - 1) / c * c - OW;
+      if (ws < waste) { best = c; waste = ws; }
+    }
+    w = best;
+  }
+  int h = 128 / w;
+  if (h > OH) {
+    int hh = 1;
+    while (hh * 2 <= h && hh < OH) hh *= 2;   // smallest power of two >= OH, capped at 128/w
+    h = hh;
+  }
+  *tw = w; *th = h; *tn = 128 / (w * h);
+  (void)N;
+}
+
+cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream) {
+  if (a.ab == kF32 || !tconv_supported(a.C, a.Kout, a.out_dtype, a.Kout)) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(a.in) & 15) || (reinterpret_cast<uintptr_t>(a.out) & 15) ||
+      (reinterpret_cast<uintptr_t>(a.residual) & 31) || (reinterpret_cast<uintptr_t>(a.wpack) & 15))
+    return cudaErrorMisalignedAddress;
+  TcParams p;
+  p.wpack = static_cast<const uint8_t*>(a.wpack);
+  p.scale = a.scale; p.shift = a.shift; p.residual = static_cast<const uint8_t*>(a.residual);
+  p.error_flag = a.error_flag;
+  p.Kout = a.Kout; p.CB = a.C / 64; p.taps = a.R * a.S; p.S = a.S; p.stride = a.stride; p.pad = a.pad;
+  p.in_off = a.in_l.off; p.out_off = a.out_l.off;
+  p.OH = a.OH; p.OW = a.OW; p.NB = a.N;
+  p.out_pitch = a.out_l.pitch; p.out_rows = a.out_l.img_rows;
+  tconv_tile(a.N, a.OH, a.OW, &p.tw, &p.th, &p.tn);
+  if (p.tw * a.stride > 256 || p.th * a.stride > 256) return cudaErrorInvalidConfiguration;
+  p.tiles_x = (a.OW + p.tw - 1) / p.tw;
+  p.tiles_y = (a.OH + p.th - 1) / p.th;
+  p.tiles_n = (a.N + p.tn - 1) / p.tn;
+  p.n_tiles = (a.Kout + a.bn - 1) / a.bn;
+  const long long mi = (long long)p.tiles_x * p.tiles_y * p.tiles_n;
+  if (mi <= 0 || mi * p.n_tiles > 0x7fffffffLL) return cudaErrorInvalidValue;
+  p.m_items = (int)mi;
+  p.relu = a.relu; p.bf16 = a.ab == kBF16; p.out_f32 = a.out_dtype == kF32;
+  p.stages = 0;
+  if (p.residual && p.out_f32) return cudaErrorInvalidValue;
+#define NNCV_TC(BN_, RES_) \
+  if (a.bn == BN_ && (a.resident != 0) == RES_) return launch_cfg<BN_, RES_>(a, p, stream);
+  NNCV_TC(64, true)
+  NNCV_TC(64, false)
+  NNCV_TC(128, true)
+  NNCV_TC(128, false)
+  NNCV_TC(256, false)
+#undef NNCV_TC
+  return cudaErrorInvalidConfiguration;
+}
+
+// N tile and residency: keep all weights of one Kout tile in shared memory when they fit beside
+// four A stages; otherwise stream them with the widest tile the grid can still fill.
+void tconv_pick(long long m_items, int C, int Kout, int taps, int* bn, int* resident) {
+  const size_t budget = kSmemLimit - (1024 + 2 * kSlabBytes + 512) - 4 * (size_t)kABytes;
+  const size_t kb = (size_t)taps * (C / 64);
+  for (int b : {128, 64}) {
+    if (Kout >= b && kb * b * 128 <= budget) {
+      *bn = b; *resident = 1;
+      return;
+    }
+  }
+  *resident = 0;
+  int b = Kout >= 256 ? 256 : (Kout > 64 ? 128 : 64);
+  while (b > 64 && m_items * ((Kout + b - 1) / b) < 148) b >>= 1;
+  *bn = b;
+}
+
+}  // namespace nncv_b200

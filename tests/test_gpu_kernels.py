@@ -63,12 +63,17 @@ CONV_CASES = [
     (3, 16, 9, 11, 24, 3, 1, 1),     # ragged everything
     (1, 256, 14, 14, 512, 1, 1, 0),
     (1, 512, 7, 7, 512, 3, 1, 1),
+    (3, 64, 56, 56, 128, 3, 2, 1),   # ResNet-18 layer2.0.conv1 shape
+    (3, 64, 56, 56, 128, 1, 2, 0),   # and its downsample conv
+    (5, 256, 14, 14, 512, 3, 2, 1),  # layer4.0.conv1: two images per M tile
+    (2, 128, 30, 50, 64, 1, 1, 0),   # ragged 1x1
 ]
 
 
 @pytest.mark.parametrize("case", CONV_CASES)
-@pytest.mark.parametrize("dtype", [F16, BF16, F32])
-def test_conv_epilogue(case, dtype):
+@pytest.mark.parametrize("dtype,algo", [(F16, 0), (F16, 3), (BF16, 0), (F32, 0)])
+def test_conv_epilogue(case, dtype, algo):
+    """algo 0: TMA-fed kernel where C % 64 == 0, gather kernel otherwise; algo 3: always the gather kernel."""
     n, c, h, w, k, r, stride, pad = case
     g = _rng(sum(case))
     x = g.standard_normal((n, c, h, w)).astype(np.float32)
@@ -77,7 +82,7 @@ def test_conv_epilogue(case, dtype):
     shift = (g.standard_normal(k) * 0.1).astype(np.float32)
     oh, ow = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - r) // stride + 1
     res = g.standard_normal((n, k, oh, ow)).astype(np.float32)
-    conv = G.Conv(wt, stride, pad, dtype)
+    conv = G.Conv(wt, stride, pad, dtype, algo)
     try:
         y, xr = conv.run(x, scale, shift, res, True)
     finally:
