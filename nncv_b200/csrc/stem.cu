@@ -18,7 +18,8 @@
 // The rows of the operand overlap in memory; the tensor core only does address arithmetic.
 // One filter row is therefore K = 32 (two MMAs of K = 16), a conv output row of up to 128
 // pixels is 14 MMAs of 128 x 64 x 16, and every input row is brought into shared memory once
-// (bulk async copy into a ring) and reused by the seven filter rows of four output rows.
+// (bulk async copies of row pairs into a ring) and reused by the seven filter rows of four
+// output rows.
 //
 // Roles (10 warps, persistent over (image, band of pooled rows) items):
 //   warp 0   bulk-copies input rows into the ring; weights (28 KB) are resident.
@@ -40,12 +41,27 @@ namespace {
 constexpr int kEpiWarps = 8;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kThreads = 64 + kEpiThreads;
-constexpr int kRingSlots = 16;      // input rows resident in shared memory
+constexpr int kRingSlots = 8;       // input row PAIRS (rows 2k, 2k+1) resident in shared memory
 constexpr int kAccBufs = 4;         // TMEM accumulators of 64 columns
 constexpr int kConvRing = 4;        // fp16 conv rows kept for pooling
 constexpr int kWBytes = 7 * 4096;   // packed weights: 7 filter rows x [64 x 32] fp16
 
+// Optional clock64() trace of CTA 0 (built only with -DNNCV_B200_TRACE; a tuning aid).
+#ifdef NNCV_B200_TRACE
+unsigned long long* g_stem_trace = nullptr;  // device buffer [2 roles][64 rows][8 stamps]
+#define ST_TRACE(role, idx, k)                                                            \
+  do {                                                                                    \
+    if (p.trace && blockIdx.x == 0 && (idx) < 64)                                          \
+      p.trace[((role) * 64 + (idx)) * 8 + (k)] = (unsigned long long)clock64();            \
+  } while (0)
+#else
+#define ST_TRACE(role, idx, k) \
+  do {                         \
+  } while (0)
+#endif
+
 struct StemParams {
+  unsigned long long* trace;
   const uint8_t* in_rows;   // [N][H][RW] pixels of 8 bytes
   const uint8_t* wpack;     // kWBytes
   const float* scale;
@@ -55,7 +71,7 @@ struct StemParams {
   Layout ol;
   int N, H, W, OH, OW, PH, PW;
   int row_bytes;            // RW * 8
-  int slot_bytes;           // ring slot size (>= row_bytes, covers the junk rows of the last tile)
+  int slot_bytes;           // ring slot of one row pair (covers the junk rows of the last x tile)
   int x_tiles;              // ceil(OW / 128)
   int bands, band_rows;     // pooled rows per item
   int bf16;
@@ -109,7 +125,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
   volatile int* abort_flag = &s_abort;
 
   const int total_items = p.N * p.bands;
-  // item -> image, conv rows [y0, y1], input rows [ir0, ir1]
+  // item -> image, conv rows [y0, y1], input row pairs [ir0, ir1] (pair k = rows 2k, 2k+1)
   auto item_of = [&](int i, int& n, int& p0, int& p1, int& y0, int& y1, int& ir0, int& ir1) {
     const int w = (int)blockIdx.x + i * (int)gridDim.x;
     if (w >= total_items) return false;
@@ -119,8 +135,8 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
     p1 = min(p.PH, p0 + p.band_rows);
     y0 = max(0, 2 * p0 - 1);
     y1 = min(p.OH - 1, 2 * p1 - 1);
-    ir0 = max(0, 2 * y0 - 3);
-    ir1 = min(p.H - 1, 2 * y1 + 3);
+    ir0 = max(0, 2 * y0 - 3) >> 1;          // first and last input-row PAIR of the item
+    ir1 = min(p.H - 1, 2 * y1 + 3) >> 1;
     return true;
   };
 
@@ -135,11 +151,12 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
         int n, p0, p1, y0, y1, ir0, ir1;
         if (!item_of(i, n, p0, p1, y0, y1, ir0, ir1)) break;
         const uint8_t* img = p.in_rows + (size_t)n * p.H * p.row_bytes;
-        for (int ir = ir0; ir <= ir1; ++ir, ++seq) {
+        for (int pk = ir0; pk <= ir1; ++pk, ++seq) {
           const uint32_t slot = seq % kRingSlots;
           if (!ptx::mbar_wait_abortable(empty + 8 * slot, ((seq / kRingSlots) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
-          ptx::mbar_arrive_expect_tx(full + 8 * slot, (uint32_t)p.row_bytes);
-          ptx::bulk_g2s(sRing + slot * p.slot_bytes, img + (size_t)ir * p.row_bytes, (uint32_t)p.row_bytes, full + 8 * slot);
+          const uint32_t bytes = (uint32_t)p.row_bytes * (uint32_t)min(2, p.H - 2 * pk);   // rows are contiguous
+          ptx::mbar_arrive_expect_tx(full + 8 * slot, bytes);
+          ptx::bulk_g2s(sRing + slot * p.slot_bytes, img + (size_t)(2 * pk) * p.row_bytes, bytes, full + 8 * slot);
         }
       }
       if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitProducer);
@@ -153,26 +170,39 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
       for (int i = 0; okw; ++i) {
         int n, p0, p1, y0, y1, ir0, ir1;
         if (!item_of(i, n, p0, p1, y0, y1, ir0, ir1)) break;
-        int waited_upto = ir0;     // input rows [ir0, waited_upto) are known to be in the ring
-        int released_upto = ir0;   // input rows [ir0, released_upto) were handed back
+        int waited_upto = ir0;     // pairs [ir0, waited_upto) are known to be in the ring
+        int released_upto = ir0;   // pairs [ir0, released_upto) were handed back
         for (int y = y0; y <= y1 && okw; ++y) {
-          const int need = min(ir1, 2 * y + 3);
+          const int need = min(ir1, y + 1);            // conv row y reads pairs y-2 .. y+1
           for (; waited_upto <= need; ++waited_upto) {
             const uint32_t s = seq_base + (uint32_t)(waited_upto - ir0);
             if (!ptx::mbar_wait_abortable(full + 8 * (s % kRingSlots), (s / kRingSlots) & 1u, abort_flag)) { okw = false; break; }
           }
           if (!okw) break;
+          ST_TRACE(0, acc_cnt, 5);
           ptx::tc_fence_after();
+          // shared-memory address of each filter row's input row (0 = zero padding row, skipped)
+          uint32_t row_addr[7];
+#pragma unroll
+          for (int r = 0; r < 7; ++r) {
+            const int ir = 2 * y + r - 3;
+            row_addr[r] = 0;
+            if (ir >= 0 && ir < p.H) {
+              const uint32_t s = seq_base + (uint32_t)((ir >> 1) - ir0);
+              row_addr[r] = sRing + (s % kRingSlots) * p.slot_bytes + (uint32_t)(ir & 1) * p.row_bytes;
+            }
+          }
           for (int xt = 0; xt < p.x_tiles && okw; ++xt) {
             const uint32_t ab = acc_cnt % kAccBufs;
+            ST_TRACE(0, acc_cnt, 0);
             if (!ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt / kAccBufs) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
+            ST_TRACE(0, acc_cnt, 1);
             ptx::tc_fence_after();
             uint32_t accumulate = 0;
+#pragma unroll
             for (int r = 0; r < 7; ++r) {
-              const int ir = 2 * y + r - 3;
-              if (ir < 0 || ir >= p.H) continue;   // zero padding rows contribute nothing
-              const uint32_t s = seq_base + (uint32_t)(ir - ir0);
-              const uint32_t a_addr = sRing + (s % kRingSlots) * p.slot_bytes + (uint32_t)xt * 2048u;
+              if (row_addr[r] == 0) continue;   // zero padding rows contribute nothing
+              const uint32_t a_addr = row_addr[r] + (uint32_t)xt * 2048u;
               const uint32_t b_addr = sW + (uint32_t)r * 4096u;
 #pragma unroll
               for (int k2 = 0; k2 < 2; ++k2) {
@@ -181,15 +211,18 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
                 accumulate = 1;
               }
             }
+            ST_TRACE(0, acc_cnt, 2);
             ptx::tc_commit(acc_full + 8 * ab);
+            ST_TRACE(0, acc_cnt, 3);
             ++acc_cnt;
           }
-          // input rows no later conv row of this item needs go back to the producer
-          const int new_upto = (y == y1) ? ir1 + 1 : min(ir1 + 1, 2 * y - 1);
+          // pairs no later conv row of this item reads go back to the producer
+          const int new_upto = (y == y1) ? ir1 + 1 : min(ir1 + 1, y - 1);
           for (; released_upto < new_upto; ++released_upto) {
             const uint32_t s = seq_base + (uint32_t)(released_upto - ir0);
             ptx::tc_commit(empty + 8 * (s % kRingSlots));
           }
+          ST_TRACE(0, acc_cnt - 1, 4);
         }
         seq_base += (uint32_t)(ir1 - ir0 + 1);
       }
@@ -217,13 +250,17 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
         const uint32_t crow = sConv + (uint32_t)(y % kConvRing) * crow_bytes;
         for (int xt = 0; xt < p.x_tiles; ++xt) {
           const uint32_t ab = acc_cnt % kAccBufs;
+          if (et == 0) ST_TRACE(1, acc_cnt, 0);
           const bool got = ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt / kAccBufs) & 1u, abort_flag);
+          if (et == 0) ST_TRACE(1, acc_cnt, 1);
           if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; break; }
+          if (et == 0) ST_TRACE(1, acc_cnt, 2);
           ptx::tc_fence_after();
           uint32_t acc[32];
           __syncwarp();
           ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + ab * 64 + half * 32, acc);
           ptx::tmem_ld_wait();
+          if (et == 0) ST_TRACE(1, acc_cnt, 3);
           ptx::tc_fence_before();
           ptx::mbar_arrive(acc_empty + 8 * ab);
           ++acc_cnt;
@@ -255,54 +292,49 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
           }
         }
         if (!okw) break;
+        if (et == 0) ST_TRACE(1, acc_cnt - 1, 4);
         ptx::named_bar_sync(1, kEpiThreads);   // conv row y is complete in shared memory
+        if (et == 0) ST_TRACE(1, acc_cnt - 1, 5);
         // pooled rows whose last conv row is y
         while (next_pool < p1 && min(2 * next_pool + 1, p.OH - 1) <= y) {
           const int pr = next_pool++;
-          const int ya = max(0, 2 * pr - 1), yb = min(p.OH - 1, 2 * pr + 1);
+          // Clamped window: a tap outside the map is replaced by its nearest valid neighbour, which
+          // is already in the window, so the maximum equals the one over the -inf padded map.
+          const uint32_t r0 = sConv + (uint32_t)(max(0, 2 * pr - 1) % kConvRing) * crow_bytes;
+          const uint32_t r1 = sConv + (uint32_t)((2 * pr) % kConvRing) * crow_bytes;
+          const uint32_t r2 = sConv + (uint32_t)(min(p.OH - 1, 2 * pr + 1) % kConvRing) * crow_bytes;
           uint16_t* orow = p.out + ((size_t)((size_t)n * p.ol.img_rows + pr + p.ol.off) * p.ol.pitch + p.ol.off) * 64;
           for (int u = et; u < p.PW * 8; u += kEpiThreads) {
             const int px = u >> 3, c = u & 7;
-            const int xa = max(0, 2 * px - 1), xb = min(p.OW - 1, 2 * px + 1);
-            uint32_t m[4];
-            bool first = true;
-            for (int yy = ya; yy <= yb; ++yy) {
-              const uint32_t cr = sConv + (uint32_t)(yy % kConvRing) * crow_bytes;
-              for (int xx = xa; xx <= xb; ++xx) {
-                uint32_t v[4];
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
-                             : "r"(cr + (uint32_t)xx * 128u + (((uint32_t)c ^ (uint32_t)(xx & 7)) << 4)));
-                if (first) {
+            const int xs[3] = {max(0, 2 * px - 1), 2 * px, min(p.OW - 1, 2 * px + 1)};
+            uint32_t v[9][4];
 #pragma unroll
-                  for (int h = 0; h < 4; ++h) m[h] = v[h];
-                  first = false;
-                } else {
-#pragma unroll
-                  for (int h = 0; h < 4; ++h) {
-                    if (p.bf16) {
-                      __nv_bfloat162 r = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&m[h]), *reinterpret_cast<__nv_bfloat162*>(&v[h]));
-                      m[h] = *reinterpret_cast<uint32_t*>(&r);
-                    } else {
-                      __half2 r = __hmax2_nan(*reinterpret_cast<__half2*>(&m[h]), *reinterpret_cast<__half2*>(&v[h]));
-                      m[h] = *reinterpret_cast<uint32_t*>(&r);
-                    }
-                  }
-                }
-              }
+            for (int j = 0; j < 3; ++j) {
+              const uint32_t off = (uint32_t)xs[j] * 128u + (((uint32_t)c ^ (uint32_t)(xs[j] & 7)) << 4);
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[j][0]), "=r"(v[j][1]), "=r"(v[j][2]), "=r"(v[j][3]) : "r"(r0 + off));
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[3 + j][0]), "=r"(v[3 + j][1]), "=r"(v[3 + j][2]), "=r"(v[3 + j][3]) : "r"(r1 + off));
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[6 + j][0]), "=r"(v[6 + j][1]), "=r"(v[6 + j][2]), "=r"(v[6 + j][3]) : "r"(r2 + off));
             }
+            uint32_t m[4];
 #pragma unroll
-            for (int h = 0; h < 4; ++h) {   // ReLU after the max (NaN passes)
+            for (int h = 0; h < 4; ++h) {
               if (p.bf16) {
-                __nv_bfloat162 r = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&m[h]), __floats2bfloat162_rn(0.f, 0.f));
+                __nv_bfloat162 r = *reinterpret_cast<__nv_bfloat162*>(&v[0][h]);
+#pragma unroll
+                for (int j = 1; j < 9; ++j) r = __hmax2_nan(r, *reinterpret_cast<__nv_bfloat162*>(&v[j][h]));
+                r = __hmax2_nan(r, __floats2bfloat162_rn(0.f, 0.f));   // ReLU after the max (NaN passes)
                 m[h] = *reinterpret_cast<uint32_t*>(&r);
               } else {
-                __half2 r = __hmax2_nan(*reinterpret_cast<__half2*>(&m[h]), __floats2half2_rn(0.f, 0.f));
+                __half2 r = *reinterpret_cast<__half2*>(&v[0][h]);
+#pragma unroll
+                for (int j = 1; j < 9; ++j) r = __hmax2_nan(r, *reinterpret_cast<__half2*>(&v[j][h]));
+                r = __hmax2_nan(r, __floats2half2_rn(0.f, 0.f));
                 m[h] = *reinterpret_cast<uint32_t*>(&r);
               }
             }
             *reinterpret_cast<uint4*>(orow + (size_t)px * 64 + c * 8) = make_uint4(m[0], m[1], m[2], m[3]);
           }
+          if (et == 0) ST_TRACE(1, acc_cnt - 1, 6);
         }
       }
       // the next item starts writing the conv ring only after everyone has finished pooling
@@ -373,6 +405,10 @@ cudaError_t by_dt(DType t, F&& f) {
 
 }  // namespace
 
+#ifdef NNCV_B200_TRACE
+extern "C" void nncv_b200_debug_set_stem_trace(unsigned long long* dev_buf) { g_stem_trace = dev_buf; }
+#endif
+
 int stem_row_pixels(int W) { return (4 + W + 4 + 1) & ~1; }
 size_t stem_rows_bytes(int N, int H, int W) { return (size_t)N * H * stem_row_pixels(W) * 8; }
 size_t stem_wpack_bytes() { return kWBytes; }
@@ -413,6 +449,11 @@ cudaError_t launch_pack_stem_weights(const void* w, DType w_dt, void* dst, DType
 cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream) {
   if (a.ab == kF32 || a.N <= 0 || a.H < 7 || a.W < 7) return cudaErrorInvalidValue;
   StemParams p;
+#ifdef NNCV_B200_TRACE
+  p.trace = g_stem_trace;
+#else
+  p.trace = nullptr;
+#endif
   p.in_rows = static_cast<const uint8_t*>(a.in_rows);
   p.wpack = static_cast<const uint8_t*>(a.wpack);
   p.scale = a.scale; p.shift = a.shift;
@@ -424,10 +465,11 @@ cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream) {
   p.ol = a.out_l.pitch ? a.out_l : dense_layout(p.PH, p.PW);
   p.row_bytes = stem_row_pixels(a.W) * 8;
   p.x_tiles = (p.OW + 127) / 128;
-  // the last x tile's junk rows read up to chunk (x_tiles*128 - 1) + 3 of the slot
-  int slot = p.x_tiles * 2048 + 64;
-  if (slot < p.row_bytes) slot = p.row_bytes;
-  p.slot_bytes = (slot + 15) & ~15;
+  // a slot holds a pair of rows; the junk rows of the last x tile read up to byte
+  // x_tiles * 2048 + 64 past the start of a row
+  int slot = p.row_bytes + p.x_tiles * 2048 + 64;
+  if (slot < 2 * p.row_bytes) slot = 2 * p.row_bytes;
+  p.slot_bytes = (slot + 127) & ~127;
   p.bf16 = a.ab == kBF16;
   const int sms = a.sm_count > 0 ? a.sm_count : 148;
   // bands: enough items to fill the SMs several times over, at least 4 pooled rows each

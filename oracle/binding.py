@@ -32,6 +32,8 @@ def oracle() -> ctypes.CDLL:
             build()
         L = ctypes.CDLL(ORACLE_SO)
         L.nncv_oracle_num_threads.restype = c_int
+        L.nncv_oracle_set_threads.argtypes = [c_int]
+        L.nncv_oracle_set_threads.restype = None
         L.nncv_oracle_conv2d_nchw_fchw.argtypes = [_f32p, _f32p, _f32p] + [c_int] * 10
         L.nncv_oracle_conv2d_nchw_fchw.restype = None
         L.nncv_oracle_batchnorm.argtypes = [_f32p] * 6 + [c_int, c_int, c_long]
@@ -127,6 +129,16 @@ def resnet_forward(depth: int, x, blob, acc64=False) -> np.ndarray:
 
 def num_threads() -> int:
     return oracle().nncv_oracle_num_threads()
+
+
+def use_all_cores() -> int:
+    """Use every host core the process may run on (overrides an exported OMP_NUM_THREADS)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    oracle().nncv_oracle_set_threads(n)
+    return num_threads()
 
 
 def ref_lib():

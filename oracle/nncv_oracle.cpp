@@ -92,6 +92,16 @@ void conv_core(const float* xp, const float* w, float* y, int N, int C, int Hp, 
 
 extern "C" {
 
+// Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU baseline is meant to use every
+// host core, so the thread count can be set explicitly.
+void nncv_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int nncv_oracle_num_threads() {
 #ifdef _OPENMP
   return omp_get_max_threads();
