@@ -152,6 +152,24 @@ int nncv_flat_array_write(const char* path, size_t n, const nncv_memref_indexer*
 int nncv_b200_matmul(const void* A, const void* B, void* C, int M, int N, int K, int ab_dtype,
                      int c_dtype, const float* bias, int relu, void* stream);
 
+/* The same matmul for callers that must never allocate device memory: a server that gave all
+ * device memory to its own pool, or a latency-bound loop that cannot take the device-wide
+ * synchronisation a cudaMalloc implies.  The repacked B lives in a fixed array inside the library
+ * image (NNCV_B200_NOALLOC_MAX_PACKED_BYTES plus a 256-byte header; every GPU that loads the
+ * library holds it until the process exits), so this call makes no cudaMalloc, cudaFree or other
+ * allocating call.  16-bit operands only (F16/BF16), K %% 8 == 0.  Problems whose packed B
+ * (about N*K*2 bytes, N and K rounded up to the tile) exceeds the array are rejected with
+ * NNCV_B200_EINVAL and a message; use nncv_b200_matmul for those.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current) and loads the kernels; make that first call outside any stream capture.
+ * All calls share the one array, which keeps the previous call's contents: the status word in it
+ * is cleared and the packed image rewritten in full at the start of every call, and two calls
+ * that overlap on the GPU (different streams, no dependency) race on it -- order them.
+ * No counterpart in the reference, which never uses a device. */
+#define NNCV_B200_NOALLOC_MAX_PACKED_BYTES (8u << 20)
+int nncv_b200_matmul_noalloc(const void* A, const void* B, void* C, int M, int N, int K, int ab_dtype,
+                             int c_dtype, const float* bias, int relu, void* stream);
+
 /* linalg.conv_2d_nchw_fchw (tests/Nets/Res18.mlir:125) + folded batch-norm / residual / ReLU
  * epilogue, on NHWC activations.  Weights are prepared once into a plan. */
 typedef struct nncv_b200_conv nncv_b200_conv;

@@ -23,7 +23,7 @@ EXPORTS = [
     "nncv_flat_array_read", "nncv_flat_array_free", "nncv_flat_array_count",
     "nncv_flat_array_indexer", "nncv_flat_array_data", "nncv_flat_array_wrapped",
     "nncv_flat_array_write",
-    "nncv_b200_matmul", "nncv_b200_conv_create", "nncv_b200_conv_destroy", "nncv_b200_conv_run",
+    "nncv_b200_matmul", "nncv_b200_matmul_noalloc", "nncv_b200_conv_create", "nncv_b200_conv_destroy", "nncv_b200_conv_run",
     "nncv_b200_conv_set_tile", "nncv_b200_stem_pool",
     "nncv_b200_maxpool_nhwc", "nncv_b200_avgpool_nhwc", "nncv_b200_nchw_to_nhwc", "nncv_b200_bn_fold",
 ]
@@ -81,6 +81,7 @@ def lib() -> ctypes.CDLL:
     L.nncv_flat_array_write.argtypes = [c_char_p, c_size_t, POINTER(MemRefIndexer), POINTER(c_void_p)]
     L.nncv_b200_matmul.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                    c_void_p, c_int, c_void_p]
+    L.nncv_b200_matmul_noalloc.argtypes = L.nncv_b200_matmul.argtypes
     L.nncv_b200_conv_create.argtypes = [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]
     L.nncv_b200_conv_create.restype = c_void_p
     L.nncv_b200_conv_destroy.argtypes = [c_void_p]

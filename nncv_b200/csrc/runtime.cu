@@ -60,6 +60,24 @@ int ok() {
     CU(call);                                                                             \
   } while (0)
 
+}  // namespace
+
+// Status plumbing for the other translation units of the library.
+namespace nncv_b200 {
+int internal_fail(int code, const char* fmt, ...) {
+  g_status = code;
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_msg, sizeof(g_msg), fmt, ap);
+  va_end(ap);
+  return code;
+}
+int internal_ok() { return ok(); }
+std::mutex& internal_mutex() { return g_mutex; }
+}  // namespace nncv_b200
+
+namespace {
+
 // =====================================================================================
 // device context
 // =====================================================================================
