@@ -566,6 +566,14 @@ Conv3x3Config conv3x3_pick(int N, int H, int W, int C, int Kout, int has_res) {
   } else {
     c.resident = 0; c.bn = 256; c.mt = 2;
   }
+  // Small batches: shrink the tile until the persistent grid has an item for every SM.
+  const long long T = (long long)N * (H + 1) * (W + 1);
+  auto items = [&]() { return ((T + c.mt * 128 - 1) / (c.mt * 128)) * (c.resident ? 1 : Kout / c.bn); };
+  while (items() < 148) {
+    if (c.mt > 1) c.mt >>= 1;
+    else if (!c.resident && c.bn > 64) c.bn >>= 1;
+    else break;
+  }
   return c;
 }
 
