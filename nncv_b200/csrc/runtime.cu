@@ -86,6 +86,8 @@ struct Device {
   int id = -1;
   cudaStream_t stream = nullptr;
   int* error_flag = nullptr;   // device
+  cudaStream_t copy_stream = nullptr;  // host->device copies of a split batch
+  cudaEvent_t copy_done[3] = {nullptr, nullptr, nullptr};
   cudaStream_t user_stream = nullptr;  // stream _mlir_ciface_forward runs on when set
   bool user_stream_set = false;
   int sm_count = 148;
@@ -715,16 +717,37 @@ int forward_impl(nncv_memref2* dst, nncv_memref4* src, void* params, cudaStream_
   if (device_only && (!src_dev || !dst_dev))
     return fail(NNCV_B200_EINVAL, "nncv_b200_forward_device needs device-resident src and dst");
   cudaStream_t st = device_only ? user_stream : (g_dev.user_stream_set ? g_dev.user_stream : g_dev.stream);
-  if ((rc = ensure_workspace(m, N, H, W))) return rc;
-  const void* src_d = sp;
-  if (!src_dev) {
-    CU(cudaMemcpyAsync(m.in_stage.p, sp, (size_t)N * 3 * H * W * ew, cudaMemcpyHostToDevice, st));
-    src_d = m.in_stage.p;
+  const size_t img_bytes = (size_t)3 * H * W * ew;
+  // Host input, large batch: run the batch as two halves so that the host->device copy of the
+  // second half overlaps the forward of the first (copies on their own stream, ordered by events).
+  const int chunks = (!src_dev && !device_only && N >= 128 && N % 2 == 0) ? 2 : 1;
+  const int Nc = N / chunks;
+  if ((rc = ensure_workspace(m, Nc, H, W))) return rc;
+  if (!src_dev && (rc = m.in_stage.reserve((size_t)N * img_bytes))) return rc;
+  if (chunks > 1) {
+    if (!g_dev.copy_stream) {
+      CU(cudaStreamCreateWithFlags(&g_dev.copy_stream, cudaStreamNonBlocking));
+      for (auto& e : g_dev.copy_done) CU(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    // the copy stream must not overwrite the staging buffer before earlier work on `st` has read it
+    CU(cudaEventRecord(g_dev.copy_done[2], st));
+    CU(cudaStreamWaitEvent(g_dev.copy_stream, g_dev.copy_done[2], 0));
+    for (int c = 0; c < chunks; ++c) {
+      CU(cudaMemcpyAsync((char*)m.in_stage.p + (size_t)c * Nc * img_bytes, sp + (size_t)c * Nc * img_bytes,
+                         (size_t)Nc * img_bytes, cudaMemcpyHostToDevice, g_dev.copy_stream));
+      CU(cudaEventRecord(g_dev.copy_done[c], g_dev.copy_stream));
+    }
+  } else if (!src_dev) {
+    CU(cudaMemcpyAsync(m.in_stage.p, sp, (size_t)N * img_bytes, cudaMemcpyHostToDevice, st));
   }
-  if ((rc = model_forward_device(m, src_d, N, H, W, st))) return rc;
-  const void* logits = m.io_dt == kF32 ? m.logits32.p : m.logits_io.p;
-  CU(cudaMemcpy2DAsync(dp, (size_t)dst->strides[0] * ew, logits, 1000 * ew, 1000 * ew, (size_t)N,
-                       dst_dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, st));
+  for (int c = 0; c < chunks; ++c) {
+    const void* src_d = src_dev ? (const void*)sp : (const void*)((char*)m.in_stage.p + (size_t)c * Nc * img_bytes);
+    if (chunks > 1) CU(cudaStreamWaitEvent(st, g_dev.copy_done[c], 0));
+    if ((rc = model_forward_device(m, src_d, Nc, H, W, st))) return rc;
+    const void* logits = m.io_dt == kF32 ? m.logits32.p : m.logits_io.p;
+    CU(cudaMemcpy2DAsync(dp + (size_t)c * Nc * dst->strides[0] * ew, (size_t)dst->strides[0] * ew, logits, 1000 * ew,
+                         1000 * ew, (size_t)Nc, dst_dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, st));
+  }
   if (device_only) return ok();
   CU(cudaStreamSynchronize(st));
   if ((rc = check_kernel_status())) return rc;

@@ -1,0 +1,129 @@
+"""Kernel and network sweeps over the benchmark configs other than the headline one.
+
+    python -m nncv_b200.sweeps [gemm] [conv] [nets]
+
+  gemm : M=N=K in {512,1024,2048,4096}, fp16 in / fp32 accumulate (fp16 and fp32 C), optional fused
+         bias + ReLU, and the fp32 CUDA-core path (config 1).
+  conv : 3x3 stride-1 pad-1, batch 32, (C=K, H=W) in {(64,64),(128,32),(256,16),(512,8)}, fp16, fused
+         scale/shift + ReLU (config 2), for the shifted-view kernel and the TMA-fed per-tap kernel.
+  nets : ResNet-18 fp32 N=1 @256 (config 0), ResNet-50 fp16 N=512 @224 (config 4), device-resident.
+One JSON line per measurement; times are CUDA-event medians on the launching stream with an L2 flush
+(256 MiB fill) before every timed call.  Torch only owns the device memory.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import sys
+
+import numpy as np
+import torch
+
+from . import runtime as rt
+from ._lib import BF16, F16, F32, check, lib
+
+PEAK_TF = 1644.0
+_flush = None
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _time(fn, reps=7):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
+    fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        _flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return sorted(ts)[len(ts) // 2]
+
+
+def gemm():
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for n in (512, 1024, 2048, 4096):
+        for ab, cdt, epi in ((F16, F32, False), (F16, F16, False), (F16, F16, True), (F32, F32, False)):
+            tdt = torch.float16 if ab == F16 else torch.float32
+            A = (torch.rand((n, n), device="cuda") * 2 - 1).to(tdt)
+            B = (torch.rand((n, n), device="cuda") * 2 - 1).to(tdt)
+            C = torch.empty((n, n), device="cuda", dtype=torch.float16 if cdt == F16 else torch.float32)
+            bias = torch.randn(n, device="cuda") if epi else None
+            ms = _time(lambda: check(lib().nncv_b200_matmul(_p(A), _p(B), _p(C), n, n, n, ab, cdt, _p(bias), int(epi), st)))
+            tf = 2.0 * n ** 3 / ms / 1e9
+            print(json.dumps({"sweep": "gemm", "M=N=K": n, "ab": "f16" if ab == F16 else "f32",
+                              "c": "f16" if cdt == F16 else "f32", "bias_relu": epi, "ms": round(ms, 4),
+                              "tflops": round(tf, 1), "frac_of_peak": round(tf / PEAK_TF, 3),
+                              "note": "includes repacking B[K,N] into K-major tiles"}), flush=True)
+
+
+def conv():
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    n = 32
+    for c, hw in ((64, 64), (128, 32), (256, 16), (512, 8)):
+        w = (torch.randn((c, c, 3, 3)) * (2.0 / (9 * c)) ** 0.5).numpy().astype(np.float32)
+        X = torch.randn((n, hw, hw, c), device="cuda", dtype=torch.float16)
+        Y = torch.empty((n, hw, hw, c), device="cuda", dtype=torch.float16)
+        sc = torch.rand(c, device="cuda") + 0.5
+        sh = torch.randn(c, device="cuda") * 0.1
+        for algo, name in ((2, "shifted-view conv3x3"), (0, "per-tap TMA tconv")):
+            h = lib().nncv_b200_conv_create(w.ctypes.data, F32, c, c, 3, 3, 1, 1, F16, algo)
+            assert h
+            call = lambda: check(lib().nncv_b200_conv_run(h, _p(X), _p(Y), n, hw, hw, _p(sc), _p(sh), None, 1, st))
+            call()
+            torch.cuda.synchronize()
+            rt.profile(True)
+            for _ in range(5):
+                _flush_fill()
+                call()
+            torch.cuda.synchronize()
+            recs = [r for r in rt.profile_records() if r["kind"] in (2, 5)]
+            rt.profile(False)
+            ms = sorted(r["ms"] for r in recs)[len(recs) // 2]
+            tf = recs[0]["flops"] / ms / 1e9
+            print(json.dumps({"sweep": "conv3x3", "N": n, "C=K": c, "H=W": hw, "kernel": name, "us": round(ms * 1e3, 1),
+                              "tflops_direct_conv": round(tf, 1), "frac_of_peak": round(tf / PEAK_TF, 3)}), flush=True)
+            lib().nncv_b200_conv_destroy(h)
+
+
+def _flush_fill():
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, device="cuda", dtype=torch.uint8)
+    _flush.zero_()
+
+
+def nets():
+    from .netspec import conv_macs
+    from .split_params import random_state_dict, to_flat_array
+    s = torch.cuda.current_stream().cuda_stream
+    for depth, dt, n, hw, name in ((18, F32, 1, 256, "R18 fp32 N=1 @256"), (18, F16, 256, 224, "R18 fp16 N=256 @224"),
+                                   (50, F16, 512, 224, "R50 fp16 N=512 @224")):
+        np_dt = np.float32 if dt == F32 else np.float16
+        blob = to_flat_array(depth, random_state_dict(depth, 0), np_dt).blob()
+        rt.load_blob(f"resnet{depth}", blob, dt)
+        x = torch.randn((n, 3, hw, hw), device="cuda").to(torch.float32 if dt == F32 else torch.float16)
+        out = torch.empty((n, 1000), device="cuda", dtype=x.dtype)
+        ms = _time(lambda: rt.forward_device(out, x, s), reps=5)
+        gf = 2.0 * conv_macs(depth, hw, hw) * n / 1e9
+        print(json.dumps({"sweep": "nets", "config": name, "ms": round(ms, 3), "images_per_s": round(n / ms * 1e3, 1),
+                          "tflops": round(gf / ms, 1)}), flush=True)
+        rt.unload()
+
+
+if __name__ == "__main__":
+    which = sys.argv[1:] or ["gemm", "conv", "nets"]
+    if "gemm" in which:
+        gemm()
+    if "conv" in which:
+        conv()
+    if "nets" in which:
+        nets()
