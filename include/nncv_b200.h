@@ -120,7 +120,7 @@ long long nncv_b200_launch_count(void);
 typedef struct {
   int kind;      /* 0 tcgen05 implicit GEMM (gathered A), 1 fp32 CUDA-core conv, 2 tcgen05 3x3 shifted-view
                     conv, 3 memory-bound helper, 4 fused stem conv + max-pool, 5 tcgen05 implicit GEMM
-                    (TMA-fed A) */
+                    (TMA-fed A), 6 Winograd F(2x2,3x3) (all three stages) */
   int M, N, K;   /* GEMM view of the launch (helpers: elements, channels, 0) */
   int bn;        /* N tile (kind 0); helper id (kind 3) */
   double flops;  /* algorithmic: 2*M*N*K with K = C*R*S (direct-convolution count) */
@@ -176,7 +176,9 @@ typedef struct nncv_b200_conv nncv_b200_conv;
 /* weights: host or device [Kout,C,R,S] of w_dtype.  dtype: activation type (F16/BF16 -> tcgen05
  * implicit GEMM, F32 -> CUDA-core).  algo: 0 = implicit GEMM, A operand fetched by strided TMA
  * copies when C %% 64 == 0 and by a cp.async gather otherwise (any shape), 3 = always the gather
- * kernel, 2 = 3x3 stride-1 pad-1 implicit GEMM whose nine taps are shifted views of one
+ * kernel, 1 = Winograd F(2x2,3x3) in three stages (input transform, 16 tcgen05 GEMMs, output
+ * transform; same shape limits as algo 2; the counterpart of nncv's disabled F(6x6,3x3) rewrite,
+ * OptimizeConv2dUsingWinograd.cpp:173-284), 2 = 3x3 stride-1 pad-1 implicit GEMM whose nine taps are shifted views of one
  * shared-memory halo tile (16-bit types, C and Kout multiples of 64).  Activation channel count is C rounded up to 8 (F16/BF16) or 4 (F32). */
 nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout, int C, int R,
                                       int S, int stride, int pad, int dtype, int algo);

@@ -106,6 +106,14 @@ void tconv_tile(int N, int OH, int OW, int* tw, int* th, int* tn);
 void tconv_pick(long long m_items, int C, int Kout, int taps, int* bn, int* resident);
 cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream);
 
+// ---- Winograd F(2x2,3x3), three stages (filter transform once; input transform, 16 GEMMs, output
+// transform per call); dense NHWC, 16-bit types ----------------------------------------------------
+cudaError_t launch_wino_filter(const void* w, DType w_dt, long long sn, long long sc, long long stap, int K, int C,
+                               void* U, DType dt, cudaStream_t st);
+cudaError_t launch_wino_input(const void* x, void* V, DType dt, int N, int H, int W, int C, cudaStream_t st);
+cudaError_t launch_wino_output(const float* M, const float* scale, const float* shift, const void* res, void* y,
+                               DType dt, int N, int H, int W, int K, int relu, cudaStream_t st);
+
 // ---- ResNet stem: 7x7 s2 p3 conv (3 -> 64) + scale/shift + ReLU + 3x3 s2 p1 max-pool, fused ---
 struct StemArgs {
   const void* in_rows = nullptr;   // rows written by launch_nchw_to_stem_rows

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <array>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -146,6 +147,7 @@ struct ProfRec {
   cudaEvent_t e0, e1;
   float ms;
 };
+bool g_autotune = getenv("NNCV_B200_AUTOTUNE") ? atoi(getenv("NNCV_B200_AUTOTUNE")) != 0 : true;
 bool g_force_gather = false;  // tuning/test hook: route algo-0 convs through the gather kernel
 bool g_prof_on = false;
 std::vector<ProfRec> g_prof;
@@ -211,6 +213,11 @@ struct DevBuf {
 // =====================================================================================
 // convolution plan
 // =====================================================================================
+struct ConvChoice {
+  int kernel = 5;  // 2 shifted-view conv3x3, 5 per-tap TMA kernel
+  int bn = 64, mt = 1, resident = 0;
+};
+
 struct nncv_b200_conv {
   int Kout = 0, C = 0, R = 1, S = 1, stride = 1, pad = 0;
   int Cpad = 0;
@@ -225,7 +232,11 @@ struct nncv_b200_conv {
   DevBuf w_f32;                                    // fp32 path: [Kout][R*S][Cpad]
   bool w_f32_ready = false;
   DevBuf sp_in, sp_out, sp_res;                    // standalone algo 2: shared-pad copies
+  DevBuf wino_U, wino_V, wino_M;                   // algo 1: transformed filters / input / products
+  std::vector<std::unique_ptr<DevBuf>> wino_w;     // algo 1: packed U per transform position
+  int wino_bn = 0, wino_resident = 0;
   bool force_gather = false;                       // algo 3: the cp.async gather kernel even where TMA would do
+  std::map<std::array<int, 5>, ConvChoice> tuned;  // measured best kernel/tile per (N, H, W, residual, out type)
   Conv3x3Config cfg3{0, 0, 0};                     // algo 2: forced tile configuration (bn 0 = auto)
 };
 
@@ -281,44 +292,97 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
   const double bytes = 2.0 * ((double)N * H * W * c->C + (double)c->Kout * c->C * c->R * c->S +
                               (double)M * c->Kout * (residual ? 2 : 1)) +
                        (out_dt == kF32 ? 2.0 * M * c->Kout : 0.0);
-  if (c->algo == 2) {
-    // shifted-view 3x3: shared-pad layouts on both sides
-    if (in_l.off != 1 || out_l.off != 1 || out_dt != c->dtype || ldo != c->Kout)
-      return fail(NNCV_B200_EINVAL, "conv3x3: needs shared-pad NHWC input and output");
-    const Conv3x3Config cfg = c->cfg3.bn ? c->cfg3 : conv3x3_pick(N, H, W, c->Cpad, c->Kout, residual != nullptr);
-    const void* wpack = nullptr;
-    int rc = conv_prepare(c, cfg.bn, st, &wpack);
-    if (rc) return rc;
-    Conv3x3Args a;
-    a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
-    a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.Kout = c->Kout;
-    a.bn = cfg.bn; a.mt = cfg.mt; a.resident = cfg.resident; a.ab = c->dtype; a.relu = relu;
-    a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
-    prof_begin(2, flops, bytes, (int)M, c->Kout, c->C * 9, cfg.bn * 1000 + cfg.mt * 10 + cfg.resident, st);
-    LAUNCH(launch_conv3x3(a, st));
-    prof_end(st);
-    return NNCV_B200_OK;
-  }
-  if (c->algo == 0 && !g_force_gather && !c->force_gather && tconv_supported(c->Cpad, c->Kout, out_dt, ldo) &&
-      (out_dt == kF32 ? 32 : 64) <= c->Kout) {
-    // TMA-fed persistent kernel: no thread-side gather
-    int tw, th, tn, bn, resident;
-    tconv_tile(N, OH, OW, &tw, &th, &tn);
-    const long long m_items = (long long)((OW + tw - 1) / tw) * ((OH + th - 1) / th) * ((N + tn - 1) / tn);
-    tconv_pick(m_items, c->Cpad, c->Kout, c->R * c->S, &bn, &resident);
-    if (c->cfg3.bn) { bn = c->cfg3.bn; resident = c->cfg3.resident; }
-    const void* wpack = nullptr;
-    int rc = conv_prepare(c, bn, st, &wpack);
-    if (rc) return rc;
-    TconvArgs a;
-    a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
-    a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
-    a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.in_l = in_l; a.out_l = out_l;
-    a.bn = bn; a.resident = resident; a.ab = c->dtype; a.out_dtype = out_dt; a.relu = relu;
-    a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
-    prof_begin(5, flops, bytes, (int)M, c->Kout, c->C * c->R * c->S, bn * 10 + resident, st);
-    LAUNCH(launch_tconv(a, st));
-    prof_end(st);
+  // ---- tensor-core kernels fed by TMA: the shifted-view 3x3 kernel (needs shared-pad layouts) and
+  // the per-tap kernel.  Which one, and with which tile, is timed once per (plan, shape).
+  const bool sv_ok = c->algo == 2 && in_l.off == 1 && out_l.off == 1 && out_dt == c->dtype && ldo == c->Kout;
+  if (c->algo == 2 && !sv_ok) return fail(NNCV_B200_EINVAL, "conv3x3: needs shared-pad NHWC input and output");
+  const bool tc_ok = !g_force_gather && !c->force_gather && tconv_supported(c->Cpad, c->Kout, out_dt, ldo) &&
+                     (out_dt == kF32 ? 32 : 64) <= c->Kout;
+  if (sv_ok || (c->algo == 0 && tc_ok)) {
+    auto launch_choice = [&](const ConvChoice& ch, bool profile) -> int {
+      const void* wpack = nullptr;
+      int rc = conv_prepare(c, ch.bn, st, &wpack);
+      if (rc) return rc;
+      if (ch.kernel == 2) {
+        Conv3x3Args a;
+        a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
+        a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.Kout = c->Kout;
+        a.bn = ch.bn; a.mt = ch.mt; a.resident = ch.resident; a.ab = c->dtype; a.relu = relu;
+        a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
+        if (profile) prof_begin(2, flops, bytes, (int)M, c->Kout, c->C * 9, ch.bn * 1000 + ch.mt * 10 + ch.resident, st);
+        ++g_launches;
+        const cudaError_t e = launch_conv3x3(a, st);
+        if (profile) prof_end(st);
+        return e == cudaSuccess ? 0 : -1;
+      }
+      TconvArgs a;
+      a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
+      a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
+      a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.in_l = in_l; a.out_l = out_l;
+      a.bn = ch.bn; a.resident = ch.resident; a.ab = c->dtype; a.out_dtype = out_dt; a.relu = relu;
+      a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
+      if (profile) prof_begin(5, flops, bytes, (int)M, c->Kout, c->C * c->R * c->S, ch.bn * 10 + ch.resident, st);
+      ++g_launches;
+      const cudaError_t e = launch_tconv(a, st);
+      if (profile) prof_end(st);
+      return e == cudaSuccess ? 0 : -1;
+    };
+    // built-in choice
+    ConvChoice ch;
+    if (sv_ok) {
+      const Conv3x3Config cfg = conv3x3_pick(N, H, W, c->Cpad, c->Kout, residual != nullptr);
+      ch = ConvChoice{2, cfg.bn, cfg.mt, cfg.resident};
+    } else {
+      int tw, th, tn, bn, resident;
+      tconv_tile(N, OH, OW, &tw, &th, &tn);
+      const long long m_items = (long long)((OW + tw - 1) / tw) * ((OH + th - 1) / th) * ((N + tn - 1) / tn);
+      tconv_pick(m_items, c->Cpad, c->Kout, c->R * c->S, &bn, &resident);
+      ch = ConvChoice{5, bn, 1, resident};
+    }
+    if (c->cfg3.bn) {
+      ch.bn = c->cfg3.bn; ch.mt = c->cfg3.mt > 0 ? c->cfg3.mt : 1; ch.resident = c->cfg3.resident;
+    } else if (g_autotune) {
+      const std::array<int, 5> key{N, H, W, residual ? 1 : 0, (int)out_dt};
+      auto it = c->tuned.find(key);
+      if (it == c->tuned.end()) {
+        // time every candidate once per shape (results are identical, each run overwrites `out`)
+        std::vector<ConvChoice> cand;
+        if (sv_ok) {
+          for (int mt : {1, 2}) cand.push_back(ConvChoice{2, 64, mt, 1});
+          for (int bn : {64, 128, 256})
+            for (int mt : {1, 2, 4})
+              if (c->Kout % bn == 0 && bn * mt <= 512) cand.push_back(ConvChoice{2, bn, mt, 0});
+        }
+        if (tc_ok) {
+          for (int bn : {64, 128}) cand.push_back(ConvChoice{5, bn, 1, 1});
+          for (int bn : {64, 128, 256})
+            if (bn <= c->Kout || bn == 64) cand.push_back(ConvChoice{5, bn, 1, 0});
+        }
+        cudaEvent_t e0, e1;
+        CU(cudaEventCreate(&e0));
+        CU(cudaEventCreate(&e1));
+        float best = 1e30f;
+        ConvChoice best_ch = ch;
+        for (const ConvChoice& k : cand) {
+          cudaGetLastError();
+          if (launch_choice(k, false) != 0) { cudaGetLastError(); continue; }   // does not fit: skip
+          cudaEventRecord(e0, st);
+          bool okl = true;
+          for (int rep = 0; rep < 3 && okl; ++rep) okl = launch_choice(k, false) == 0;
+          cudaEventRecord(e1, st);
+          if (cudaEventSynchronize(e1) != cudaSuccess || !okl) { cudaGetLastError(); continue; }
+          float ms = 0.f;
+          cudaEventElapsedTime(&ms, e0, e1);
+          if (ms < best) { best = ms; best_ch = k; }
+        }
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        it = c->tuned.emplace(key, best_ch).first;
+      }
+      ch = it->second;
+    }
+    if (launch_choice(ch, true) != 0)
+      return fail(NNCV_B200_ECUDA, "conv launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     return NNCV_B200_OK;
   }
   const int bn = igemm_pick_bn(M, c->Kout);
@@ -1030,12 +1094,12 @@ nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout
     fail(NNCV_B200_EINVAL, "conv_create: bad argument");
     return nullptr;
   }
-  if (algo != 0 && algo != 2 && algo != 3) {
+  if (algo < 0 || algo > 3) {
     fail(NNCV_B200_EINVAL, "conv_create: algo %d is not available", algo);
     return nullptr;
   }
-  if (algo == 2 && (dtype == NNCV_B200_F32 || !conv3x3_supported(C, Kout, R, S, stride, pad))) {
-    fail(NNCV_B200_EINVAL, "conv_create: algo 2 needs a 16-bit 3x3 stride-1 pad-1 conv with C, Kout %% 64 == 0");
+  if ((algo == 2 || algo == 1) && (dtype == NNCV_B200_F32 || !conv3x3_supported(C, Kout, R, S, stride, pad))) {
+    fail(NNCV_B200_EINVAL, "conv_create: algo 1 and 2 need a 16-bit 3x3 stride-1 pad-1 conv with C, Kout %% 64 == 0");
     return nullptr;
   }
   auto c = std::make_unique<nncv_b200_conv>();
@@ -1085,6 +1149,44 @@ int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int 
     rc = conv_run(c, c->sp_in.p, sl, c->sp_out.p, sl, N, H, W, scale, shift, res, relu, c->dtype, c->Kout, st);
     if (rc) return rc;
     LAUNCH(launch_relayout(c->sp_out.p, sl, out, dl, c->dtype, N, H, W, c->Kout, st));
+    return ok();
+  }
+  if (c->algo == 1) {
+    // Winograd F(2x2,3x3): input transform -> 16 GEMMs [tiles x C] * [C x Kout] -> output transform
+    const size_t es = dtype_size(c->dtype);
+    const long long T = (long long)N * ((H + 1) / 2) * ((W + 1) / 2);
+    if (T > 0x7fffffffLL) return fail(NNCV_B200_EINVAL, "winograd: too many tiles");
+    if (c->wino_w.empty()) {
+      if ((rc = c->wino_U.reserve((size_t)16 * c->Kout * c->Cpad * es))) return rc;
+      LAUNCH(launch_wino_filter(c->raw, c->raw_dt, c->sn, c->sc, c->stap, c->Kout, c->C, c->wino_U.p, c->dtype, st));
+      tconv_pick((T + 127) / 128, c->Cpad, c->Kout, 1, &c->wino_bn, &c->wino_resident);
+      for (int p = 0; p < 16; ++p) {
+        auto b = std::make_unique<DevBuf>();
+        if ((rc = b->reserve(packed_weight_bytes(c->Kout, c->Cpad, 1, 1, c->wino_bn)))) return rc;
+        LAUNCH(launch_pack_weights((const char*)c->wino_U.p + (size_t)p * c->Kout * c->Cpad * es, c->dtype, c->Cpad, 1, 0,
+                                   c->Kout, c->Cpad, c->Cpad, 1, c->wino_bn, c->dtype, b->p, st));
+        c->wino_w.push_back(std::move(b));
+      }
+    }
+    if ((rc = c->wino_V.reserve((size_t)16 * T * c->Cpad * es))) return rc;
+    if ((rc = c->wino_M.reserve((size_t)16 * T * c->Kout * sizeof(float)))) return rc;
+    const double flops = 2.0 * N * H * W * (double)c->Kout * c->C * 9.0;
+    prof_begin(6, flops, 2.0 * ((double)N * H * W * (c->C + c->Kout * (residual ? 2 : 1)) + 9.0 * c->Kout * c->C), (int)T,
+               c->Kout, c->C, c->wino_bn, st);
+    LAUNCH(launch_wino_input(in, c->wino_V.p, c->dtype, N, H, W, c->Cpad, st));
+    for (int p = 0; p < 16; ++p) {
+      TconvArgs a;
+      a.in = (const char*)c->wino_V.p + (size_t)p * T * c->Cpad * es;
+      a.wpack = c->wino_w[p]->p;
+      a.out = (float*)c->wino_M.p + (size_t)p * T * c->Kout;
+      a.N = 1; a.H = 1; a.W = (int)T; a.OH = 1; a.OW = (int)T; a.C = c->Cpad; a.Kout = c->Kout;
+      a.in_l = Layout{1, (int)T, 0}; a.out_l = Layout{1, (int)T, 0};
+      a.bn = c->wino_bn; a.resident = c->wino_resident; a.ab = c->dtype; a.out_dtype = kF32;
+      a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
+      LAUNCH(launch_tconv(a, st));
+    }
+    LAUNCH(launch_wino_output((const float*)c->wino_M.p, scale, shift, residual, out, c->dtype, N, H, W, c->Kout, relu, st));
+    prof_end(st);
     return ok();
   }
   rc = conv_run(c, in, Layout{0, 0, 0}, out, Layout{0, 0, 0}, N, H, W, scale, shift, residual, relu, c->dtype,

@@ -144,9 +144,11 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         int n0, oy0, ox0, n_tile;
         if (!item_of(i, n0, oy0, ox0, n_tile)) break;
         const int xb = p.stride * ox0 - p.pad + p.in_off, yb = p.stride * oy0 - p.pad + p.in_off;
-        for (int tap = 0; tap < p.taps && okw; ++tap) {
-          const int r = tap / p.S, s = tap - r * p.S;
-          for (int cb = 0; cb < p.CB; ++cb, ++cnt) {
+        // channel block outermost, taps innermost: the same accumulation order as the shifted-view
+        // 3x3 kernel, so both kernels give bit-identical sums
+        for (int cb = 0; cb < p.CB && okw; ++cb) {
+          for (int tap = 0; tap < p.taps; ++tap, ++cnt) {
+            const int r = tap / p.S, s = tap - r * p.S;
             const uint32_t st = cnt % (uint32_t)p.stages;
             if (!ptx::mbar_wait_abortable(empty + 8 * st, ((cnt / (uint32_t)p.stages) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
             ptx::mbar_arrive_expect_tx(full + 8 * st, (uint32_t)stage_bytes);
@@ -175,12 +177,13 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         ptx::tc_fence_after();
         const uint32_t d = tmem_base + ab * BN;
         for (int kb = 0; kb < KB; ++kb, ++cnt) {
+          const int cb = kb / p.taps, tap = kb - cb * p.taps;   // producer order: cb outer, tap inner
           const uint32_t st = cnt % (uint32_t)p.stages;
           if (!ptx::mbar_wait_abortable(full + 8 * st, (cnt / (uint32_t)p.stages) & 1u, abort_flag)) { okw = false; break; }
           ptx::tc_fence_after();
           const uint32_t a_addr = sRing + st * stage_bytes;
           const uint32_t a_lo = ptx::smem_desc_k128_lo(a_addr);
-          const uint32_t b_lo = ptx::smem_desc_k128_lo(RESIDENT ? sW + (uint32_t)kb * WTILE : a_addr + kABytes);
+          const uint32_t b_lo = ptx::smem_desc_k128_lo(RESIDENT ? sW + (uint32_t)(tap * p.CB + cb) * WTILE : a_addr + kABytes);
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4)
             ptx::umma_f16(d, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),

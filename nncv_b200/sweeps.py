@@ -4,7 +4,7 @@
 
   gemm : M=N=K in {512,1024,2048,4096}, fp16 in / fp32 accumulate (fp16 and fp32 C), optional fused
          bias + ReLU, and the fp32 CUDA-core path (config 1).
-  conv : 3x3 stride-1 pad-1, batch 32, (C=K, H=W) in {(64,64),(128,32),(256,16),(512,8)}, fp16, fused
+  conv : 3x3 stride-1 pad-1, batch 32 (and 256 with "conv256"), (C=K, H=W) in {(64,64),(128,32),(256,16),(512,8)}, fp16, fused
          scale/shift + ReLU (config 2), for the shifted-view kernel and the TMA-fed per-tap kernel.
   nets : ResNet-18 fp32 N=1 @256 (config 0), ResNet-50 fp16 N=512 @224 (config 4), device-resident.
 One JSON line per measurement; times are CUDA-event medians on the launching stream with an L2 flush
@@ -65,16 +65,15 @@ def gemm():
                               "note": "includes repacking B[K,N] into K-major tiles"}), flush=True)
 
 
-def conv():
+def conv(n=32):
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    n = 32
     for c, hw in ((64, 64), (128, 32), (256, 16), (512, 8)):
         w = (torch.randn((c, c, 3, 3)) * (2.0 / (9 * c)) ** 0.5).numpy().astype(np.float32)
         X = torch.randn((n, hw, hw, c), device="cuda", dtype=torch.float16)
         Y = torch.empty((n, hw, hw, c), device="cuda", dtype=torch.float16)
         sc = torch.rand(c, device="cuda") + 0.5
         sh = torch.randn(c, device="cuda") * 0.1
-        for algo, name in ((2, "shifted-view conv3x3"), (0, "per-tap TMA tconv")):
+        for algo, name in ((2, "shifted-view conv3x3"), (0, "per-tap TMA tconv"), (1, "winograd F(2x2,3x3) 3-stage")):
             h = lib().nncv_b200_conv_create(w.ctypes.data, F32, c, c, 3, 3, 1, 1, F16, algo)
             assert h
             call = lambda: check(lib().nncv_b200_conv_run(h, _p(X), _p(Y), n, hw, hw, _p(sc), _p(sh), None, 1, st))
@@ -85,7 +84,7 @@ def conv():
                 _flush_fill()
                 call()
             torch.cuda.synchronize()
-            recs = [r for r in rt.profile_records() if r["kind"] in (2, 5)]
+            recs = [r for r in rt.profile_records() if r["kind"] in (2, 5, 6)]
             rt.profile(False)
             ms = sorted(r["ms"] for r in recs)[len(recs) // 2]
             tf = recs[0]["flops"] / ms / 1e9
@@ -125,5 +124,7 @@ if __name__ == "__main__":
         gemm()
     if "conv" in which:
         conv()
+    if "conv256" in which:
+        conv(256)
     if "nets" in which:
         nets()

@@ -145,6 +145,45 @@ def test_conv3x3_shifted_view(case, dtype, res):
     assert G.rel_l2(y, ref) <= (TOL_16 if dtype == F16 else 8e-3)
 
 
+@pytest.mark.parametrize("case", [(2, 64, 16, 16, 64), (1, 64, 17, 23, 128), (3, 128, 7, 7, 64), (2, 256, 14, 14, 256)])
+@pytest.mark.parametrize("dtype,res", [(F16, True), (F16, False), (BF16, False)])
+def test_conv3x3_winograd_f2x2(case, dtype, res):
+    """Winograd F(2x2,3x3) in three stages (algo 1), odd map sizes included; V is rounded to 16 bits
+    between the stages, hence the wider tolerance than for the direct kernels."""
+    n, c, h, w, k = case
+    g = _rng(3 * n + c + h + w + k)
+    x = g.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = (g.standard_normal((k, c, 3, 3)) * np.sqrt(2.0 / (9 * c))).astype(np.float32)
+    scale = g.uniform(0.5, 1.5, k).astype(np.float32)
+    shift = (g.standard_normal(k) * 0.1).astype(np.float32)
+    rs = g.standard_normal((n, k, h, w)).astype(np.float32) if res else None
+    conv = G.Conv(wt, 1, 1, dtype, algo=1)
+    try:
+        y, xr = conv.run(x, scale, shift, rs, True)
+    finally:
+        conv.close()
+    tdt = G.TORCH_DT[dtype]
+    ref = ob.conv2d(xr, wt, 1, 1, acc64=True) * scale[None, :, None, None] + shift[None, :, None, None]
+    if res:
+        ref = ref + torch.from_numpy(rs).to(tdt).float().numpy()
+    ref = np.where(ref > 0, ref, 0)
+    assert np.isfinite(y).all()
+    assert G.rel_l2(y, ref) <= (5e-3 if dtype == F16 else 3e-2)
+
+
+def test_winograd_fixture_through_winograd_kernel():
+    """The reference's Winograd fixture (conv2dNchwWinograd.mlir: filter splat 0.1) padded to 64 channels:
+    all-ones input, interior outputs = 0.1 * 9 * 64."""
+    x = np.ones((1, 64, 16, 16), np.float32)
+    w = np.full((64, 64, 3, 3), 0.1, np.float32)
+    conv = G.Conv(w, 1, 1, F16, algo=1)
+    try:
+        y, _ = conv.run(x)
+    finally:
+        conv.close()
+    np.testing.assert_allclose(y[:, :, 1:-1, 1:-1], 0.1 * 9 * 64, rtol=2e-3)
+
+
 def test_conv3x3_shifted_view_matches_gather_kernel():
     """The two tcgen05 kernels agree on the same layer up to the order of the fp32 sums."""
     g = _rng(77)
