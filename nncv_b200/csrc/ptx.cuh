@@ -170,6 +170,17 @@ __device__ __forceinline__ bool named_bar_and(int id, int nthreads, bool pred) {
   return out != 0;
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may
+// start while its predecessor in the stream is still draining; it must not touch the
+// predecessor's results before grid_dependency_wait(), which returns once that grid has finished
+// and its writes are visible.  launch_dependents lets the successor be scheduled early.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 -------------
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -282,4 +293,22 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int ab_format) {
 }
 
 }  // namespace ptx
+
+// Host side: launch with programmatic stream serialization allowed (see grid_dependency_wait).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 }  // namespace nncv_b200

@@ -122,6 +122,10 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
+  // The prologue above touched nothing the previous kernel of the stream writes; everything
+  // below may, so wait for that kernel here and let the next one start its own prologue.
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
   volatile int* abort_flag = &s_abort;
 
   const int total_items = p.N * p.bands;
@@ -483,8 +487,7 @@ cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(stem_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int items = a.N * p.bands;
-  stem_pool_kernel<<<items < sms ? items : sms, kThreads, smem, stream>>>(p);
-  return cudaGetLastError();
+  return launch_pdl(stem_pool_kernel, dim3(items < sms ? items : sms), dim3(kThreads), smem, stream, p);
 }
 
 }  // namespace nncv_b200

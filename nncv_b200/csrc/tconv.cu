@@ -105,6 +105,10 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
+  // The prologue above touched nothing the previous kernel of the stream writes; everything
+  // below may, so wait for that kernel here and let the next one start its own prologue.
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
   volatile int* abort_flag = &s_abort;
 
   // Resident weights pin a CTA to one Kout tile (blockIdx.y); otherwise the CTA strides over
@@ -413,8 +417,7 @@ cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
     const long long items = (long long)p.m_items * p.n_tiles;
     grid = dim3((unsigned)(items < sms ? items : sms), 1);
   }
-  kern<<<grid, kThreads, smem, stream>>>(tm_in, tm_out, p);
-  return cudaGetLastError();
+  return launch_pdl(kern, grid, dim3(kThreads), smem, stream, tm_in, tm_out, p);
 }
 
 }  // namespace
