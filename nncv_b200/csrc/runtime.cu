@@ -573,7 +573,7 @@ int ensure_workspace(Model& m, int N, int H, int W) {
   m.act_next = 0;
   int rc = 0;
   if ((rc = m.in_stage.reserve((size_t)N * 3 * H * W * m.ele_width))) return rc;
-  if (m.fused_stem) {
+  if (m.fused_stem && W <= 512) {
     if ((rc = m.stem_rows.reserve(stem_rows_bytes(N, H, W)))) return rc;
   } else {
     if ((rc = m.in_nhwc.reserve((size_t)N * H * W * cpad0 * es))) return rc;
@@ -623,7 +623,7 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
     return conv_run(&c, in, il, out, ol, N, ih, iw, m.scale[idx], m.shift[idx], res, relu, adt, c.Kout, st);
   };
   void* x = nullptr;
-  if (m.fused_stem) {
+  if (m.fused_stem && W <= 512) {
     // stem conv + BN + ReLU + max-pool in one kernel (Res18.mlir:118-151)
     const int oh = out_hw(h, *m.convs[0]), ow = out_hw(w, *m.convs[0]);
     const int ph = (oh + 2 - 3) / 2 + 1, pw = (ow + 2 - 3) / 2 + 1;

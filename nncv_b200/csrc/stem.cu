@@ -21,13 +21,14 @@
 // (bulk async copies of row pairs into a ring) and reused by the seven filter rows of four
 // output rows.
 //
-// Roles (10 warps, persistent over (image, band of pooled rows) items):
+// Roles (11 warps, persistent over (image, band of pooled rows) items):
 //   warp 0   bulk-copies input rows into the ring; weights (28 KB) are resident.
-//   warp 1   issues the MMAs of one conv row into one of four TMEM accumulators.
-//   warps 2-9  read the accumulator, apply scale/shift, write the fp16 conv row into a 4-row
-//            ring in shared memory; after every second row they max-pool (3x3 window, -inf
-//            padding, so out-of-range taps are skipped), apply ReLU (it commutes with max)
-//            and store the pooled row, 16 bytes per thread, fully coalesced.
+//   warps 1, 10  one thread each issues the MMAs of alternate conv rows into four TMEM accumulators.
+//   warps 2-9  read the accumulator, apply scale/shift, keep the vertical maximum of the three
+//            conv rows of a pooling window in registers, write one fp16 row per pooled row to
+//            shared memory, take the horizontal maximum there (clamped window = -inf padding),
+//            apply ReLU (it commutes with max) and store the pooled row, 16 bytes per thread,
+//            fully coalesced.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -40,10 +41,11 @@ namespace {
 
 constexpr int kEpiWarps = 8;
 constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kThreads = 64 + kEpiThreads;
+constexpr int kIssuerBWarp = 2 + kEpiWarps;          // second MMA-issuing warp, after the epilogue warps
+constexpr int kThreads = 64 + kEpiThreads + 32;
 constexpr int kRingSlots = 8;       // input row PAIRS (rows 2k, 2k+1) resident in shared memory
 constexpr int kAccBufs = 4;         // TMEM accumulators of 64 columns
-constexpr int kConvRing = 4;        // fp16 conv rows kept for pooling
+constexpr int kConvRing = 2;        // rows of vertical maxima in shared memory (double buffer)
 constexpr int kWBytes = 7 * 4096;   // packed weights: 7 filter rows x [64 x 32] fp16
 
 // Optional clock64() trace of CTA 0 (built only with -DNNCV_B200_TRACE; a tuning aid).
@@ -85,6 +87,7 @@ __device__ __forceinline__ uint64_t desc_noswz(uint32_t addr, uint32_t lbo, uint
   return ptx::desc_from_halves(lo, hi);
 }
 
+template <int XT>   // x tiles of 128 output columns per conv row (1 or 2)
 __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_abort;
@@ -165,9 +168,13 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
       }
       if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitProducer);
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer -------
+  } else if (warp == 1 || warp == kIssuerBWarp) {
+    // ---------------------------------------------------------------- MMA issuers ------
+    // Two issuing threads take alternate accumulators (conv rows): while one waits on its
+    // barriers and commits, the other keeps the tensor pipe fed.  Input row pairs are handed
+    // back by the epilogue (it sees every row finish, in order), not by the issuers.
     if (lane == 0) {
+      const uint32_t issuer = warp == 1 ? 0u : 1u;
       const uint32_t idesc = ptx::umma_idesc(128, 64, p.bf16 ? 1 : 0);
       bool okw = ptx::mbar_wait_abortable(w_full, 0, abort_flag);
       uint32_t seq_base = 0, acc_cnt = 0;
@@ -175,8 +182,11 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
         int n, p0, p1, y0, y1, ir0, ir1;
         if (!item_of(i, n, p0, p1, y0, y1, ir0, ir1)) break;
         int waited_upto = ir0;     // pairs [ir0, waited_upto) are known to be in the ring
-        int released_upto = ir0;   // pairs [ir0, released_upto) were handed back
         for (int y = y0; y <= y1 && okw; ++y) {
+          // does this issuer own any accumulator of row y?
+          bool mine = false;
+          for (int xt = 0; xt < p.x_tiles; ++xt) mine |= ((acc_cnt + xt) & 1u) == issuer;
+          if (!mine) { acc_cnt += p.x_tiles; continue; }
           const int need = min(ir1, y + 1);            // conv row y reads pairs y-2 .. y+1
           for (; waited_upto <= need; ++waited_upto) {
             const uint32_t s = seq_base + (uint32_t)(waited_upto - ir0);
@@ -196,7 +206,8 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
               row_addr[r] = sRing + (s % kRingSlots) * p.slot_bytes + (uint32_t)(ir & 1) * p.row_bytes;
             }
           }
-          for (int xt = 0; xt < p.x_tiles && okw; ++xt) {
+          for (int xt = 0; xt < p.x_tiles && okw; ++xt, ++acc_cnt) {
+            if ((acc_cnt & 1u) != issuer) continue;
             const uint32_t ab = acc_cnt % kAccBufs;
             ST_TRACE(0, acc_cnt, 0);
             if (!ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt / kAccBufs) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
@@ -218,15 +229,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
             ST_TRACE(0, acc_cnt, 2);
             ptx::tc_commit(acc_full + 8 * ab);
             ST_TRACE(0, acc_cnt, 3);
-            ++acc_cnt;
           }
-          // pairs no later conv row of this item reads go back to the producer
-          const int new_upto = (y == y1) ? ir1 + 1 : min(ir1 + 1, y - 1);
-          for (; released_upto < new_upto; ++released_upto) {
-            const uint32_t s = seq_base + (uint32_t)(released_upto - ir0);
-            ptx::tc_commit(empty + 8 * (s % kRingSlots));
-          }
-          ST_TRACE(0, acc_cnt - 1, 4);
         }
         seq_base += (uint32_t)(ir1 - ir0 + 1);
       }
@@ -234,6 +237,11 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
     }
   } else {
     // ---------------------------------------------------------------- epilogue ---------
+    // Thread (quadrant, lane) owns output column x = xt*128 + row and 32 of the 64 channels of
+    // every conv row, so the VERTICAL part of the 3x3 max-pool runs in its registers: `prev`
+    // holds the last odd conv row (the top row of the next pooled row), `vm` the running
+    // maximum.  Only one row per pooled row goes to shared memory; the horizontal part reads
+    // three pixels of it.
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;          // output column within the x tile
@@ -244,15 +252,30 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
       sc[i] = p.scale ? __ldg(reinterpret_cast<const float4*>(p.scale + half * 32) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
       sh[i] = p.shift ? __ldg(reinterpret_cast<const float4*>(p.shift + half * 32) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    uint32_t acc_cnt = 0;
+    auto hmax = [&](uint32_t a, uint32_t b) -> uint32_t {
+      if (p.bf16) {
+        __nv_bfloat162 r = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+        return *reinterpret_cast<uint32_t*>(&r);
+      }
+      __half2 r = __hmax2_nan(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+      return *reinterpret_cast<uint32_t*>(&r);
+    };
+    uint32_t acc_cnt = 0, epi_seq_base = 0;
     bool okw = true;
     for (int i = 0; okw; ++i) {
       int n, p0, p1, y0, y1, ir0, ir1;
       if (!item_of(i, n, p0, p1, y0, y1, ir0, ir1)) break;
       int next_pool = p0;
+      int released_upto = ir0;   // input row pairs [ir0, released_upto) were handed back to the producer
+      uint32_t prev[XT][16], vm[XT][16];
+      bool has_prev = false;
       for (int y = y0; y <= y1 && okw; ++y) {
-        const uint32_t crow = sConv + (uint32_t)(y % kConvRing) * crow_bytes;
-        for (int xt = 0; xt < p.x_tiles; ++xt) {
+        const bool completes = next_pool < p1 && min(2 * next_pool + 1, p.OH - 1) == y;
+        const bool top_only = (y & 1) && y == 2 * next_pool - 1;   // first row of a band: only the top of a window
+        const uint32_t vrow = sConv + (uint32_t)(next_pool & 1) * crow_bytes;
+#pragma unroll
+        for (int xt = 0; xt < XT; ++xt) {
+          if (xt >= p.x_tiles) break;
           const uint32_t ab = acc_cnt % kAccBufs;
           if (et == 0) ST_TRACE(1, acc_cnt, 0);
           const bool got = ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt / kAccBufs) & 1u, abort_flag);
@@ -268,80 +291,83 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const StemParams
           ptx::tc_fence_before();
           ptx::mbar_arrive(acc_empty + 8 * ab);
           ++acc_cnt;
-          const int x = xt * 128 + row;
-          const uint32_t prow = crow + (uint32_t)x * 128u;
+          uint32_t cur[16];
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            uint32_t o[4];
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const int e = c4 * 8 + h * 2;
-              const float4 s4 = sc[e >> 2], b4 = sh[e >> 2];
-              const float sa = (e & 2) ? s4.z : s4.x, sb = (e & 2) ? s4.w : s4.y;
-              const float ba = (e & 2) ? b4.z : b4.x, bb = (e & 2) ? b4.w : b4.y;
-              const float a = fmaf(__uint_as_float(acc[e]), sa, ba);
-              const float b = fmaf(__uint_as_float(acc[e + 1]), sb, bb);
-              if (p.bf16) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-                o[h] = *reinterpret_cast<uint32_t*>(&v);
-              } else {
-                __half2 v = __floats2half2_rn(a, b);
-                o[h] = *reinterpret_cast<uint32_t*>(&v);
-              }
+          for (int h = 0; h < 16; ++h) {
+            const int e = 2 * h;
+            const float4 s4 = sc[e >> 2], b4 = sh[e >> 2];
+            const float sa = (e & 2) ? s4.z : s4.x, sb = (e & 2) ? s4.w : s4.y;
+            const float ba = (e & 2) ? b4.z : b4.x, bb = (e & 2) ? b4.w : b4.y;
+            const float a = fmaf(__uint_as_float(acc[e]), sa, ba);
+            const float b = fmaf(__uint_as_float(acc[e + 1]), sb, bb);
+            if (p.bf16) {
+              __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+              cur[h] = *reinterpret_cast<uint32_t*>(&v);
+            } else {
+              __half2 v = __floats2half2_rn(a, b);
+              cur[h] = *reinterpret_cast<uint32_t*>(&v);
             }
-            const uint32_t chunk = (uint32_t)(half * 4 + c4);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + ((chunk ^ (uint32_t)(x & 7)) << 4)),
-                         "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                         : "memory");
+          }
+          if ((y & 1) == 0) {          // middle row of window y/2
+#pragma unroll
+            for (int h = 0; h < 16; ++h) vm[xt][h] = has_prev ? hmax(prev[xt][h], cur[h]) : cur[h];
+          } else {                     // bottom row of window (y-1)/2 and top row of the next one
+            if (!top_only) {
+#pragma unroll
+              for (int h = 0; h < 16; ++h) vm[xt][h] = hmax(vm[xt][h], cur[h]);
+            }
+#pragma unroll
+            for (int h = 0; h < 16; ++h) prev[xt][h] = cur[h];
+          }
+          if (completes) {
+            const int x = xt * 128 + row;
+            const uint32_t prow = vrow + (uint32_t)x * 128u;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              const uint32_t chunk = (uint32_t)(half * 4 + c4);
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(prow + ((chunk ^ (uint32_t)(x & 7)) << 4)),
+                           "r"(vm[xt][c4 * 4]), "r"(vm[xt][c4 * 4 + 1]), "r"(vm[xt][c4 * 4 + 2]), "r"(vm[xt][c4 * 4 + 3])
+                           : "memory");
+            }
           }
         }
         if (!okw) break;
+        if (y & 1) has_prev = true;
+        if (et == 0) {
+          // every MMA of rows <= y has finished (their accumulators were seen full, in order): the
+          // pairs that only those rows read go back to the producer
+          const int new_upto = (y == y1) ? ir1 + 1 : min(ir1 + 1, y - 1);
+          for (; released_upto < new_upto; ++released_upto)
+            ptx::mbar_arrive(empty + 8 * ((epi_seq_base + (uint32_t)(released_upto - ir0)) % kRingSlots));
+        }
+        if (!completes) continue;
         if (et == 0) ST_TRACE(1, acc_cnt - 1, 4);
-        ptx::named_bar_sync(1, kEpiThreads);   // conv row y is complete in shared memory
+        ptx::named_bar_sync(1, kEpiThreads);   // the vertical maxima of pooled row next_pool are in shared memory
         if (et == 0) ST_TRACE(1, acc_cnt - 1, 5);
-        // pooled rows whose last conv row is y
-        while (next_pool < p1 && min(2 * next_pool + 1, p.OH - 1) <= y) {
+        {
           const int pr = next_pool++;
-          // Clamped window: a tap outside the map is replaced by its nearest valid neighbour, which
-          // is already in the window, so the maximum equals the one over the -inf padded map.
-          const uint32_t r0 = sConv + (uint32_t)(max(0, 2 * pr - 1) % kConvRing) * crow_bytes;
-          const uint32_t r1 = sConv + (uint32_t)((2 * pr) % kConvRing) * crow_bytes;
-          const uint32_t r2 = sConv + (uint32_t)(min(p.OH - 1, 2 * pr + 1) % kConvRing) * crow_bytes;
           uint16_t* orow = p.out + ((size_t)((size_t)n * p.ol.img_rows + pr + p.ol.off) * p.ol.pitch + p.ol.off) * 64;
           for (int u = et; u < p.PW * 8; u += kEpiThreads) {
             const int px = u >> 3, c = u & 7;
+            // clamped window: a tap outside the map is replaced by a neighbour already in the window
             const int xs[3] = {max(0, 2 * px - 1), 2 * px, min(p.OW - 1, 2 * px + 1)};
-            uint32_t v[9][4];
+            uint32_t v[3][4];
 #pragma unroll
-            for (int j = 0; j < 3; ++j) {
-              const uint32_t off = (uint32_t)xs[j] * 128u + (((uint32_t)c ^ (uint32_t)(xs[j] & 7)) << 4);
-              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[j][0]), "=r"(v[j][1]), "=r"(v[j][2]), "=r"(v[j][3]) : "r"(r0 + off));
-              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[3 + j][0]), "=r"(v[3 + j][1]), "=r"(v[3 + j][2]), "=r"(v[3 + j][3]) : "r"(r1 + off));
-              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v[6 + j][0]), "=r"(v[6 + j][1]), "=r"(v[6 + j][2]), "=r"(v[6 + j][3]) : "r"(r2 + off));
-            }
+            for (int j = 0; j < 3; ++j)
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(v[j][0]), "=r"(v[j][1]), "=r"(v[j][2]), "=r"(v[j][3])
+                           : "r"(vrow + (uint32_t)xs[j] * 128u + (((uint32_t)c ^ (uint32_t)(xs[j] & 7)) << 4)));
             uint32_t m[4];
+            const uint32_t zero = 0u;   // +0.0 in both halves, for fp16 and bf16
 #pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              if (p.bf16) {
-                __nv_bfloat162 r = *reinterpret_cast<__nv_bfloat162*>(&v[0][h]);
-#pragma unroll
-                for (int j = 1; j < 9; ++j) r = __hmax2_nan(r, *reinterpret_cast<__nv_bfloat162*>(&v[j][h]));
-                r = __hmax2_nan(r, __floats2bfloat162_rn(0.f, 0.f));   // ReLU after the max (NaN passes)
-                m[h] = *reinterpret_cast<uint32_t*>(&r);
-              } else {
-                __half2 r = *reinterpret_cast<__half2*>(&v[0][h]);
-#pragma unroll
-                for (int j = 1; j < 9; ++j) r = __hmax2_nan(r, *reinterpret_cast<__half2*>(&v[j][h]));
-                r = __hmax2_nan(r, __floats2half2_rn(0.f, 0.f));
-                m[h] = *reinterpret_cast<uint32_t*>(&r);
-              }
-            }
+            for (int h = 0; h < 4; ++h) m[h] = hmax(hmax(hmax(v[0][h], v[1][h]), v[2][h]), zero);   // ReLU after the max
             *reinterpret_cast<uint4*>(orow + (size_t)px * 64 + c * 8) = make_uint4(m[0], m[1], m[2], m[3]);
           }
           if (et == 0) ST_TRACE(1, acc_cnt - 1, 6);
         }
       }
-      // the next item starts writing the conv ring only after everyone has finished pooling
+      epi_seq_base += (uint32_t)(ir1 - ir0 + 1);
+      // the next item reuses the two shared-memory rows only after everyone has finished pooling
       ptx::named_bar_sync(2, kEpiThreads);
     }
     if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitEpilogue);
@@ -484,10 +510,14 @@ cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream) {
   const size_t smem = 128 + kWBytes + (size_t)kRingSlots * p.slot_bytes + 256 +
                       (size_t)kConvRing * p.x_tiles * 128 * 128 + 8 + 8 * (2 * kRingSlots + 2 * kAccBufs + 1) + 16;
   if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
-  cudaError_t e = cudaFuncSetAttribute(stem_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (p.x_tiles > 2) return cudaErrorInvalidConfiguration;   // wider than 512 pixels: not covered by the fused kernel
+  cudaError_t e = p.x_tiles == 1
+                      ? cudaFuncSetAttribute(stem_pool_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                      : cudaFuncSetAttribute(stem_pool_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int items = a.N * p.bands;
-  return launch_pdl(stem_pool_kernel, dim3(items < sms ? items : sms), dim3(kThreads), smem, stream, p);
+  if (p.x_tiles == 1) return launch_pdl(stem_pool_kernel<1>, dim3(items < sms ? items : sms), dim3(kThreads), smem, stream, p);
+  return launch_pdl(stem_pool_kernel<2>, dim3(items < sms ? items : sms), dim3(kThreads), smem, stream, p);
 }
 
 }  // namespace nncv_b200
