@@ -279,7 +279,7 @@ def run_ours(args):
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s",
                          "frac": (achieved / tf_peak) if achieved else None, "traffic": traffic,
                          "peak_source": f"{which} burst bf16/fp16 dense; sustained {tf_sus}",
-                         "kernel": "stem_pool_kernel + conv3x3_kernel + conv_igemm_kernel (all tcgen05 conv/FC launches of one step, rank 0)",
+                         "kernel": "stem_pool_kernel + conv3x3_kernel + tconv_kernel (all tcgen05 conv/FC launches of one step, rank 0)",
                          "launches_per_step": n_conv // 5 if n_conv else 0,
                          "conv_ms_per_step": conv_ms / 5 if conv_ms else None,
                          "other_kernels_ms_per_step": other_ms / 5 if prof else None},
