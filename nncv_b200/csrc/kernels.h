@@ -130,8 +130,9 @@ struct StemArgs {
 int stem_row_pixels(int W);
 size_t stem_rows_bytes(int N, int H, int W);
 size_t stem_wpack_bytes();
+// pads_are_zero: the zero pixels around every row of dst are already zero (enables the wide variant)
 cudaError_t launch_nchw_to_stem_rows(const void* src, DType src_dt, void* dst, DType dst_dt, int N, int H,
-                                     int W, cudaStream_t stream);
+                                     int W, bool pads_are_zero, cudaStream_t stream);
 cudaError_t launch_pack_stem_weights(const void* w, DType w_dt, void* dst, DType dst_dt, cudaStream_t stream);
 cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream);
 

@@ -575,6 +575,7 @@ int ensure_workspace(Model& m, int N, int H, int W) {
   if ((rc = m.in_stage.reserve((size_t)N * 3 * H * W * m.ele_width))) return rc;
   if (m.fused_stem && W <= 512) {
     if ((rc = m.stem_rows.reserve(stem_rows_bytes(N, H, W)))) return rc;
+    CU(cudaMemset(m.stem_rows.p, 0, stem_rows_bytes(N, H, W)));   // the pad pixels of every row stay zero
   } else {
     if ((rc = m.in_nhwc.reserve((size_t)N * H * W * cpad0 * es))) return rc;
     if ((rc = m.stem.reserve((size_t)N * h1 * w1 * 64 * es))) return rc;
@@ -628,7 +629,7 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
     const int oh = out_hw(h, *m.convs[0]), ow = out_hw(w, *m.convs[0]);
     const int ph = (oh + 2 - 3) / 2 + 1, pw = (ow + 2 - 3) / 2 + 1;
     prof_begin(3, 0, (double)N * H * (3.0 * W * m.ele_width + stem_row_pixels(W) * 8.0), N * H * W, 3, 0, 3, st);
-    LAUNCH(launch_nchw_to_stem_rows(src_dev, m.io_dt, m.stem_rows.p, adt, N, H, W, st));
+    LAUNCH(launch_nchw_to_stem_rows(src_dev, m.io_dt, m.stem_rows.p, adt, N, H, W, true, st));
     prof_end(st);
     if ((rc = next_act(m, N, ph, pw, 64, lay(ph, pw), st, &x))) return rc;
     StemArgs a;
@@ -1213,7 +1214,7 @@ int nncv_b200_stem_pool(const void* in_nchw, int in_dtype, const void* weights, 
   const size_t rows = (stem_rows_bytes(N, H, W) + 255) & ~(size_t)255;
   if ((rc = ensure_scratch(rows + stem_wpack_bytes()))) return rc;
   char* sp = (char*)g_dev.scratch;
-  LAUNCH(launch_nchw_to_stem_rows(in_nchw, (DType)in_dtype, sp, (DType)dtype, N, H, W, st));
+  LAUNCH(launch_nchw_to_stem_rows(in_nchw, (DType)in_dtype, sp, (DType)dtype, N, H, W, false, st));
   LAUNCH(launch_pack_stem_weights(weights, (DType)w_dtype, sp + rows, (DType)dtype, st));
   StemArgs a;
   a.in_rows = sp; a.wpack = sp + rows; a.scale = scale; a.shift = shift; a.out = out_nhwc;

@@ -194,33 +194,48 @@ __global__ void maxpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ d
   }
 }
 
-// Global average pool: sum in fp32 over HW then divide by HW; one thread per channel vector.
+// Global average pool: sum in fp32 over HW then divide by HW.  Eight adjacent lanes share one
+// (image, 16-byte channel vector): each sums every eighth pixel, a shuffle tree adds the partial
+// sums, the first lane stores.  (One thread per vector would walk the map as a chain of dependent
+// loads and take ~15 us however small the tensor.)
 template <typename T>
 __global__ void avgpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int H,
                                     int W, int C, Layout il) {
   const int HW = H * W;
   constexpr int V = 16 / sizeof(T);
+  constexpr int kSlices = 8;
   const int cv = C / V;
-  const long long total = (long long)N * cv;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(i % cv) * V;
-    const int n = (int)(i / cv);
+  const long long total = (long long)N * cv * kSlices;   // a multiple of 8: whole groups of lanes
+  for (long long i0 = blockIdx.x * (long long)blockDim.x; i0 < total; i0 += (long long)gridDim.x * blockDim.x) {
+    const long long i = i0 + threadIdx.x;
+    const bool live = i < total;
+    const int slice = (int)(i % kSlices);
+    const long long g = live ? i / kSlices : 0;
+    const int c = (int)(g % cv) * V;
+    const int n = (int)(g / cv);
     float s[V];
 #pragma unroll
     for (int e = 0; e < V; ++e) s[e] = 0.0f;
-    for (int px = 0; px < HW; ++px) {
-      const int y = px / W, x = px - y * W;
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
-          src + (((size_t)n * il.img_rows + y + il.off) * il.pitch + x + il.off) * C + c));
-      const T* v = reinterpret_cast<const T*>(&raw);
+    if (live) {
+      for (int px = slice; px < HW; px += kSlices) {
+        const int y = px / W, x = px - y * W;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+            src + (((size_t)n * il.img_rows + y + il.off) * il.pitch + x + il.off) * C + c));
+        const T* v = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-      for (int e = 0; e < V; ++e) s[e] += to_f<T>(v[e]);
+        for (int e = 0; e < V; ++e) s[e] += to_f<T>(v[e]);
+      }
     }
-    alignas(16) T o[V];
 #pragma unroll
-    for (int e = 0; e < V; ++e) o[e] = from_f<T>(s[e] / (float)HW);
-    *reinterpret_cast<uint4*>(dst + (size_t)n * C + c) = *reinterpret_cast<const uint4*>(o);
+    for (int d = 1; d < kSlices; d <<= 1)
+#pragma unroll
+      for (int e = 0; e < V; ++e) s[e] += __shfl_xor_sync(0xffffffffu, s[e], d);
+    if (live && slice == 0) {
+      alignas(16) T o[V];
+#pragma unroll
+      for (int e = 0; e < V; ++e) o[e] = from_f<T>(s[e] / (float)HW);
+      *reinterpret_cast<uint4*>(dst + (size_t)n * C + c) = *reinterpret_cast<const uint4*>(o);
+    }
   }
 }
 
@@ -345,8 +360,8 @@ cudaError_t launch_avgpool_nhwc(const void* src, void* dst, DType dt, int N, int
     using T = decltype(tag);
     constexpr int V = 16 / sizeof(T);
     if (C % V != 0) return cudaErrorInvalidValue;
-    const long long total = (long long)N * (C / V);
-    avgpool_nhwc_kernel<T><<<grid_for(total, 128), 128, 0, stream>>>(
+    const long long total = (long long)N * (C / V) * 8;
+    avgpool_nhwc_kernel<T><<<grid_for(total, 256), 256, 0, stream>>>(
         static_cast<const T*>(src), static_cast<T*>(dst), N, H, W, C, in_l);
     return cudaGetLastError();
   });

@@ -408,6 +408,43 @@ __global__ void nchw_to_stem_rows_kernel(const SrcT* __restrict__ src, DstT* __r
   }
 }
 
+// Fast variant for W % 8 == 0: one thread per 8 pixels (three 16- or 32-byte channel reads, one
+// 64-byte write).  It writes only real pixels: the zero pixels in front of and behind every row
+// must already be zero in dst (the executor clears the buffer once per shape).
+template <typename SrcT, typename DstT>
+__global__ void nchw_to_stem_rows8_kernel(const SrcT* __restrict__ src, DstT* __restrict__ dst, int N,
+                                          int H, int W, int RW) {
+  const int gw = W / 8;
+  const long long total = (long long)N * H * gw;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int xg = (int)(i % gw);
+    const long long t = i / gw;
+    const int y = (int)(t % H);
+    const int n = (int)(t / H);
+    const SrcT* s = src + ((size_t)n * 3 * H + y) * W + xg * 8;
+    alignas(16) SrcT c0[8], c1[8], c2[8];
+    constexpr int kVec = (int)(8 * sizeof(SrcT) / 16);   // uint4 loads per channel
+#pragma unroll
+    for (int v = 0; v < kVec; ++v) {
+      reinterpret_cast<uint4*>(c0)[v] = __ldg(reinterpret_cast<const uint4*>(s) + v);
+      reinterpret_cast<uint4*>(c1)[v] = __ldg(reinterpret_cast<const uint4*>(s + (size_t)H * W) + v);
+      reinterpret_cast<uint4*>(c2)[v] = __ldg(reinterpret_cast<const uint4*>(s + (size_t)2 * H * W) + v);
+    }
+    alignas(16) DstT o[32];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      o[4 * k] = (DstT)(float)c0[k];
+      o[4 * k + 1] = (DstT)(float)c1[k];
+      o[4 * k + 2] = (DstT)(float)c2[k];
+      o[4 * k + 3] = (DstT)0.0f;
+    }
+    uint4* d = reinterpret_cast<uint4*>(dst + (((size_t)n * H + y) * RW + 4 + xg * 8) * 4);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) d[v] = reinterpret_cast<const uint4*>(o)[v];
+  }
+}
+
 // W[64][3][7][7] -> per filter row r a [64 x 32] K-major un-swizzled tile: element (n, k) at
 // (k / 8) * 1024 + (n / 8) * 128 + (n % 8) * 16 + (k % 8) * 2; k = 4 * tap + channel, tap 0 is the
 // zero-weight pixel in front of the window, channel 3 is the zero padding channel.
@@ -444,20 +481,29 @@ size_t stem_rows_bytes(int N, int H, int W) { return (size_t)N * H * stem_row_pi
 size_t stem_wpack_bytes() { return kWBytes; }
 
 cudaError_t launch_nchw_to_stem_rows(const void* src, DType src_dt, void* dst, DType dst_dt, int N, int H,
-                                     int W, cudaStream_t stream) {
+                                     int W, bool pads_are_zero, cudaStream_t stream) {
   const int RW = stem_row_pixels(W);
-  const long long total = (long long)N * H * RW;
+  if (dst_dt == kF32) return cudaErrorInvalidValue;
+  const bool fast = pads_are_zero && W % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+  const long long total = fast ? (long long)N * H * (W / 8) : (long long)N * H * RW;
   long long blocks = (total + 255) / 256;
   if (blocks > 148LL * 32) blocks = 148LL * 32;
-  if (dst_dt == kF32) return cudaErrorInvalidValue;
   return by_dt(src_dt, [&](auto st) {
     using S = decltype(st);
-    if (dst_dt == kBF16)
+    if (fast) {
+      if (dst_dt == kBF16)
+        nchw_to_stem_rows8_kernel<S, __nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+            static_cast<const S*>(src), static_cast<__nv_bfloat16*>(dst), N, H, W, RW);
+      else
+        nchw_to_stem_rows8_kernel<S, __half><<<(int)blocks, 256, 0, stream>>>(
+            static_cast<const S*>(src), static_cast<__half*>(dst), N, H, W, RW);
+    } else if (dst_dt == kBF16) {
       nchw_to_stem_rows_kernel<S, __nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
           static_cast<const S*>(src), static_cast<__nv_bfloat16*>(dst), N, H, W, RW);
-    else
+    } else {
       nchw_to_stem_rows_kernel<S, __half><<<(int)blocks, 256, 0, stream>>>(
           static_cast<const S*>(src), static_cast<__half*>(dst), N, H, W, RW);
+    }
     return cudaGetLastError();
   });
 }
