@@ -132,3 +132,33 @@ def test_large_host_batch_is_split_and_matches_device_path():
     assert G.rel_l2(out_host, out_dev.cpu().numpy()) <= 1e-6
     ref = ob.resnet_forward(18, x[:8], blob)
     assert G.rel_l2(out_host[:8], ref) <= 1e-2
+
+
+@pytest.mark.parametrize("n,h,w", [(1, 256, 256), (3, 97, 131), (5, 224, 224), (2, 64, 600)])
+def test_resnet18_fp16_odd_shapes(n, h, w):
+    """Ragged maps, batch 1, a map wider than one stem tile, and one too wide for the fused stem (falls
+    back to the unfused stem + pool kernels): fp16 path vs the fp32 oracle."""
+    blob = to_flat_array(18, random_state_dict(18, 0)).blob()
+    rt.load_blob("resnet18", blob, F16)
+    x = random_input(n, h, w, 11, "normal")
+    out = np.zeros((n, 1000), np.float32)
+    rt.forward(out, x)
+    ref = ob.resnet_forward(18, x, blob)
+    assert np.isfinite(out).all()
+    assert G.rel_l2(out, ref) <= 1e-2
+    assert (out.argmax(1) == ref.argmax(1)).all()
+
+
+def test_logits_do_not_depend_on_the_tile_choice():
+    """Which kernel or tile the first-call timing picks must not change the result: both tcgen05 conv
+    kernels accumulate in the same order.  Compare two shapes of batch against each other instead of
+    toggling the library-wide switch (it is read once at load)."""
+    blob = to_flat_array(18, random_state_dict(18, 0)).blob()
+    rt.load_blob("resnet18", blob, F16)
+    x = random_input(40, 96, 96, 13, "normal")
+    X = torch.from_numpy(x).cuda()
+    full = torch.zeros((40, 1000), device="cuda")
+    rt.forward(full, X)
+    part = torch.zeros((7, 1000), device="cuda")
+    rt.forward(part, X[30:37].contiguous())
+    assert torch.equal(part, full[30:37])
