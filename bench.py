@@ -244,11 +244,11 @@ def run_ours(args):
 
     if rank == 0:
         tf_peak, tf_sus, hbm_peak, which = peaks()
-        conv = [r for r in prof if r["kind"] in (0, 2, 4, 5)]
+        conv = [r for r in prof if r["kind"] in (0, 2, 4, 5, 7)]
         conv_ms = sum(r["ms"] for r in conv)
         conv_fl = sum(r["flops"] for r in conv)
         n_conv = len(conv)
-        other_ms = sum(r["ms"] for r in prof if r["kind"] not in (0, 2, 4, 5))
+        other_ms = sum(r["ms"] for r in prof if r["kind"] not in (0, 2, 4, 5, 7))
         achieved = conv_fl / (conv_ms * 1e-3) / 1e12 if conv_ms > 0 else None
         traffic = None
         try:
@@ -279,7 +279,7 @@ def run_ours(args):
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s",
                          "frac": (achieved / tf_peak) if achieved else None, "traffic": traffic,
                          "peak_source": f"{which} burst bf16/fp16 dense; sustained {tf_sus}",
-                         "kernel": "stem_pool_kernel + conv3x3_kernel + tconv_kernel (all tcgen05 conv/FC launches of one step, rank 0)",
+                         "kernel": "stem_pool_kernel + conv3x3_kernel + conv3x3_pair_kernel + tconv_kernel (all tcgen05 conv/FC launches of one step, rank 0)",
                          "launches_per_step": n_conv // 5 if n_conv else 0,
                          "conv_ms_per_step": conv_ms / 5 if conv_ms else None,
                          "other_kernels_ms_per_step": other_ms / 5 if prof else None},

@@ -120,7 +120,7 @@ long long nncv_b200_launch_count(void);
 typedef struct {
   int kind;      /* 0 tcgen05 implicit GEMM (gathered A), 1 fp32 CUDA-core conv, 2 tcgen05 3x3 shifted-view
                     conv, 3 memory-bound helper, 4 fused stem conv + max-pool, 5 tcgen05 implicit GEMM
-                    (TMA-fed A), 6 Winograd F(2x2,3x3) (all three stages) */
+                    (TMA-fed A), 6 Winograd F(2x2,3x3) (all three stages), 7 shifted-view conv on CTA pairs */
   int M, N, K;   /* GEMM view of the launch (helpers: elements, channels, 0) */
   int bn;        /* N tile (kind 0); helper id (kind 3) */
   double flops;  /* algorithmic: 2*M*N*K with K = C*R*S (direct-convolution count) */
@@ -188,8 +188,9 @@ int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int 
                        const float* scale, const float* shift, const void* residual, int relu,
                        void* stream);
 
-/* Force the tile configuration (N tile 64/128/256; algo 2: sub-tiles per CTA 1/2/4; weights
- * resident in shared memory or streamed); bn = 0 restores the built-in choice.  A tuning
+/* Force the tile configuration (N tile 64/128/256; algo 2: sub-tiles per CTA 1/2/4; resident: 1 =
+ * weights resident in shared memory, 0 = streamed, 2 = (algo 2, Kout %% 256 == 0) the CTA-pair
+ * kernel on tcgen05.mma.cta_group::2); bn = 0 restores the built-in choice.  A tuning
  * and test hook with no counterpart in the reference. */
 int nncv_b200_conv_set_tile(nncv_b200_conv* c, int bn, int mt, int resident);
 

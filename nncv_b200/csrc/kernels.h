@@ -84,6 +84,9 @@ struct Conv3x3Args {
 bool conv3x3_supported(int C, int Kout, int R, int S, int stride, int pad);
 Conv3x3Config conv3x3_pick(int N, int H, int W, int C, int Kout, int has_res);
 cudaError_t launch_conv3x3(const Conv3x3Args& a, cudaStream_t stream);
+// CTA-pair variant (tcgen05.mma.cta_group::2, 256 slots x 256 channels per pair): Kout % 256 == 0,
+// maps up to 62 pixels wide, weights packed for N tile 128.
+cudaError_t launch_conv3x3_pair(const Conv3x3Args& a, cudaStream_t stream);
 
 // ---- TMA-fed persistent implicit GEMM (1x1 / strided convs, GEMM): C % 64 == 0 -----------------
 struct TconvArgs {

@@ -111,6 +111,10 @@ SV_CASES = [
     (3, 256, 14, 14, 256, (256, 2, 0)),
     (3, 256, 14, 14, 256, (64, 1, 0)),
     (5, 512, 7, 7, 512, None),
+    (3, 256, 14, 14, 256, (256, 1, 2)),   # CTA-pair kernel (tcgen05.mma.cta_group::2)
+    (5, 512, 7, 7, 512, (256, 1, 2)),
+    (9, 128, 28, 28, 256, (256, 1, 2)),
+    (1, 64, 8, 8, 256, (256, 1, 2)),
     (2, 64, 17, 23, 128, None),      # ragged map, Kout != C
     (1, 192, 5, 3, 64, None),
 ]
