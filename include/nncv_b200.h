@@ -201,6 +201,13 @@ int nncv_b200_conv_set_tile(nncv_b200_conv* c, int bn, int mt, int resident);
 int nncv_b200_stem_pool(const void* in_nchw, int in_dtype, const void* weights, int w_dtype,
                         const float* scale, const float* shift, void* out_nhwc, int dtype, int N, int H,
                         int W, void* stream);
+/* The stem kernel has two operand paths: one tiled TMA copy per input row pair through a tensor
+ * map with overlapping strides into a 128-byte-swizzled operand (used when the output row fits
+ * 128 pixels and H is even), and bulk copies of plain rows read through an un-swizzled operand
+ * (any shape up to 512 pixels wide).  policy 0 = automatic, 1 = always the plain-row path,
+ * negative = leave unchanged.  Returns the path the last stem launch took (0 none yet, 1 plain
+ * rows, 2 swizzled).  A test hook with no counterpart in the reference. */
+int nncv_b200_stem_variant(int policy);
 
 /* tensor.pad(-inf) + linalg.pooling_nchw_max (Res18.mlir:144-151), NHWC. */
 int nncv_b200_maxpool_nhwc(const void* in, void* out, int dtype, int N, int H, int W, int C,

@@ -120,6 +120,7 @@ cudaError_t launch_wino_output(const float* M, const float* scale, const float* 
 // ---- ResNet stem: 7x7 s2 p3 conv (3 -> 64) + scale/shift + ReLU + 3x3 s2 p1 max-pool, fused ---
 struct StemArgs {
   const void* in_rows = nullptr;   // rows written by launch_nchw_to_stem_rows
+  bool paired = false;             // in_rows holds interleaved row pairs (needs stem_paired_ok)
   const void* wpack = nullptr;     // written by launch_pack_stem_weights
   const float* scale = nullptr;
   const float* shift = nullptr;
@@ -130,14 +131,18 @@ struct StemArgs {
   int sm_count = 0;
   int* error_flag = nullptr;
 };
+bool stem_paired_ok(int H, int W);   // may the rows be stored as interleaved pairs (swizzled-operand kernel)?
 int stem_row_pixels(int W);
 size_t stem_rows_bytes(int N, int H, int W);
 size_t stem_wpack_bytes();
-// pads_are_zero: the zero pixels around every row of dst are already zero (enables the wide variant)
+// pads_are_zero: the zero pixels around every row of dst are already zero (enables the wide variant);
+// paired: rows 2k and 2k+1 interleaved in 16-byte chunks (H even)
 cudaError_t launch_nchw_to_stem_rows(const void* src, DType src_dt, void* dst, DType dst_dt, int N, int H,
-                                     int W, bool pads_are_zero, cudaStream_t stream);
+                                     int W, bool pads_are_zero, bool paired, cudaStream_t stream);
 cudaError_t launch_pack_stem_weights(const void* w, DType w_dt, void* dst, DType dst_dt, cudaStream_t stream);
 cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream);
+extern bool g_stem_force_plain;   // keep the plain-row (un-swizzled operand) kernel
+extern int g_stem_last_variant;   // 0 none yet, 1 plain rows, 2 swizzled operand
 
 // ---- fp32 SIMT implicit-GEMM convolution (the fp32-accurate path) ------------------------
 struct SimtConvArgs {

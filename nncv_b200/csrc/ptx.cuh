@@ -41,13 +41,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test, but the hardware may keep the thread suspended until the phase completes or
+// about `kWaitSuspendNs` have passed: a waiting warp then costs no issue slots and no
+// shared-memory traffic, which the single MMA-issuing and copy-issuing threads of the CTA need.
+constexpr uint32_t kWaitSuspendNs = 2000;
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(kWaitSuspendNs)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait that also gives up as soon as another role of the CTA has raised `*abort_flag`
 // (a shared-memory word), so one lost arrival ends the whole CTA within about a second.
 __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parity,
                                                     volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  while (!mbar_try_wait_suspend(bar, parity)) {
     if (*abort_flag) return false;
     if (clock64() - t0 > (1LL << 31)) {
       *abort_flag = 1;
@@ -62,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint32_t bar, uint32_t parit
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  while (!mbar_try_wait_suspend(bar, parity)) {
     if (clock64() - t0 > (1LL << 31)) return false;
   }
   return true;
@@ -118,6 +136,14 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, int c0, int c1, u
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap),
                "r"(c0), "r"(c1), "r"(src)
                : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int c0, int c1, int c2,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::
+          "r"(dst),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
 }
 // 4-D variants (c0 innermost).  Loads may start at negative or out-of-range coordinates in the
 // outer dimensions (those elements read as zero); stores are clipped to the tensor.
@@ -245,6 +271,16 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -283,11 +319,24 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try_wait_cluster_suspend(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(kWaitSuspendNs)
+      : "memory");
+  return ok != 0;
+}
 // Bounded, abortable wait on a barrier that another CTA of the cluster arrives on.
 __device__ __forceinline__ bool mbar_wait_cluster_abortable(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait_cluster(bar, parity)) {
+  while (!mbar_try_wait_cluster_suspend(bar, parity)) {
     if (*abort_flag) return false;
     if (clock64() - t0 > (1LL << 31)) {
       *abort_flag = 1;

@@ -495,6 +495,7 @@ struct Model {
   DevBuf in_stage, in_nhwc, stem, pooled, logits32, logits_io;
   DevBuf stem_rows, stem_w;  // fused stem (16-bit path): reformatted input rows, packed weights
   bool fused_stem = false;
+  int stem_rows_paired = -1;  // layout the zeroed pad pixels of stem_rows belong to (-1: none yet)
   // One buffer per activation tensor of the forward, handed out in call order.  Buffers are
   // zeroed when created and never shared between tensors, so the pad slots of shared-pad
   // tensors stay zero no matter which kernel writes the interior.
@@ -589,6 +590,7 @@ int ensure_workspace(Model& m, int N, int H, int W) {
   if (m.fused_stem && W <= 512) {
     if ((rc = m.stem_rows.reserve(stem_rows_bytes(N, H, W)))) return rc;
     CU(cudaMemset(m.stem_rows.p, 0, stem_rows_bytes(N, H, W)));   // the pad pixels of every row stay zero
+    m.stem_rows_paired = (int)stem_paired_ok(H, W);
   } else {
     if ((rc = m.in_nhwc.reserve((size_t)N * H * W * cpad0 * es))) return rc;
     if ((rc = m.stem.reserve((size_t)N * h1 * w1 * 64 * es))) return rc;
@@ -642,11 +644,16 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
     const int oh = out_hw(h, *m.convs[0]), ow = out_hw(w, *m.convs[0]);
     const int ph = (oh + 2 - 3) / 2 + 1, pw = (ow + 2 - 3) / 2 + 1;
     prof_begin(3, 0, (double)N * H * (3.0 * W * m.ele_width + stem_row_pixels(W) * 8.0), N * H * W, 3, 0, 3, st);
-    LAUNCH(launch_nchw_to_stem_rows(src_dev, m.io_dt, m.stem_rows.p, adt, N, H, W, true, st));
+    const bool paired = stem_paired_ok(H, W);
+    if (m.stem_rows_paired != (int)paired) {   // pad pixels sit elsewhere in the other layout
+      CU(cudaMemsetAsync(m.stem_rows.p, 0, stem_rows_bytes(N, H, W), st));
+      m.stem_rows_paired = (int)paired;
+    }
+    LAUNCH(launch_nchw_to_stem_rows(src_dev, m.io_dt, m.stem_rows.p, adt, N, H, W, true, paired, st));
     prof_end(st);
     if ((rc = next_act(m, N, ph, pw, 64, lay(ph, pw), st, &x))) return rc;
     StemArgs a;
-    a.in_rows = m.stem_rows.p; a.wpack = m.stem_w.p; a.scale = m.scale[0]; a.shift = m.shift[0];
+    a.in_rows = m.stem_rows.p; a.paired = paired; a.wpack = m.stem_w.p; a.scale = m.scale[0]; a.shift = m.shift[0];
     a.out = x; a.out_l = lay(ph, pw); a.N = N; a.H = H; a.W = W; a.ab = adt;
     a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
     prof_begin(4, 2.0 * N * oh * ow * 64.0 * 147.0,
@@ -1227,13 +1234,20 @@ int nncv_b200_stem_pool(const void* in_nchw, int in_dtype, const void* weights, 
   const size_t rows = (stem_rows_bytes(N, H, W) + 255) & ~(size_t)255;
   if ((rc = ensure_scratch(rows + stem_wpack_bytes()))) return rc;
   char* sp = (char*)g_dev.scratch;
-  LAUNCH(launch_nchw_to_stem_rows(in_nchw, (DType)in_dtype, sp, (DType)dtype, N, H, W, false, st));
+  const bool paired = stem_paired_ok(H, W);
+  LAUNCH(launch_nchw_to_stem_rows(in_nchw, (DType)in_dtype, sp, (DType)dtype, N, H, W, false, paired, st));
   LAUNCH(launch_pack_stem_weights(weights, (DType)w_dtype, sp + rows, (DType)dtype, st));
   StemArgs a;
-  a.in_rows = sp; a.wpack = sp + rows; a.scale = scale; a.shift = shift; a.out = out_nhwc;
+  a.in_rows = sp; a.paired = paired; a.wpack = sp + rows; a.scale = scale; a.shift = shift; a.out = out_nhwc;
   a.N = N; a.H = H; a.W = W; a.ab = (DType)dtype; a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
   LAUNCH(launch_stem_pool(a, st));
   return ok();
+}
+
+int nncv_b200_stem_variant(int policy) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (policy >= 0) g_stem_force_plain = policy == 1;
+  return g_stem_last_variant;
 }
 
 int nncv_b200_maxpool_nhwc(const void* in, void* out, int dtype, int N, int H, int W, int C,

@@ -237,9 +237,12 @@ def test_conv_winograd_fixture_closed_form():
 
 @pytest.mark.parametrize("shape", [(2, 32, 32), (2, 224, 224), (1, 37, 53), (1, 64, 300), (3, 256, 256), (1, 7, 7)])
 @pytest.mark.parametrize("dtype,in_dt", [(F16, F32), (F16, F16), (BF16, F32)])
-def test_stem_pool_fused(shape, dtype, in_dt):
+@pytest.mark.parametrize("policy", [0, 1])
+def test_stem_pool_fused(shape, dtype, in_dt, policy):
     """7x7 s2 conv + scale/shift + ReLU + 3x3 s2 max-pool in one kernel vs the oracle's
-    conv -> batch-norm-style affine -> ReLU -> max-pool chain (Res18.mlir:118-151)."""
+    conv -> batch-norm-style affine -> ReLU -> max-pool chain (Res18.mlir:118-151), on both
+    operand paths (policy 0: swizzled operand through an overlapping-stride tensor map where the
+    shape allows it; policy 1: plain rows and the un-swizzled operand)."""
     n, h, w = shape
     g = _rng(n * 1000 + h + w)
     x = g.standard_normal((n, 3, h, w)).astype(np.float32)
@@ -252,9 +255,15 @@ def test_stem_pool_fused(shape, dtype, in_dt):
     oh, ow = (h + 6 - 7) // 2 + 1, (w + 6 - 7) // 2 + 1
     ph, pw = (oh + 2 - 3) // 2 + 1, (ow + 2 - 3) // 2 + 1
     Y = torch.full((n, ph, pw, 64), float("nan"), device="cuda", dtype=G.TORCH_DT[dtype])
-    check(lib().nncv_b200_stem_pool(G.p(X), in_dt, G.p(Wd), F32, G.p(sc), G.p(sh), G.p(Y), dtype, n, h, w,
-                                    G.stream_ptr()))
-    torch.cuda.synchronize()
+    lib().nncv_b200_stem_variant(policy)
+    try:
+        check(lib().nncv_b200_stem_pool(G.p(X), in_dt, G.p(Wd), F32, G.p(sc), G.p(sh), G.p(Y), dtype, n, h, w,
+                                        G.stream_ptr()))
+        torch.cuda.synchronize()
+        took = lib().nncv_b200_stem_variant(-1)
+    finally:
+        lib().nncv_b200_stem_variant(0)
+    assert took == (2 if policy == 0 and ow <= 128 and h % 2 == 0 else 1)
     tdt = G.TORCH_DT[dtype]
     xr = torch.from_numpy(x).to(G.TORCH_DT[in_dt]).to(tdt).float().numpy()
     wr = torch.from_numpy(wt).to(tdt).float().numpy()
