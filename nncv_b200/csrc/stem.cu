@@ -638,43 +638,47 @@ __global__ void nchw_to_stem_rows8_kernel(const SrcT* __restrict__ src, DstT* __
   }
 }
 
-// Paired variant of the fast kernel (W % 8 == 0, H even): one thread per 8 pixels of a row PAIR,
-// 128 contiguous bytes written (chunks of row 2k and row 2k+1 alternate).
+// Paired variant of the fast kernel (W even, H even): one thread per 16-byte chunk (two pixels of
+// one row) of the interleaved pair layout, so consecutive threads write consecutive chunks (a
+// warp stores 512 contiguous bytes) and read 64-byte runs of two rows of the three channel
+// planes.  Pad chunks are written as zeros.
 template <typename SrcT, typename DstT>
-__global__ void nchw_to_stem_pairs8_kernel(const SrcT* __restrict__ src, DstT* __restrict__ dst, int N,
+__global__ void nchw_to_stem_pairs2_kernel(const SrcT* __restrict__ src, DstT* __restrict__ dst, int N,
                                            int H, int W, int RW) {
-  const int gw = W / 8;
-  const long long total = (long long)N * (H / 2) * gw;
+  const int cw = RW;                       // chunks per row pair: RW / 2 per row, two rows
+  const long long total = (long long)N * (H / 2) * cw;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const int xg = (int)(i % gw);
-    const long long t = i / gw;
+    const int k = (int)(i % cw);
+    const long long t = i / cw;
     const int yp = (int)(t % (H / 2));
     const int n = (int)(t / (H / 2));
-    alignas(16) DstT o[64];
-    constexpr int kVec = (int)(8 * sizeof(SrcT) / 16);   // uint4 loads per channel
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const SrcT* s = src + ((size_t)n * 3 * H + 2 * yp + r) * W + xg * 8;
-      alignas(16) SrcT c0[8], c1[8], c2[8];
-#pragma unroll
-      for (int v = 0; v < kVec; ++v) {
-        reinterpret_cast<uint4*>(c0)[v] = __ldg(reinterpret_cast<const uint4*>(s) + v);
-        reinterpret_cast<uint4*>(c1)[v] = __ldg(reinterpret_cast<const uint4*>(s + (size_t)H * W) + v);
-        reinterpret_cast<uint4*>(c2)[v] = __ldg(reinterpret_cast<const uint4*>(s + (size_t)2 * H * W) + v);
+    const int r = k & 1, x = (k >> 1) * 2 - 4;   // row of the pair, first pixel of the chunk
+    alignas(16) DstT o[8];
+    if (x >= 0 && x < W) {
+      const SrcT* s = src + ((size_t)n * 3 * H + 2 * yp + r) * W + x;
+      alignas(8) SrcT c0[2], c1[2], c2[2];
+      if (sizeof(SrcT) == 2) {
+        *reinterpret_cast<uint32_t*>(c0) = __ldg(reinterpret_cast<const uint32_t*>(s));
+        *reinterpret_cast<uint32_t*>(c1) = __ldg(reinterpret_cast<const uint32_t*>(s + (size_t)H * W));
+        *reinterpret_cast<uint32_t*>(c2) = __ldg(reinterpret_cast<const uint32_t*>(s + (size_t)2 * H * W));
+      } else {
+        *reinterpret_cast<uint2*>(c0) = __ldg(reinterpret_cast<const uint2*>(s));
+        *reinterpret_cast<uint2*>(c1) = __ldg(reinterpret_cast<const uint2*>(s + (size_t)H * W));
+        *reinterpret_cast<uint2*>(c2) = __ldg(reinterpret_cast<const uint2*>(s + (size_t)2 * H * W));
       }
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int e = (k >> 1) * 16 + r * 8 + (k & 1) * 4;   // chunk k/2 of row r
-        o[e] = (DstT)(float)c0[k];
-        o[e + 1] = (DstT)(float)c1[k];
-        o[e + 2] = (DstT)(float)c2[k];
-        o[e + 3] = (DstT)0.0f;
+      for (int q = 0; q < 2; ++q) {
+        o[4 * q] = (DstT)(float)c0[q];
+        o[4 * q + 1] = (DstT)(float)c1[q];
+        o[4 * q + 2] = (DstT)(float)c2[q];
+        o[4 * q + 3] = (DstT)0.0f;
       }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) o[q] = (DstT)0.0f;
     }
-    uint4* d = reinterpret_cast<uint4*>(dst + ((size_t)n * H + 2 * yp) * RW * 4 + (size_t)(2 + xg * 4) * 16);
-#pragma unroll
-    for (int v = 0; v < 8; ++v) d[v] = reinterpret_cast<const uint4*>(o)[v];
+    *reinterpret_cast<uint4*>(dst + (size_t)i * 8) = *reinterpret_cast<const uint4*>(o);
   }
 }
 
@@ -755,18 +759,20 @@ cudaError_t launch_nchw_to_stem_rows(const void* src, DType src_dt, void* dst, D
                                      int W, bool pads_are_zero, bool paired, cudaStream_t stream) {
   const int RW = stem_row_pixels(W);
   if (dst_dt == kF32 || (paired && H % 2 != 0)) return cudaErrorInvalidValue;
-  const bool fast = pads_are_zero && W % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0;
-  const long long total = fast ? (long long)N * (paired ? H / 2 : H) * (W / 8) : (long long)N * H * RW;
+  // the paired fast kernel writes the pads itself and needs 2-pixel alignment only
+  const bool fast = paired ? (W % 2 == 0 && (reinterpret_cast<uintptr_t>(src) & 7) == 0)
+                           : (pads_are_zero && W % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  const long long total = fast ? (paired ? (long long)N * (H / 2) * RW : (long long)N * H * (W / 8)) : (long long)N * H * RW;
   long long blocks = (total + 255) / 256;
   if (blocks > 148LL * 32) blocks = 148LL * 32;
   return by_dt(src_dt, [&](auto st) {
     using S = decltype(st);
     if (fast && paired) {
       if (dst_dt == kBF16)
-        nchw_to_stem_pairs8_kernel<S, __nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
+        nchw_to_stem_pairs2_kernel<S, __nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(
             static_cast<const S*>(src), static_cast<__nv_bfloat16*>(dst), N, H, W, RW);
       else
-        nchw_to_stem_pairs8_kernel<S, __half><<<(int)blocks, 256, 0, stream>>>(
+        nchw_to_stem_pairs2_kernel<S, __half><<<(int)blocks, 256, 0, stream>>>(
             static_cast<const S*>(src), static_cast<__half*>(dst), N, H, W, RW);
     } else if (fast) {
       if (dst_dt == kBF16)
