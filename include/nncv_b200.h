@@ -188,6 +188,18 @@ int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int 
                        const float* scale, const float* shift, const void* residual, int relu,
                        void* stream);
 
+/* One launch for the two convolutions that open a ResNet BasicBlock which changes resolution
+ * (tests/Nets/Res18.mlir: the 3x3 stride-2 conv on %padded_107 and the 1x1 stride-2 downsample
+ * conv on %cst_62 read the same tensor; likewise in layers 3 and 4): `c` is an odd square filter
+ * with pad = R/2, `branch` a 1x1 pad-0 filter of the same stride, input and output channels
+ * (Kout a multiple of 128), both 16-bit plans made with algo 0.  The branch rides along as an
+ * extra tap on the centre pixel; it gets its own scale/shift, no ReLU, and its own dense NHWC
+ * output.  Results equal two separate nncv_b200_conv_run calls bit for bit. */
+int nncv_b200_conv_run_fused(nncv_b200_conv* c, nncv_b200_conv* branch, const void* in, void* out,
+                             void* out_branch, int N, int H, int W, const float* scale,
+                             const float* shift, const float* scale_branch,
+                             const float* shift_branch, int relu, void* stream);
+
 /* Force the tile configuration (N tile 64/128/256; algo 2: sub-tiles per CTA 1/2/4; resident: 1 =
  * weights resident in shared memory, 0 = streamed, 2 = (algo 2, Kout %% 256 == 0) the CTA-pair
  * kernel on tcgen05.mma.cta_group::2); bn = 0 restores the built-in choice.  A tuning

@@ -24,7 +24,7 @@ EXPORTS = [
     "nncv_flat_array_indexer", "nncv_flat_array_data", "nncv_flat_array_wrapped",
     "nncv_flat_array_write",
     "nncv_b200_matmul", "nncv_b200_matmul_noalloc", "nncv_b200_conv_create", "nncv_b200_conv_destroy", "nncv_b200_conv_run",
-    "nncv_b200_conv_set_tile", "nncv_b200_stem_pool", "nncv_b200_stem_variant",
+    "nncv_b200_conv_run_fused", "nncv_b200_conv_set_tile", "nncv_b200_stem_pool", "nncv_b200_stem_variant",
     "nncv_b200_maxpool_nhwc", "nncv_b200_avgpool_nhwc", "nncv_b200_nchw_to_nhwc", "nncv_b200_bn_fold",
 ]
 
@@ -88,6 +88,8 @@ def lib() -> ctypes.CDLL:
     L.nncv_b200_conv_destroy.restype = None
     L.nncv_b200_conv_run.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_void_p]
+    L.nncv_b200_conv_run_fused.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
     L.nncv_b200_conv_set_tile.argtypes = [c_void_p, c_int, c_int, c_int]
     L.nncv_b200_stem_pool.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                       c_int, c_int, c_void_p]

@@ -96,6 +96,12 @@ struct TconvArgs {
   const float* shift = nullptr;
   const void* residual = nullptr;  // layout out_l, 16-bit
   void* out = nullptr;             // layout out_l, row pitch == Kout
+  // fused 1x1 branch on the same input (same stride, pad 0, Kout outputs): weights packed for
+  // N tile 128 as a 1-tap filter, its own scale/shift, no ReLU, written to out2 (layout out_l)
+  const void* wpack2 = nullptr;
+  const float* scale2 = nullptr;
+  const float* shift2 = nullptr;
+  void* out2 = nullptr;
   int N = 0, H = 0, W = 0, C = 0, OH = 0, OW = 0, Kout = 0, R = 1, S = 1, stride = 1, pad = 0;
   Layout in_l{0, 0, 0}, out_l{0, 0, 0};
   int bn = 64, resident = 0;

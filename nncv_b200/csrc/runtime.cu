@@ -213,6 +213,9 @@ struct DevBuf {
 // =====================================================================================
 // convolution plan
 // =====================================================================================
+// NNCV_B200_FUSE_DS=0 runs the downsample 1x1 convs as their own launches
+bool g_fuse_downsample = getenv("NNCV_B200_FUSE_DS") ? atoi(getenv("NNCV_B200_FUSE_DS")) != 0 : true;
+
 struct ConvChoice {
   int kernel = 5;  // 2 shifted-view conv3x3, 5 per-tap TMA kernel
   int bn = 64, mt = 1, resident = 0;
@@ -238,6 +241,7 @@ struct nncv_b200_conv {
   bool force_gather = false;                       // algo 3: the cp.async gather kernel even where TMA would do
   std::map<std::array<int, 5>, ConvChoice> tuned;  // measured best kernel/tile per (N, H, W, residual, out type)
   Conv3x3Config cfg3{0, 0, 0};                     // algo 2: forced tile configuration (bn 0 = auto)
+  std::map<std::array<int, 3>, bool> fuse_tuned;   // per (N, H, W): is the launch fused with the 1x1 branch faster?
 };
 
 namespace {
@@ -256,9 +260,24 @@ int conv_prepare(nncv_b200_conv* c, int bn, cudaStream_t st, const void** wpack)
   return NNCV_B200_OK;
 }
 
+// A 1x1 convolution of the same stride on the same input, fused into the per-tap kernel as an
+// extra tap on the centre pixel (ResNet's downsample branch beside the block's first 3x3 conv).
+struct FusedBranch {
+  nncv_b200_conv* conv = nullptr;
+  const float* scale = nullptr;
+  const float* shift = nullptr;
+  void* out = nullptr;   // layout and type of the main output
+};
+
+bool fused_branch_ok(const nncv_b200_conv& c, const nncv_b200_conv& b) {
+  return !g_force_gather && g_fuse_downsample && c.dtype != kF32 && b.dtype == c.dtype && c.algo == 0 && b.algo == 0 &&
+         !c.force_gather && c.R == c.S && (c.R & 1) && c.pad == c.R / 2 && b.R == 1 && b.S == 1 && b.pad == 0 &&
+         b.stride == c.stride && b.Cpad == c.Cpad && b.Kout == c.Kout && c.Kout % 128 == 0 && c.Cpad % 64 == 0;
+}
+
 int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout out_l, int N, int H,
              int W, const float* scale, const float* shift, const void* residual, int relu,
-             DType out_dt, long long ldo, cudaStream_t st) {
+             DType out_dt, long long ldo, cudaStream_t st, const FusedBranch* fb = nullptr) {
   const int OH = (H + 2 * c->pad - c->R) / c->stride + 1;
   const int OW = (W + 2 * c->pad - c->S) / c->stride + 1;
   if (N <= 0 || OH <= 0 || OW <= 0) return fail(NNCV_B200_EINVAL, "conv: empty output");
@@ -288,9 +307,11 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
     return NNCV_B200_OK;
   }
   const long long M = (long long)N * OH * OW;
-  const double flops = 2.0 * (double)M * c->Kout * c->C * c->R * c->S;
-  const double bytes = 2.0 * ((double)N * H * W * c->C + (double)c->Kout * c->C * c->R * c->S +
-                              (double)M * c->Kout * (residual ? 2 : 1)) +
+  if (fb && (c->dtype == kF32 || out_dt != c->dtype || ldo != c->Kout || !fused_branch_ok(*c, *fb->conv)))
+    return fail(NNCV_B200_EINVAL, "conv: the fused 1x1 branch does not fit this convolution");
+  const double flops = 2.0 * (double)M * c->Kout * c->C * (c->R * c->S + (fb ? 1 : 0));
+  const double bytes = 2.0 * ((double)N * H * W * c->C + (double)c->Kout * c->C * (c->R * c->S + (fb ? 1 : 0)) +
+                              (double)M * c->Kout * ((residual ? 2 : 1) + (fb ? 1 : 0))) +
                        (out_dt == kF32 ? 2.0 * M * c->Kout : 0.0);
   // ---- tensor-core kernels fed by TMA: the shifted-view 3x3 kernel (needs shared-pad layouts) and
   // the per-tap kernel.  Which one, and with which tile, is timed once per (plan, shape).
@@ -328,6 +349,11 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
       }
       TconvArgs a;
       a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
+      if (fb) {
+        rc = conv_prepare(fb->conv, 128, st, &a.wpack2);
+        if (rc) return rc;
+        a.scale2 = fb->scale; a.shift2 = fb->shift; a.out2 = fb->out;
+      }
       a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
       a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.in_l = in_l; a.out_l = out_l;
       a.bn = ch.bn; a.resident = ch.resident; a.ab = c->dtype; a.out_dtype = out_dt; a.relu = relu;
@@ -350,7 +376,9 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
       tconv_pick(m_items, c->Cpad, c->Kout, c->R * c->S, &bn, &resident);
       ch = ConvChoice{5, bn, 1, resident};
     }
-    if (c->cfg3.bn) {
+    if (fb) {
+      ch = ConvChoice{5, 128, 1, 0};   // the one configuration the fused kernel is built for
+    } else if (c->cfg3.bn) {
       ch.bn = c->cfg3.bn; ch.mt = c->cfg3.mt > 0 ? c->cfg3.mt : 1; ch.resident = c->cfg3.resident;
       if (c->cfg3.resident == 2 && sv_ok) { ch.kernel = 7; ch.resident = 0; }   // forced CTA-pair kernel
     } else if (g_autotune) {
@@ -692,12 +720,65 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
       int ch = h, cw = w;       // spatial size of the tensor flowing through the block body
       const void* cur = x;
       const int body = m.spec.depth == 18 ? 1 : 2;  // convs before the last one
+      void* ds_done = nullptr;   // output of the downsample branch when it ran fused with the first conv
+      void* ds_buf = nullptr;
       for (int k = 0; k < body; ++k) {
         nncv_b200_conv& c = *m.convs[gi];
         const int oh = out_hw(ch, c), ow = out_hw(cw, c);
         void* t = nullptr;
         if ((rc = next_act(m, N, oh, ow, c.Kout, lay(oh, ow), st, &t))) return rc;
-        if ((rc = run(gi, cur, lay(ch, cw), t, lay(oh, ow), ch, cw, nullptr, 1))) return rc;
+        // BasicBlock: the 3x3 stride-2 conv and the 1x1 stride-2 downsample conv read the same tensor
+        const size_t ds_idx = gi + (size_t)body + 1;
+        bool fuse = false;
+        if (k == 0 && has_ds && body == 1 && sp && ds_idx < m.convs.size() && fused_branch_ok(c, *m.convs[ds_idx])) {
+          if ((rc = next_act(m, N, oh, ow, c.Kout, lay(oh, ow), st, &ds_buf))) return rc;
+          FusedBranch fb{m.convs[ds_idx].get(), m.scale[ds_idx], m.shift[ds_idx], ds_buf};
+          fuse = c.Kout <= 128;   // one Kout tile: the input is read once for both convolutions
+          if (g_autotune) {
+            // time both ways once per shape: one fused launch against the two tuned separate ones
+            const std::array<int, 3> key{N, ch, cw};
+            auto it = c.fuse_tuned.find(key);
+            if (it == c.fuse_tuned.end()) {
+              cudaEvent_t e[3];
+              for (auto& ev : e) CU(cudaEventCreate(&ev));
+              const bool was = g_prof_on;
+              g_prof_on = false;
+              auto both = [&](bool fused) -> int {
+                if (fused)
+                  return conv_run(&c, cur, lay(ch, cw), t, lay(oh, ow), N, ch, cw, m.scale[gi], m.shift[gi], nullptr, 1,
+                                  adt, c.Kout, st, &fb);
+                int r = run(gi, cur, lay(ch, cw), t, lay(oh, ow), ch, cw, nullptr, 1);
+                return r ? r : run(ds_idx, cur, lay(ch, cw), ds_buf, lay(oh, ow), ch, cw, nullptr, 0);
+              };
+              rc = both(false);            // also lets each separate conv pick its own kernel
+              if (!rc) rc = both(true);
+              float ms_sep = 0.f, ms_fused = 0.f;
+              if (!rc) {
+                cudaEventRecord(e[0], st);
+                for (int rep = 0; rep < 3 && !rc; ++rep) rc = both(false);
+                cudaEventRecord(e[1], st);
+                for (int rep = 0; rep < 3 && !rc; ++rep) rc = both(true);
+                cudaEventRecord(e[2], st);
+                if (!rc && cudaEventSynchronize(e[2]) == cudaSuccess) {
+                  cudaEventElapsedTime(&ms_sep, e[0], e[1]);
+                  cudaEventElapsedTime(&ms_fused, e[1], e[2]);
+                }
+              }
+              g_prof_on = was;
+              for (auto& ev : e) cudaEventDestroy(ev);
+              if (rc) return rc;
+              it = c.fuse_tuned.emplace(key, ms_fused > 0.f && ms_fused < ms_sep).first;
+            }
+            fuse = it->second;
+          }
+          if (fuse) {
+            rc = conv_run(&c, cur, lay(ch, cw), t, lay(oh, ow), N, ch, cw, m.scale[gi], m.shift[gi], nullptr, 1, adt,
+                          c.Kout, st, &fb);
+            if (rc) return rc;
+            ds_done = ds_buf;
+          }
+        }
+        if (!fuse && (rc = run(gi, cur, lay(ch, cw), t, lay(oh, ow), ch, cw, nullptr, 1))) return rc;
         cur = t; ch = oh; cw = ow;
         ++gi;
       }
@@ -706,9 +787,12 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
       const int oh = out_hw(ch, cl), ow = out_hw(cw, cl);
       const void* identity = x;
       if (has_ds) {  // BN(conv1x1(identity)) (Res18.mlir:297-311)
-        void* ds = nullptr;
-        if ((rc = next_act(m, N, oh, ow, cl.Kout, lay(oh, ow), st, &ds))) return rc;
-        if ((rc = run(gi, x, lay(h, w), ds, lay(oh, ow), h, w, nullptr, 0))) return rc;
+        void* ds = ds_done;
+        if (!ds) {
+          ds = ds_buf;
+          if (!ds && (rc = next_act(m, N, oh, ow, cl.Kout, lay(oh, ow), st, &ds))) return rc;
+          if ((rc = run(gi, x, lay(h, w), ds, lay(oh, ow), h, w, nullptr, 0))) return rc;
+        }
         ++gi;
         identity = ds;
       }
@@ -1212,6 +1296,23 @@ int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int 
   }
   rc = conv_run(c, in, Layout{0, 0, 0}, out, Layout{0, 0, 0}, N, H, W, scale, shift, residual, relu, c->dtype,
                 c->Kout, st);
+  return rc ? rc : ok();
+}
+
+int nncv_b200_conv_run_fused(nncv_b200_conv* c, nncv_b200_conv* branch, const void* in, void* out, void* out_branch,
+                             int N, int H, int W, const float* scale, const float* shift, const float* scale_branch,
+                             const float* shift_branch, int relu, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!c || !branch || !in || !out || !out_branch) return fail(NNCV_B200_EINVAL, "conv_run_fused: null argument");
+  if (N <= 0 || H <= 0 || W <= 0) return fail(NNCV_B200_EINVAL, "conv_run_fused: bad shape");
+  if (!fused_branch_ok(*c, *branch))
+    return fail(NNCV_B200_EINVAL, "conv_run_fused: needs an odd square filter with pad = R/2 and a 1x1 pad-0 branch of the "
+                                  "same stride, channels and (multiple of 128) output channels, 16-bit, algo 0");
+  FusedBranch fb{branch, scale_branch, shift_branch, out_branch};
+  rc = conv_run(c, in, Layout{0, 0, 0}, out, Layout{0, 0, 0}, N, H, W, scale, shift, nullptr, relu, c->dtype, c->Kout,
+                (cudaStream_t)stream, &fb);
   return rc ? rc : ok();
 }
 

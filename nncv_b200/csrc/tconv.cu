@@ -47,6 +47,9 @@ struct TcParams {
   const float* scale;
   const float* shift;
   const uint8_t* residual;   // same layout / type as out, or null
+  const uint8_t* wpack2;     // DUAL: packed 1x1 weights of the fused downsample branch
+  const float* scale2;
+  const float* shift2;
   int* error_flag;
   int Kout, CB, taps, S, stride, pad;
   int in_off;                // layout offset of the input (0 dense, 1 shared-pad)
@@ -59,12 +62,22 @@ struct TcParams {
   int relu, bf16, out_f32;
 };
 
-template <int BN, bool RESIDENT>
+// DUAL: a ResNet block that changes resolution applies a 3x3 stride-2 pad-1 convolution and a 1x1
+// stride-2 convolution to the SAME tensor (tests/Nets/Res18.mlir: the convs on %padded_107 and on
+// %cst_62 both read the output of layer 1, and likewise for layers 3 and 4).  The 1x1 conv reads
+// exactly the pixels of the 3x3 conv's centre tap, so it rides along as a tenth "tap" per channel
+// block: the same A tile coordinates, its own weight tile, and a second accumulator beside the
+// first.  Both results leave through the same epilogue (the second one with its own scale/shift,
+// no ReLU, no residual) into a second output tensor.
+template <int BN, bool RESIDENT, bool DUAL>
 __global__ void __launch_bounds__(kThreads, 1)
 tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_out,
-             const TcParams p) {
+             const __grid_constant__ CUtensorMap tm_out2, const TcParams p) {
+  static_assert(!DUAL || !RESIDENT, "the fused downsample branch streams its weights");
   constexpr int WTILE = BN * 128;
-  constexpr int ACC_COLS = 2 * BN;   // two accumulator buffers
+  constexpr int ACC_W = DUAL ? 2 * BN : BN;   // columns of one accumulator buffer
+  constexpr int ACC_COLS = 2 * ACC_W;         // two accumulator buffers
+  const int taps_x = p.taps + (DUAL ? 1 : 0); // taps per channel block in the pipeline
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_abort;
@@ -96,6 +109,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
     ptx::mbar_fence_init();
     ptx::prefetch_tensormap(&tm_in);
     ptx::prefetch_tensormap(&tm_out);
+    if (DUAL) ptx::prefetch_tensormap(&tm_out2);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, ACC_COLS);
@@ -151,16 +165,19 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         // channel block outermost, taps innermost: the same accumulation order as the shifted-view
         // 3x3 kernel, so both kernels give bit-identical sums
         for (int cb = 0; cb < p.CB && okw; ++cb) {
-          for (int tap = 0; tap < p.taps; ++tap, ++cnt) {
-            const int r = tap / p.S, s = tap - r * p.S;
+          for (int tap = 0; tap < taps_x; ++tap, ++cnt) {
+            const int gtap = tap < p.taps ? tap : p.taps / 2;   // the extra tap re-reads the centre tap's pixels
+            const int r = gtap / p.S, s = gtap - r * p.S;
             const uint32_t st = cnt % (uint32_t)p.stages;
             if (!ptx::mbar_wait_abortable(empty + 8 * st, ((cnt / (uint32_t)p.stages) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
             ptx::mbar_arrive_expect_tx(full + 8 * st, (uint32_t)stage_bytes);
             const uint32_t dst = sRing + st * stage_bytes;
             ptx::tma_load_4d(dst, &tm_in, cb * 64, xb + s, yb + r, n0, full + 8 * st);
-            if (!RESIDENT)
-              ptx::bulk_g2s(dst + kABytes, p.wpack + ((size_t)n_tile * KB + (size_t)tap * p.CB + cb) * WTILE, WTILE,
-                            full + 8 * st);
+            if (!RESIDENT) {
+              const uint8_t* wsrc = (DUAL && tap == p.taps) ? p.wpack2 + ((size_t)n_tile * p.CB + cb) * WTILE
+                                                             : p.wpack + ((size_t)n_tile * KB + (size_t)tap * p.CB + cb) * WTILE;
+              ptx::bulk_g2s(dst + kABytes, wsrc, WTILE, full + 8 * st);
+            }
           }
         }
       }
@@ -179,9 +196,11 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         const uint32_t ab = acc_cnt & 1u;
         if (!ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt >> 1) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
         ptx::tc_fence_after();
-        const uint32_t d = tmem_base + ab * BN;
-        for (int kb = 0; kb < KB; ++kb, ++cnt) {
-          const int cb = kb / p.taps, tap = kb - cb * p.taps;   // producer order: cb outer, tap inner
+        const uint32_t d = tmem_base + ab * ACC_W;
+        const int KBX = taps_x * p.CB;
+        for (int kb = 0; kb < KBX; ++kb, ++cnt) {
+          const int cb = kb / taps_x, tap = kb - cb * taps_x;   // producer order: cb outer, tap inner
+          const bool second = DUAL && tap == p.taps;
           const uint32_t st = cnt % (uint32_t)p.stages;
           if (!ptx::mbar_wait_abortable(full + 8 * st, (cnt / (uint32_t)p.stages) & 1u, abort_flag)) { okw = false; break; }
           ptx::tc_fence_after();
@@ -190,8 +209,9 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
           const uint32_t b_lo = ptx::smem_desc_k128_lo(RESIDENT ? sW + (uint32_t)(tap * p.CB + cb) * WTILE : a_addr + kABytes);
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4)
-            ptx::umma_f16(d, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
-                          ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi), idesc, (kb | k4) != 0 ? 1u : 0u);
+            ptx::umma_f16(second ? d + BN : d, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
+                          ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi), idesc,
+                          (second ? (cb | k4) : (cb | tap | k4)) != 0 ? 1u : 0u);
           ptx::tc_commit(empty + 8 * st);
         }
         if (!okw) break;
@@ -225,7 +245,12 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
       const bool got = ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt >> 1) & 1u, abort_flag);
       if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; break; }
       ptx::tc_fence_after();
+      for (int oi = 0; oi < (DUAL ? 2 : 1); ++oi)
       for (int sl = 0; sl < slabs; ++sl, ++jglob) {
+        const float* scale_o = oi ? p.scale2 : p.scale;
+        const float* shift_o = oi ? p.shift2 : p.shift;
+        const uint8_t* residual_o = oi ? nullptr : p.residual;
+        const bool relu_o = oi ? false : p.relu != 0;
         const uint32_t sb = (uint32_t)jglob & 1u;
         const int ncol = n_tile * BN + sl * slab_cols;     // first column of the slab
         // this warp's 32 accumulator columns inside the slab: 16-bit output -> columns
@@ -237,17 +262,17 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         const int n_first = ncol + c0;
         uint32_t acc[32];
         __syncwarp();
-        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + ab * BN + (uint32_t)(sl * slab_cols + c0), acc);
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + ab * ACC_W + (uint32_t)(oi * BN + sl * slab_cols + c0), acc);
         uint32_t res[2][8];
-        const bool use_res = p.residual != nullptr && valid && active && n_first + 32 <= p.Kout;
+        const bool use_res = residual_o != nullptr && valid && active && n_first + 32 <= p.Kout;
         if (use_res) {
-          const uint8_t* rp = p.residual + (pix * (size_t)p.Kout + n_first) * 2;
+          const uint8_t* rp = residual_o + (pix * (size_t)p.Kout + n_first) * 2;
           ptx::ldg_256(rp, res[0]);
           ptx::ldg_256(rp + 32, res[1]);
         }
         __syncwarp();
         ptx::tmem_ld_wait();
-        if (sl == slabs - 1) {
+        if (sl == slabs - 1 && oi == (DUAL ? 1 : 0)) {
           ptx::tc_fence_before();
           ptx::mbar_arrive(acc_empty + 8 * ab);
         }
@@ -257,8 +282,8 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
 #pragma unroll
             for (int e = 0; e < 32; e += 4) {
               float4 sc = make_float4(1.f, 1.f, 1.f, 1.f), sh = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (p.scale) sc = __ldg(reinterpret_cast<const float4*>(p.scale + n_first + e));
-              if (p.shift) sh = __ldg(reinterpret_cast<const float4*>(p.shift + n_first + e));
+              if (scale_o) sc = __ldg(reinterpret_cast<const float4*>(scale_o + n_first + e));
+              if (shift_o) sh = __ldg(reinterpret_cast<const float4*>(shift_o + n_first + e));
               v[e] = fmaf(__uint_as_float(acc[e]), sc.x, sh.x);
               v[e + 1] = fmaf(__uint_as_float(acc[e + 1]), sc.y, sh.y);
               v[e + 2] = fmaf(__uint_as_float(acc[e + 2]), sc.z, sh.z);
@@ -270,8 +295,8 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
               const int n = n_first + e;
               float x = __uint_as_float(acc[e]);
               if (n < p.Kout) {
-                if (p.scale) x *= __ldg(p.scale + n);
-                if (p.shift) x += __ldg(p.shift + n);
+                if (scale_o) x *= __ldg(scale_o + n);
+                if (shift_o) x += __ldg(shift_o + n);
               }
               v[e] = x;
             }
@@ -295,7 +320,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
 #pragma unroll
               for (int h = 0; h < 4; ++h) {
                 const float a = v[c4 * 4 + h];
-                o[h] = p.relu ? (!(a <= 0.0f) ? a : 0.0f) : a;
+                o[h] = relu_o ? (!(a <= 0.0f) ? a : 0.0f) : a;
               }
               asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(srow + (((uint32_t)c4 ^ sw) << 4)), "f"(o[0]),
                            "f"(o[1]), "f"(o[2]), "f"(o[3])
@@ -310,11 +335,11 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
                 const float a = v[c4 * 8 + h * 2], b = v[c4 * 8 + h * 2 + 1];
                 if (p.bf16) {
                   __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
-                  if (p.relu) x = __hmax2_nan(x, __floats2bfloat162_rn(0.f, 0.f));
+                  if (relu_o) x = __hmax2_nan(x, __floats2bfloat162_rn(0.f, 0.f));
                   o[h] = *reinterpret_cast<uint32_t*>(&x);
                 } else {
                   __half2 x = __floats2half2_rn(a, b);
-                  if (p.relu) x = __hmax2_nan(x, __floats2half2_rn(0.f, 0.f));
+                  if (relu_o) x = __hmax2_nan(x, __floats2half2_rn(0.f, 0.f));
                   o[h] = *reinterpret_cast<uint32_t*>(&x);
                 }
               }
@@ -329,7 +354,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         ptx::named_bar_sync(1, kEpiThreads);
         if (elected) {
           if (ncol < p.Kout)
-            ptx::tma_store_4d(&tm_out, ncol, ox0 + p.out_off, oy0 + p.out_off, n0, sStage + sb * kSlabBytes);
+            ptx::tma_store_4d((DUAL && oi) ? &tm_out2 : &tm_out, ncol, ox0 + p.out_off, oy0 + p.out_off, n0, sStage + sb * kSlabBytes);
           ptx::bulk_commit();
           ptx::bulk_wait_read<1>();
         }
@@ -380,7 +405,7 @@ bool make_map4(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esz,
 
 constexpr size_t kSmemLimit = 227 * 1024;
 
-template <int BN, bool RESIDENT>
+template <int BN, bool RESIDENT, bool DUAL = false>
 cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
   const size_t wtile = (size_t)BN * 128;
   const int KB = p.taps * p.CB;
@@ -403,7 +428,10 @@ cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
   if (!make_map4(&tm_out, a.out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : dt, f32 ? 4 : 2, a.Kout, ol.pitch, ol.img_rows,
                  a.N, f32 ? 32 : 64, p.tw, p.th, p.tn, 1, 1))
     return cudaErrorInvalidValue;
-  auto kern = tconv_kernel<BN, RESIDENT>;
+  CUtensorMap tm_out2 = tm_out;
+  if (DUAL && !make_map4(&tm_out2, a.out2, dt, 2, a.Kout, ol.pitch, ol.img_rows, a.N, 64, p.tw, p.th, p.tn, 1, 1))
+    return cudaErrorInvalidValue;
+  auto kern = tconv_kernel<BN, RESIDENT, DUAL>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int sms = a.sm_count > 0 ? a.sm_count : 148;
@@ -417,7 +445,7 @@ cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
     const long long items = (long long)p.m_items * p.n_tiles;
     grid = dim3((unsigned)(items < sms ? items : sms), 1);
   }
-  return launch_pdl(kern, grid, dim3(kThreads), smem, stream, tm_in, tm_out, p);
+  return launch_pdl(kern, grid, dim3(kThreads), smem, stream, tm_in, tm_out, tm_out2, p);
 }
 
 }  // namespace
@@ -462,6 +490,7 @@ cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream) {
   TcParams p;
   p.wpack = static_cast<const uint8_t*>(a.wpack);
   p.scale = a.scale; p.shift = a.shift; p.residual = static_cast<const uint8_t*>(a.residual);
+  p.wpack2 = static_cast<const uint8_t*>(a.wpack2); p.scale2 = a.scale2; p.shift2 = a.shift2;
   p.error_flag = a.error_flag;
   p.Kout = a.Kout; p.CB = a.C / 64; p.taps = a.R * a.S; p.S = a.S; p.stride = a.stride; p.pad = a.pad;
   p.in_off = a.in_l.off; p.out_off = a.out_l.off;
@@ -479,6 +508,12 @@ cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream) {
   p.relu = a.relu; p.bf16 = a.ab == kBF16; p.out_f32 = a.out_dtype == kF32;
   p.stages = 0;
   if (p.residual && p.out_f32) return cudaErrorInvalidValue;
+  if (a.wpack2) {   // fused 1x1 stride-s branch on the centre tap: odd square filter, pad = R/2, N tile 128 streamed
+    if (!a.out2 || a.bn != 128 || a.resident || p.out_f32 || a.R != a.S || a.R % 2 == 0 || a.pad != a.R / 2 ||
+        a.Kout % 128 != 0 || (reinterpret_cast<uintptr_t>(a.wpack2) & 15) || (reinterpret_cast<uintptr_t>(a.out2) & 15))
+      return cudaErrorInvalidValue;
+    return launch_cfg<128, false, true>(a, p, stream);
+  }
 #define NNCV_TC(BN_, RES_) \
   if (a.bn == BN_ && (a.resident != 0) == RES_) return launch_cfg<BN_, RES_>(a, p, stream);
   NNCV_TC(64, true)

@@ -235,6 +235,44 @@ def test_conv_winograd_fixture_closed_form():
     np.testing.assert_allclose(y, 3.6, rtol=1e-6)
 
 
+@pytest.mark.parametrize("shape", [(3, 64, 56, 56, 128), (2, 128, 28, 28, 256), (5, 256, 14, 14, 512), (1, 64, 9, 13, 128)])
+@pytest.mark.parametrize("dtype", [F16, BF16])
+def test_conv_fused_downsample(shape, dtype):
+    """The 3x3 stride-2 conv and the 1x1 stride-2 downsample conv of a BasicBlock in one launch
+    (Res18.mlir: convs on %padded_107 and %cst_62): equal to two separate launches bit for bit and
+    to the oracle within the 16-bit tolerance."""
+    n, c, h, w, k = shape
+    g = _rng(n + c + h + k)
+    x = g.standard_normal((n, c, h, w)).astype(np.float32)
+    w3 = (g.standard_normal((k, c, 3, 3)) * np.sqrt(2.0 / (9 * c))).astype(np.float32)
+    w1 = (g.standard_normal((k, c, 1, 1)) * np.sqrt(2.0 / c)).astype(np.float32)
+    sc3, sh3 = g.uniform(0.5, 1.5, k).astype(np.float32), (g.standard_normal(k) * 0.1).astype(np.float32)
+    sc1, sh1 = g.uniform(0.5, 1.5, k).astype(np.float32), (g.standard_normal(k) * 0.1).astype(np.float32)
+    main, branch = G.Conv(w3, 2, 1, dtype), G.Conv(w1, 2, 0, dtype)
+    try:
+        y3, xq = main.run(x, sc3, sh3, relu=True)
+        y1, _ = branch.run(x, sc1, sh1, relu=False)
+        X = G.dev(np.ascontiguousarray(x.transpose(0, 2, 3, 1)), dtype)
+        oh, ow = (h + 2 - 3) // 2 + 1, (w + 2 - 3) // 2 + 1
+        Y3 = torch.full((n, oh, ow, k), float("nan"), device="cuda", dtype=G.TORCH_DT[dtype])
+        Y1 = torch.full((n, oh, ow, k), float("nan"), device="cuda", dtype=G.TORCH_DT[dtype])
+        S3, H3, S1, H1 = (G.dev(a, F32) for a in (sc3, sh3, sc1, sh1))
+        check(lib().nncv_b200_conv_run_fused(main.h, branch.h, G.p(X), G.p(Y3), G.p(Y1), n, h, w, G.p(S3), G.p(H3),
+                                             G.p(S1), G.p(H1), 1, G.stream_ptr()))
+        G.sync_check()
+    finally:
+        main.close()
+        branch.close()
+    f3, f1 = G.host(Y3).transpose(0, 3, 1, 2), G.host(Y1).transpose(0, 3, 1, 2)
+    assert np.array_equal(f3, y3) and np.array_equal(f1, y1)
+    tdt = G.TORCH_DT[dtype]
+    q = lambda a: torch.from_numpy(a).to(tdt).float().numpy()
+    r3 = ob.relu(ob.conv2d(xq, q(w3), 2, 1, acc64=True) * sc3[None, :, None, None] + sh3[None, :, None, None])
+    r1 = ob.conv2d(xq, q(w1), 2, 0, acc64=True) * sc1[None, :, None, None] + sh1[None, :, None, None]
+    tol = TOL_16 if dtype == F16 else 8e-3
+    assert G.rel_l2(f3, r3) <= tol and G.rel_l2(f1, r1) <= tol
+
+
 @pytest.mark.parametrize("shape", [(2, 32, 32), (2, 224, 224), (1, 37, 53), (1, 64, 300), (3, 256, 256), (1, 7, 7)])
 @pytest.mark.parametrize("dtype,in_dt", [(F16, F32), (F16, F16), (BF16, F32)])
 @pytest.mark.parametrize("policy", [0, 1])
