@@ -33,26 +33,31 @@ constexpr int kEpiWarps = 8;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kSlabBytes = 128 * 128;
-constexpr int kBNPair = 256;          // columns of the pair's tile
-constexpr int kWTile = 128 * 128;     // this CTA's half of a weight tile
 constexpr int kWGroup = 3;            // taps (one filter row) per weight stage: fewer barrier round trips per MMA
-constexpr int kWStage = kWGroup * kWTile;
-constexpr int kMaxIn = 4, kMaxW = 8;
+constexpr int kMaxIn = 4, kMaxW = 12;
 
 struct PairParams {
-  const uint8_t* wpack;      // packed for N tile 128: tile index 2 * n_tile + cta rank
+  const uint8_t* wpack;      // packed for N tile max(64, BNP / 2); each CTA of the pair takes BNP / 2 rows
   const float* scale;
   const float* shift;
   const uint16_t* residual;
   int* error_flag;
   int T, P, Himg, CB, Kout, n_tiles, m_items;   // m_items of 256 slots
   int box_rows, in_stages, w_stages;
+  int w_resident;            // all 3 * CB weight stages stay in shared memory (one Kout tile only)
+  unsigned long long wpack_bytes;   // size of the packed weights (copies are range-checked against it)
   int relu, has_res, bf16;
 };
 
+template <int BNP>   // columns of the pair's tile: 64, 128 or 256
 __global__ void __launch_bounds__(kThreads, 1)
 conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_out,
                     const PairParams p) {
+  constexpr int kBNPair = BNP;
+  constexpr int kWTile = (BNP / 2) * 128;          // this CTA's half of a weight tile
+  constexpr int kWStage = kWGroup * kWTile;
+  constexpr int kPackBN = BNP / 2 < 64 ? 64 : BNP / 2;   // N tile of the packed weights
+  constexpr int kPackTile = kPackBN * 128;
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_abort;
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -91,7 +96,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
     ptx::prefetch_tensormap(&tm_out);
   }
   if (warp == 1) {
-    ptx::tmem_alloc_pair(tmem_slot, 512);
+    ptx::tmem_alloc_pair(tmem_slot, 2 * BNP < 32 ? 32 : 2 * BNP);
     ptx::tmem_relinquish_pair();
   }
   ptx::tc_fence_before();
@@ -121,21 +126,33 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
         int m_item, n_tile;
         if (!item_of(i, m_item, n_tile)) break;
         const int row0 = m_item * 256 + (int)rank * 128 - p.P - 1;
-        const uint8_t* wsrc = p.wpack + (size_t)(2 * n_tile + (int)rank) * kb_total * kWTile;
+        // this CTA's rows [n_tile * BNP + rank * BNP/2, + BNP/2) inside the packed N tiles
+        const int wrow = n_tile * BNP + (int)rank * (BNP / 2);
+        const uint8_t* wsrc = p.wpack + (size_t)(wrow / kPackBN) * kb_total * kPackTile + (size_t)(wrow % kPackBN) * 128;
         for (int cb = 0; cb < p.CB && okw; ++cb) {
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
           if (!ptx::mbar_wait_cluster_abortable(in_empty + 8 * st, ((in_cnt / (uint32_t)p.in_stages) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
           ptx::mbar_arrive_expect_tx(in_full + 8 * st, (uint32_t)in_stage_bytes);
           ptx::tma_load_2d(sIn + st * in_stage_bytes, &tm_in, cb * 64, row0, in_full + 8 * st);
           ++in_cnt;
+          if (p.w_resident && i > 0) continue;       // resident weights were loaded with the first item
           for (int fr = 0; fr < 3; ++fr, ++w_cnt) {   // one filter row (three taps) per weight stage
             const uint32_t ws = w_cnt % (uint32_t)p.w_stages;
             if (!ptx::mbar_wait_cluster_abortable(w_empty + 8 * ws, ((w_cnt / (uint32_t)p.w_stages) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
             ptx::mbar_arrive_expect_tx(w_full + 8 * ws, kWStage);
 #pragma unroll
-            for (int s3 = 0; s3 < kWGroup; ++s3)
-              ptx::bulk_g2s(sW + ws * kWStage + s3 * kWTile, wsrc + ((size_t)(fr * 3 + s3) * p.CB + cb) * kWTile, kWTile,
-                            w_full + 8 * ws);
+            for (int s3 = 0; s3 < kWGroup; ++s3) {
+              const uint8_t* src = wsrc + ((size_t)(fr * 3 + s3) * p.CB + cb) * kPackTile;
+              // never start a copy that would leave the packed weights: report and let the waits run out
+              if ((size_t)(src - p.wpack) + kWTile > p.wpack_bytes || sW + ws * kWStage + (s3 + 1) * kWTile > sStage) {
+                if (p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrBounds);
+                *abort_flag = 1;
+                okw = false;
+                break;
+              }
+              ptx::bulk_g2s(sW + ws * kWStage + s3 * kWTile, src, kWTile, w_full + 8 * ws);
+            }
+            if (!okw) break;
           }
         }
       }
@@ -164,11 +181,14 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
           ptx::tc_fence_after();
           const uint32_t a_stage = sIn + st * in_stage_bytes;
           for (int fr = 0; fr < 3; ++fr, ++w_cnt) {
-            const uint32_t ws = w_cnt % (uint32_t)p.w_stages;
-            const uint32_t wpar = (w_cnt / (uint32_t)p.w_stages) & 1u;
-            if (!ptx::mbar_wait_abortable(w_full + 8 * ws, wpar, abort_flag) ||
-                !ptx::mbar_wait_cluster_abortable(w_peer + 8 * ws, wpar, abort_flag)) { okw = false; break; }
-            ptx::tc_fence_after();
+            // resident: stage cb * 3 + fr, filled once (phase 0)
+            const uint32_t ws = p.w_resident ? (uint32_t)(cb * 3 + fr) : w_cnt % (uint32_t)p.w_stages;
+            const uint32_t wpar = p.w_resident ? 0u : (w_cnt / (uint32_t)p.w_stages) & 1u;
+            if (!p.w_resident || i == 0) {
+              if (!ptx::mbar_wait_abortable(w_full + 8 * ws, wpar, abort_flag) ||
+                  !ptx::mbar_wait_cluster_abortable(w_peer + 8 * ws, wpar, abort_flag)) { okw = false; break; }
+              ptx::tc_fence_after();
+            }
 #pragma unroll
             for (int s3 = 0; s3 < kWGroup; ++s3) {
               const uint32_t a_lo = ptx::smem_desc_k128_lo(a_stage + (uint32_t)(fr * p.P + s3) * 128u);
@@ -179,8 +199,10 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
                                    ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi), idesc,
                                    (cb | fr | s3 | k4) != 0 ? 1u : 0u);
             }
-            ptx::tc_commit_pair(w_empty + 8 * ws);
-            ptx::tc_commit_pair(peer_w_empty + 8 * ws);
+            if (!p.w_resident) {
+              ptx::tc_commit_pair(w_empty + 8 * ws);
+              ptx::tc_commit_pair(peer_w_empty + 8 * ws);
+            }
           }
           if (!okw) break;
           ptx::tc_commit_pair(in_empty + 8 * st);
@@ -207,6 +229,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
           if (!ptx::mbar_wait_abortable(in_full + 8 * st, (in_cnt / (uint32_t)p.in_stages) & 1u, abort_flag)) { okw = false; break; }
           ptx::mbar_arrive_remote(lead_in_peer + 8 * st);
           ++in_cnt;
+          if (p.w_resident && i > 0) continue;
           for (int fr = 0; fr < 3; ++fr, ++w_cnt) {
             const uint32_t ws = w_cnt % (uint32_t)p.w_stages;
             if (!ptx::mbar_wait_abortable(w_full + 8 * ws, (w_cnt / (uint32_t)p.w_stages) & 1u, abort_flag)) { okw = false; break; }
@@ -225,7 +248,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
   ptx::cluster_sync_all();   // the peer's shared memory and barriers stay valid until both are done
   if (warp == 1) {
     __syncwarp();
-    ptx::tmem_dealloc_pair(tmem_base, 512);
+    ptx::tmem_dealloc_pair(tmem_base, 2 * BNP < 32 ? 32 : 2 * BNP);
   }
 }
 

@@ -18,6 +18,7 @@ enum KernelError : int {
   kErrWaitLoader = 2,    // weight loader gave up waiting for a free stage
   kErrWaitMma = 3,       // MMA issuer gave up waiting for a full stage
   kErrWaitEpilogue = 4,  // epilogue gave up waiting for the accumulator
+  kErrBounds = 5,        // a copy would have left its buffer and was not started
 };
 
 // Where pixel (n, y, x) of a logical [N,H,W,C] activation lives: slot

@@ -322,14 +322,14 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
   if (sv_ok || (c->algo == 0 && tc_ok)) {
     auto launch_choice = [&](const ConvChoice& ch, bool profile) -> int {
       const void* wpack = nullptr;
-      int rc = conv_prepare(c, ch.kernel == 7 ? 128 : ch.bn, st, &wpack);
+      int rc = conv_prepare(c, ch.kernel == 7 ? (ch.bn / 2 < 64 ? 64 : ch.bn / 2) : ch.bn, st, &wpack);
       if (rc) return rc;
       if (ch.kernel == 7) {   // CTA-pair shifted-view kernel
         Conv3x3Args a;
         a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
-        a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.Kout = c->Kout; a.ab = c->dtype; a.relu = relu;
+        a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.Kout = c->Kout; a.ab = c->dtype; a.relu = relu; a.bn = ch.bn;
         a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
-        if (profile) prof_begin(7, flops, bytes, (int)M, c->Kout, c->C * 9, 256, st);
+        if (profile) prof_begin(7, flops, bytes, (int)M, c->Kout, c->C * 9, ch.bn, st);
         ++g_launches;
         const cudaError_t e = launch_conv3x3_pair(a, st);
         if (profile) prof_end(st);
@@ -392,7 +392,8 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
           for (int bn : {64, 128, 256})
             for (int mt : {1, 2, 4})
               if (c->Kout % bn == 0 && bn * mt <= 512) cand.push_back(ConvChoice{2, bn, mt, 0});
-          if (c->Kout % 256 == 0 && W <= 62) cand.push_back(ConvChoice{7, 256, 1, 0});   // CTA pairs
+          for (int bn : {64, 128, 256})
+            if (c->Kout % bn == 0 && W <= 62) cand.push_back(ConvChoice{7, bn, 1, 0});   // CTA pairs
         }
         if (tc_ok) {
           for (int bn : {64, 128}) cand.push_back(ConvChoice{5, bn, 1, 1});

@@ -115,6 +115,10 @@ SV_CASES = [
     (5, 512, 7, 7, 512, (256, 1, 2)),
     (9, 128, 28, 28, 256, (256, 1, 2)),
     (1, 64, 8, 8, 256, (256, 1, 2)),
+    (3, 64, 56, 56, 64, (64, 1, 2)),      # pair kernel, N = 64, weights resident
+    (4, 128, 28, 28, 128, (128, 1, 2)),   # N = 128, weights resident
+    (2, 64, 17, 23, 128, (64, 1, 2)),     # two Kout tiles of 64, streamed weights
+    (5, 256, 14, 14, 256, (128, 1, 2)),
     (2, 64, 17, 23, 128, None),      # ragged map, Kout != C
     (1, 192, 5, 3, 64, None),
 ]
