@@ -377,7 +377,10 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
       ch = ConvChoice{5, bn, 1, resident};
     }
     if (fb) {
-      ch = ConvChoice{5, 128, 1, 0};   // the one configuration the fused kernel is built for
+      // N tile 128, weights streamed with the A tiles: resident weights (160 KB for 64 channels) leave
+      // room for two A stages only, too few copies in flight to cover the L2 latency (measured: 92 us
+      // against 80 us on the 64 -> 128 channel block at batch 256)
+      ch = ConvChoice{5, 128, 1, 0};
     } else if (c->cfg3.bn) {
       ch.bn = c->cfg3.bn; ch.mt = c->cfg3.mt > 0 ? c->cfg3.mt : 1; ch.resident = c->cfg3.resident;
       if (c->cfg3.resident == 2 && sv_ok) { ch.kernel = 7; ch.resident = 0; }   // forced CTA-pair kernel

@@ -73,7 +73,6 @@ template <int BN, bool RESIDENT, bool DUAL>
 __global__ void __launch_bounds__(kThreads, 1)
 tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_out,
              const __grid_constant__ CUtensorMap tm_out2, const TcParams p) {
-  static_assert(!DUAL || !RESIDENT, "the fused downsample branch streams its weights");
   constexpr int WTILE = BN * 128;
   constexpr int ACC_W = DUAL ? 2 * BN : BN;   // columns of one accumulator buffer
   constexpr int ACC_COLS = 2 * ACC_W;         // two accumulator buffers
@@ -87,7 +86,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
   const int stage_bytes = RESIDENT ? kABytes : kABytes + WTILE;
   const uint32_t sRing = base;
   const uint32_t sW = sRing + (uint32_t)p.stages * stage_bytes;       // resident weights
-  const uint32_t sStage = sW + (RESIDENT ? (uint32_t)KB * WTILE : 0u);
+  const uint32_t sStage = sW + (RESIDENT ? (uint32_t)(KB + (DUAL ? p.CB : 0)) * WTILE : 0u);   // resident: main tiles, then the branch's
   const uint32_t bars = sStage + 2 * kSlabBytes;
   const uint32_t full = bars, empty = bars + 8 * kMaxStages;
   const uint32_t acc_full = empty + 8 * kMaxStages, acc_empty = acc_full + 16;
@@ -153,8 +152,13 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
     if (lane == 0) {
       if (RESIDENT) {
         const uint8_t* src = p.wpack + (size_t)blockIdx.y * KB * WTILE;
-        ptx::mbar_arrive_expect_tx(w_full, (uint32_t)KB * WTILE);
+        ptx::mbar_arrive_expect_tx(w_full, (uint32_t)(KB + (DUAL ? p.CB : 0)) * WTILE);
         for (int i = 0; i < KB; ++i) ptx::bulk_g2s(sW + (uint32_t)i * WTILE, src + (size_t)i * WTILE, WTILE, w_full);
+        if (DUAL) {
+          const uint8_t* src2 = p.wpack2 + (size_t)blockIdx.y * p.CB * WTILE;
+          for (int i = 0; i < p.CB; ++i)
+            ptx::bulk_g2s(sW + (uint32_t)(KB + i) * WTILE, src2 + (size_t)i * WTILE, WTILE, w_full);
+        }
       }
       uint32_t cnt = 0;
       bool okw = true;
@@ -206,7 +210,8 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
           ptx::tc_fence_after();
           const uint32_t a_addr = sRing + st * stage_bytes;
           const uint32_t a_lo = ptx::smem_desc_k128_lo(a_addr);
-          const uint32_t b_lo = ptx::smem_desc_k128_lo(RESIDENT ? sW + (uint32_t)(tap * p.CB + cb) * WTILE : a_addr + kABytes);
+          const uint32_t b_lo = ptx::smem_desc_k128_lo(
+              RESIDENT ? sW + (uint32_t)(second ? KB + cb : tap * p.CB + cb) * WTILE : a_addr + kABytes);
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4)
             ptx::umma_f16(second ? d + BN : d, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
@@ -411,7 +416,7 @@ cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
   const int KB = p.taps * p.CB;
   const size_t fixed = 1024 + 2 * kSlabBytes + 512;
   const size_t stage = RESIDENT ? kABytes : kABytes + wtile;
-  const size_t wres = RESIDENT ? (size_t)KB * wtile : 0;
+  const size_t wres = RESIDENT ? (size_t)(KB + (DUAL ? p.CB : 0)) * wtile : 0;
   if (fixed + wres + 2 * stage > kSmemLimit) return cudaErrorInvalidConfiguration;
   size_t st = (kSmemLimit - fixed - wres) / stage;
   if (st > kMaxStages) st = kMaxStages;
@@ -509,10 +514,10 @@ cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream) {
   p.stages = 0;
   if (p.residual && p.out_f32) return cudaErrorInvalidValue;
   if (a.wpack2) {   // fused 1x1 stride-s branch on the centre tap: odd square filter, pad = R/2, N tile 128 streamed
-    if (!a.out2 || a.bn != 128 || a.resident || p.out_f32 || a.R != a.S || a.R % 2 == 0 || a.pad != a.R / 2 ||
+    if (!a.out2 || a.bn != 128 || p.out_f32 || a.R != a.S || a.R % 2 == 0 || a.pad != a.R / 2 ||
         a.Kout % 128 != 0 || (reinterpret_cast<uintptr_t>(a.wpack2) & 15) || (reinterpret_cast<uintptr_t>(a.out2) & 15))
       return cudaErrorInvalidValue;
-    return launch_cfg<128, false, true>(a, p, stream);
+    return a.resident ? launch_cfg<128, true, true>(a, p, stream) : launch_cfg<128, false, true>(a, p, stream);
   }
 #define NNCV_TC(BN_, RES_) \
   if (a.bn == BN_ && (a.resident != 0) == RES_) return launch_cfg<BN_, RES_>(a, p, stream);
