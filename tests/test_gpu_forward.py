@@ -162,3 +162,35 @@ def test_logits_do_not_depend_on_the_tile_choice():
     part = torch.zeros((7, 1000), device="cuda")
     rt.forward(part, X[30:37].contiguous())
     assert torch.equal(part, full[30:37])
+
+
+@pytest.mark.gpu
+def test_tuning_decisions_persist_across_processes(tmp_path):
+    """NNCV_B200_TUNE_CACHE: the first process times its candidates and writes its decisions, the
+    second one reads them back, launches far fewer kernels and returns the same logits."""
+    import json
+    import subprocess
+    import sys
+    cache = tmp_path / "tune.txt"
+    prog = (
+        "import sys, json, torch, numpy as np\n"
+        f"sys.path.insert(0, {os.path.dirname(os.path.dirname(os.path.abspath(__file__)))!r})\n"
+        "from nncv_b200 import runtime as rt\n"
+        "from nncv_b200._lib import F16\n"
+        "from nncv_b200.split_params import random_input, random_state_dict, to_flat_array\n"
+        "rt.load_blob('resnet18', to_flat_array(18, random_state_dict(18, 0)).blob(), F16)\n"
+        "X = torch.from_numpy(random_input(8, 64, 64, 5, 'normal')).cuda()\n"
+        "Y = torch.zeros((8, 1000), device='cuda')\n"
+        "rt.forward(Y, X)\n"
+        "print(json.dumps({'launches': rt.launch_count(), 'sum': float(Y.double().sum()), 'max': float(Y.max())}))\n"
+    )
+    env = dict(os.environ, NNCV_B200_TUNE_CACHE=str(cache))
+    outs = []
+    for _ in range(2):
+        r = subprocess.run([sys.executable, "-c", prog], env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        outs.append(json.loads(r.stdout.strip().splitlines()[-1]))
+    lines = cache.read_text().splitlines()
+    assert any(l.startswith("conv ") for l in lines)
+    assert outs[1]["launches"] < outs[0]["launches"]
+    assert outs[0]["sum"] == outs[1]["sum"] and outs[0]["max"] == outs[1]["max"]
