@@ -118,16 +118,17 @@ def test_bad_descriptors_are_rejected_without_touching_dst():
     assert (out == 7.0).all()
 
 
-def test_large_host_batch_is_split_and_matches_device_path():
-    """Host batches of 128 or more run as two halves so the second half's host->device copy overlaps
-    the first half's forward; the logits must equal the unsplit device-resident forward."""
+@pytest.mark.parametrize("n", [128, 256])
+def test_large_host_batch_is_split_and_matches_device_path(n):
+    """Host batches of 128 or more run as two halves so that the second half's host->device copy
+    overlaps the first half's forward; the logits must equal the unsplit device-resident forward."""
     blob = to_flat_array(18, random_state_dict(18, 0)).blob()
     rt.load_blob("resnet18", blob, F16)
-    x = random_input(128, 64, 64, 5, "normal")
-    out_host = np.zeros((128, 1000), np.float32)
+    x = random_input(n, 64, 64, 5, "normal")
+    out_host = np.zeros((n, 1000), np.float32)
     rt.forward(out_host, x)
     X = torch.from_numpy(x).cuda()
-    out_dev = torch.zeros((128, 1000), device="cuda")
+    out_dev = torch.zeros((n, 1000), device="cuda")
     rt.forward(out_dev, X)
     assert G.rel_l2(out_host, out_dev.cpu().numpy()) <= 1e-6
     ref = ob.resnet_forward(18, x[:8], blob)
