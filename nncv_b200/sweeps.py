@@ -84,7 +84,7 @@ def conv(n=32):
                 _flush_fill()
                 call()
             torch.cuda.synchronize()
-            recs = [r for r in rt.profile_records() if r["kind"] in (2, 5, 6)]
+            recs = [r for r in rt.profile_records() if r["kind"] in (2, 5, 6, 7)]
             rt.profile(False)
             ms = sorted(r["ms"] for r in recs)[len(recs) // 2]
             tf = recs[0]["flops"] / ms / 1e9
