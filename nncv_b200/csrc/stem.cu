@@ -123,7 +123,8 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
   const uint32_t full = bars, empty = bars + 8 * kRingSlots;
   const uint32_t acc_full = empty + 8 * kRingSlots, acc_empty = acc_full + 8 * kAcc;
   const uint32_t w_full = acc_empty + 8 * kAcc;
-  const uint32_t tmem_slot = w_full + 8;
+  const uint32_t go = w_full + 8;                 // pair kernel: "everything pair seq needs is there", 4 in flight
+  const uint32_t tmem_slot = go + 8 * 4;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -138,6 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
       ptx::mbar_init(acc_empty + 8 * i, kEpiWarps);
     }
     ptx::mbar_init(w_full, 1);
+    for (int i = 0; i < 4; ++i) ptx::mbar_init(go + 8 * i, 1);
     ptx::mbar_fence_init();
   }
   if (SW && threadIdx.x == 32) ptx::prefetch_tensormap(&tm_in);
@@ -224,29 +226,18 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
         for (int pk = ir0; pk <= ir1 && okw; ++pk, ++seq) {
           const uint32_t slot = seq % kRingSlots;
           ST_TRACE(0, seq, 0);
-          if (!ptx::mbar_wait_abortable(full + 8 * slot, (seq / kRingSlots) & 1u, abort_flag)) { okw = false; break; }
+          // the scout warp has seen the pair's tile arrive, the epilogue move past pair seq - 8 and
+          // the accumulator slots of the rows this pair starts come free
+          if (!ptx::mbar_wait_abortable(go + 8 * (seq & 3u), (seq >> 2) & 1u, abort_flag)) { okw = false; break; }
           ST_TRACE(0, seq, 5);
-          // The commit below completes a phase of empty[slot] that the epilogue may still have to
-          // test for pair seq - 8 (it tests only the pairs that finish a pooling step), so this
-          // pair is held back until the epilogue has moved past that one.  It is never more than
-          // a few pairs behind the pair it waits for, so this cannot block for long.
-          if ((int)seq - (int)kRingSlots > *(volatile int*)&s_consumed) {
-            const long long t0 = clock64();
-            while ((int)seq - (int)kRingSlots > *(volatile int*)&s_consumed) {
-              if (*abort_flag) { okw = false; break; }
-              if (clock64() - t0 > (1LL << 31)) { *abort_flag = 1; okw = false; break; }
-            }
-            if (!okw) break;
-          }
+          ptx::tc_fence_after();
           const uint32_t a_lo = ring_lo + slot * (uint32_t)(kSwSlot >> 4);
           if (pk > ir0 && pk < ir1 && pk - 1 >= y0 && pk + 2 <= y1) {
             // Interior pair, straight-line: rows pk-1 .. pk+1 accumulate (N = 192, or two pieces
             // where the slots wrap), row pk+2 starts (N = 64, accumulate off at the first K step).
             const uint32_t c_lo = rc_base + (uint32_t)(pk - 1 - y0);
             const uint32_t cf = c_lo + 3;
-            if (!ptx::mbar_wait_abortable(acc_empty + 8 * (cf % kAcc), ((cf / kAcc) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
             ST_TRACE(0, seq, 1);
-            ptx::tc_fence_after();
             const uint32_t s0 = c_lo % kAcc;
             if (s0 + 3 <= kAcc) {
 #pragma unroll
@@ -277,13 +268,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
           // rows that get their first partial sum from this pair: all of them for the first pair
           // of the item, else only row pk + 2
           const int fresh_lo = (pk == ir0) ? lo : (pk + 2 <= y1 ? pk + 2 : hi + 1);
-          for (int y = fresh_lo; y <= hi && okw; ++y) {
-            const uint32_t c = rc_base + (uint32_t)(y - y0);
-            if (!ptx::mbar_wait_abortable(acc_empty + 8 * (c % kAcc), ((c / kAcc) & 1u) ^ 1u, abort_flag)) okw = false;
-          }
-          if (!okw) break;
           ST_TRACE(0, seq, 1);
-          ptx::tc_fence_after();
           // rows [a, b] -> consecutive accumulator slots, in two pieces where the slot index wraps:
           // TMEM address, weight descriptor (low word) and instruction descriptor of each piece
           auto split = [&](int a, int b, uint32_t (&d)[2], uint32_t (&bl)[2], uint32_t (&id)[2]) -> int {
@@ -322,6 +307,47 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
           ST_TRACE(0, seq, 2);
           ptx::tc_commit(empty + 8 * slot);
           ST_TRACE(0, seq, 3);
+        }
+        rc_base += (uint32_t)(y1 - y0 + 1);
+      }
+      if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitMma);
+    }
+  } else if (SW && warp == kIssuerBWarp) {
+    // ---------------------------------------------------------------- scout (pairs) -------
+    // Does the issuing lane's waiting for it, up to four pairs ahead: the issuer then tests one
+    // barrier per pair and spends its instructions on MMAs (a lone lane runs ~10 clocks per
+    // instruction, and the tensor pipe idles while it does anything else).
+    if (lane == 0) {
+      uint32_t seq = 0, rc_base = 0;
+      bool okw = true;
+      for (int i = 0; okw; ++i) {
+        int n, p0, p1, y0, y1, ir0, ir1;
+        if (!item_of(i, n, p0, p1, y0, y1, ir0, ir1)) break;
+        for (int pk = ir0; pk <= ir1 && okw; ++pk, ++seq) {
+          // go[seq & 3] is free again once the MMAs of pair seq - 4 are done (the issuer has long passed it)
+          if (seq >= 4 && !ptx::mbar_wait_abortable(empty + 8 * ((seq - 4) % kRingSlots), ((seq - 4) / kRingSlots) & 1u, abort_flag)) { okw = false; break; }
+          if (!ptx::mbar_wait_abortable(full + 8 * (seq % kRingSlots), (seq / kRingSlots) & 1u, abort_flag)) { okw = false; break; }
+          // The issuer's commit completes a phase of empty[slot] that the epilogue may still have to
+          // test for pair seq - 8 (it tests only the pairs that finish a pooling step), so the pair
+          // is held back until the epilogue has moved past that one.  It is never more than a few
+          // pairs behind the pair it waits for, so this cannot block for long.
+          if ((int)seq - (int)kRingSlots > *(volatile int*)&s_consumed) {
+            const long long t0 = clock64();
+            while ((int)seq - (int)kRingSlots > *(volatile int*)&s_consumed) {
+              if (*abort_flag) { okw = false; break; }
+              if (clock64() - t0 > (1LL << 31)) { *abort_flag = 1; okw = false; break; }
+            }
+            if (!okw) break;
+          }
+          // accumulator slots of the rows that get their first partial sum from this pair
+          const int lo = max(y0, pk - 1), hi = min(y1, pk + 2);
+          const int fresh_lo = (pk == ir0) ? lo : (pk + 2 <= y1 ? pk + 2 : hi + 1);
+          for (int y = fresh_lo; y <= hi && okw; ++y) {
+            const uint32_t c = rc_base + (uint32_t)(y - y0);
+            if (!ptx::mbar_wait_abortable(acc_empty + 8 * (c % kAcc), ((c / kAcc) & 1u) ^ 1u, abort_flag)) okw = false;
+          }
+          if (!okw) break;
+          ptx::mbar_arrive(go + 8 * (seq & 3u));
         }
         rc_base += (uint32_t)(y1 - y0 + 1);
       }
@@ -864,7 +890,7 @@ cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream) {
   p.band_rows = band_rows;
   p.bands = (p.PH + band_rows - 1) / band_rows;
   const size_t smem = 1024 + p.w_bytes + (size_t)kRingSlots * p.slot_bytes + 256 +
-                      (size_t)kConvRing * p.x_tiles * 128 * 128 + 8 + 8 * (2 * kRingSlots + 4 * kAccBufs + 1) + 16;
+                      (size_t)kConvRing * p.x_tiles * 128 * 128 + 8 + 8 * (2 * kRingSlots + 4 * kAccBufs + 1 + 4) + 16;
   if (smem > 227 * 1024) return cudaErrorInvalidConfiguration;
   if (p.x_tiles > 2) return cudaErrorInvalidConfiguration;   // wider than 512 pixels: not covered by the fused kernel
   auto kern = sw ? stem_pool_kernel<1, true> : p.x_tiles == 1 ? stem_pool_kernel<1, false> : stem_pool_kernel<2, false>;
