@@ -284,16 +284,18 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       ncol = n_tile * BN + sl * 64;
       return true;
     };
-    // residual of the first slab (later slabs are fetched one slab ahead inside the loop)
-    uint32_t res_cur[2][8];
-    bool have_cur = false;
+    // residual of the first slab (later slabs are fetched one slab ahead inside the loop).  Two
+    // register sets alternate between "in use" and "in flight": copying one into the other at the
+    // end of a slab would make every slab wait for the loads it has just issued.
+    uint32_t res_a[2][8], res_b[2][8];
+    bool have_a = false, have_b = false;
     if (p.has_res) {
       int q_tile, ncol;
       if (slab_of(0, q_tile, ncol) && q_tile + row < p.T) {
-        have_cur = true;
+        have_a = true;
         const uint16_t* rp = p.residual + ((size_t)(q_tile + row) * p.Kout + ncol + half * 32);
-        ptx::ldg_256(rp, res_cur[0]);
-        ptx::ldg_256(rp + 16, res_cur[1]);
+        ptx::ldg_256(rp, res_a[0]);
+        ptx::ldg_256(rp + 16, res_a[1]);
       }
     }
     if (p.has_res) {
@@ -305,9 +307,10 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     }
     uint32_t acc_cnt = 0;
     bool okw = true;
-    for (int j = 0; okw; ++j) {
+    // one slab; returns false when the loop is over (no more slabs, or a wait gave up: okw false)
+    auto do_slab = [&](int j, uint32_t (&res_cur)[2][8], bool& have_cur, uint32_t (&res_next)[2][8], bool& have_next) -> bool {
       int q_tile, ncol;
-      if (!slab_of(j, q_tile, ncol)) break;
+      if (!slab_of(j, q_tile, ncol)) return false;
       const int rem = j % SPI;
       const int t = rem / SLABS, sl = rem - t * SLABS;
       const uint32_t sb = (uint32_t)j & 1u;
@@ -332,7 +335,7 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       if (rem == 0) got = ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt / AB) & 1u, abort_flag);
       if (elected) C3_TRACE(2, j, 1);
       // all epilogue threads take the same exit: nobody is left alone at a named barrier
-      if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; break; }
+      if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; return false; }
       if (elected) C3_TRACE(2, j, 2);
       ptx::tc_fence_after();
       const uint32_t srow = sStage + sb * kSlabBytes + (uint32_t)row * 128u;
@@ -341,8 +344,7 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       __syncwarp();
       ptx::tmem_ld_32x32(t_addr + half * 32, acc);
       // residual of the next slab: in flight while this slab is converted and stored
-      uint32_t res_next[2][8];
-      bool have_next = false;
+      have_next = false;
       if (p.has_res) {
         int qn, nn;
         if (slab_of(j + 1, qn, nn)) {
@@ -410,11 +412,6 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         }
         asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
       }
-      if (p.has_res) {
-        have_cur = have_next;
-#pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) res_cur[c4 >> 3][c4 & 7] = res_next[c4 >> 3][c4 & 7];
-      }
       if (elected) C3_TRACE(2, j, 4);
       ptx::fence_proxy_async_smem();
       ptx::named_bar_sync(1, kEpiThreads);
@@ -426,6 +423,11 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       }
       if (elected) C3_TRACE(2, j, 6);
       ptx::named_bar_sync(2, kEpiThreads);  // the other staging buffer is free for everyone
+      return true;
+    };
+    for (int j = 0;; j += 2) {
+      if (!do_slab(j, res_a, have_a, res_b, have_b)) break;
+      if (!do_slab(j + 1, res_b, have_b, res_a, have_a)) break;
     }
     if (elected) ptx::bulk_wait<0>();
     if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitEpilogue);
