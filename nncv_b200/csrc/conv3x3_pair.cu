@@ -9,7 +9,8 @@
 //
 // Synchronisation (all barriers live at the same shared-memory offsets in both CTAs):
 //   in_full / w_full    local TMA completion in each CTA; the peer CTA's idle MMA warp relays each
-//                       completion to the leader's in_peer / w_peer barriers with a remote arrive.
+//                       completion to the LEADER's in_full / w_full with a remote arrive (those expect
+//                       two arrivals), so the issuing lane tests one barrier per stage.
 //   in_empty / w_empty  the leader commits its MMAs to the local AND (mapped address) the peer's
 //                       barrier, so both producers reuse the stage.
 //   acc_full            committed to both CTAs; acc_empty (leader) collects one arrive per CTA.
@@ -46,6 +47,10 @@ struct PairParams {
   int box_rows, in_stages, w_stages;
   int w_resident;            // all 3 * CB weight stages stay in shared memory (one Kout tile only)
   unsigned long long wpack_bytes;   // size of the packed weights (copies are range-checked against it)
+  // Tail of the item list: the items of the last, partly filled round are split into tail_parts
+  // column slices (BNP / tail_parts columns each) that run on different pairs at the same time.
+  // Items [0, tail_start) are whole; tail_start is a multiple of the number of pairs.
+  int tail_start, tail_parts;
   int relu, has_res, bf16;
 };
 
@@ -78,12 +83,12 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int i = 0; i < kMaxIn; ++i) {
-      ptx::mbar_init(in_full + 8 * i, 1);
+      ptx::mbar_init(in_full + 8 * i, rank == 0 ? 2 : 1);   // leader: own copy + the peer's relay
       ptx::mbar_init(in_empty + 8 * i, 1);
       ptx::mbar_init(in_peer + 8 * i, 1);
     }
     for (int i = 0; i < kMaxW; ++i) {
-      ptx::mbar_init(w_full + 8 * i, 1);
+      ptx::mbar_init(w_full + 8 * i, rank == 0 ? 2 : 1);
       ptx::mbar_init(w_empty + 8 * i, 1);
       ptx::mbar_init(w_peer + 8 * i, 1);
     }
@@ -110,8 +115,17 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
 
   const int pairs = (int)gridDim.x >> 1, pair = (int)blockIdx.x >> 1;
   const int total_items = p.m_items * p.n_tiles;
-  auto item_of = [&](int i, int& m_item, int& n_tile) {
-    const int w = pair + i * pairs;
+  const int full_rounds = p.tail_start / pairs;   // whole items every pair processes before the tail
+  // item i of this pair -> pixel tile, Kout tile, column slice `sub` of `parts`
+  auto item_of = [&](int i, int& m_item, int& n_tile, int& sub, int& parts) {
+    int w = pair + i * pairs;
+    sub = 0; parts = 1;
+    if (i >= full_rounds && p.tail_parts > 1) {
+      if (i > full_rounds) return false;          // at most one slice per pair
+      parts = p.tail_parts;
+      w = p.tail_start + pair / parts;
+      sub = pair - (pair / parts) * parts;
+    }
     m_item = w / p.n_tiles;
     n_tile = w - m_item * p.n_tiles;
     return w < total_items;
@@ -123,11 +137,13 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
       uint32_t in_cnt = 0, w_cnt = 0;
       bool okw = true;
       for (int i = 0; okw; ++i) {
-        int m_item, n_tile;
-        if (!item_of(i, m_item, n_tile)) break;
+        int m_item, n_tile, sub, parts;
+        if (!item_of(i, m_item, n_tile, sub, parts)) break;
         const int row0 = m_item * 256 + (int)rank * 128 - p.P - 1;
-        // this CTA's rows [n_tile * BNP + rank * BNP/2, + BNP/2) inside the packed N tiles
-        const int wrow = n_tile * BNP + (int)rank * (BNP / 2);
+        // this CTA's half of the item's columns, as rows of the packed N tiles
+        const int ncols = BNP / parts;
+        const int wrow = n_tile * BNP + sub * ncols + (int)rank * (ncols / 2);
+        const uint32_t wbytes = (uint32_t)(ncols / 2) * 128u;   // per tap
         const uint8_t* wsrc = p.wpack + (size_t)(wrow / kPackBN) * kb_total * kPackTile + (size_t)(wrow % kPackBN) * 128;
         for (int cb = 0; cb < p.CB && okw; ++cb) {
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
@@ -139,18 +155,18 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
           for (int fr = 0; fr < 3; ++fr, ++w_cnt) {   // one filter row (three taps) per weight stage
             const uint32_t ws = w_cnt % (uint32_t)p.w_stages;
             if (!ptx::mbar_wait_cluster_abortable(w_empty + 8 * ws, ((w_cnt / (uint32_t)p.w_stages) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
-            ptx::mbar_arrive_expect_tx(w_full + 8 * ws, kWStage);
+            ptx::mbar_arrive_expect_tx(w_full + 8 * ws, kWGroup * wbytes);
 #pragma unroll
             for (int s3 = 0; s3 < kWGroup; ++s3) {
               const uint8_t* src = wsrc + ((size_t)(fr * 3 + s3) * p.CB + cb) * kPackTile;
               // never start a copy that would leave the packed weights: report and let the waits run out
-              if ((size_t)(src - p.wpack) + kWTile > p.wpack_bytes || sW + ws * kWStage + (s3 + 1) * kWTile > sStage) {
+              if ((size_t)(src - p.wpack) + wbytes > p.wpack_bytes || sW + ws * kWStage + (s3 + 1) * kWTile > sStage) {
                 if (p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrBounds);
                 *abort_flag = 1;
                 okw = false;
                 break;
               }
-              ptx::bulk_g2s(sW + ws * kWStage + s3 * kWTile, src, kWTile, w_full + 8 * ws);
+              ptx::bulk_g2s(sW + ws * kWStage + s3 * kWTile, src, wbytes, w_full + 8 * ws);
             }
             if (!okw) break;
           }
@@ -161,14 +177,15 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       // ---------------------------------------------------------------- MMA issuer (leader) --
-      const uint32_t idesc = ptx::umma_idesc(256, kBNPair, p.bf16 ? 1 : 0);
+      const uint32_t idesc_full = ptx::umma_idesc(256, kBNPair, p.bf16 ? 1 : 0);
       const uint32_t peer_in_empty = ptx::map_to_cta(in_empty, 1), peer_w_empty = ptx::map_to_cta(w_empty, 1);
       const uint32_t peer_acc_full = ptx::map_to_cta(acc_full, 1);
       uint32_t in_cnt = 0, w_cnt = 0, acc_cnt = 0;
       bool okw = true;
       for (int i = 0; okw; ++i) {
-        int m_item, n_tile;
-        if (!item_of(i, m_item, n_tile)) break;
+        int m_item, n_tile, sub, parts;
+        if (!item_of(i, m_item, n_tile, sub, parts)) break;
+        const uint32_t idesc = parts == 1 ? idesc_full : ptx::umma_idesc(256, kBNPair / parts, p.bf16 ? 1 : 0);
         const uint32_t ab = acc_cnt & 1u;
         if (!ptx::mbar_wait_cluster_abortable(acc_empty + 8 * ab, ((acc_cnt >> 1) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
         ptx::tc_fence_after();
@@ -176,8 +193,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
         for (int cb = 0; cb < p.CB && okw; ++cb) {
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
           const uint32_t ipar = (in_cnt / (uint32_t)p.in_stages) & 1u;
-          if (!ptx::mbar_wait_abortable(in_full + 8 * st, ipar, abort_flag) ||
-              !ptx::mbar_wait_cluster_abortable(in_peer + 8 * st, ipar, abort_flag)) { okw = false; break; }
+          if (!ptx::mbar_wait_cluster_abortable(in_full + 8 * st, ipar, abort_flag)) { okw = false; break; }
           ptx::tc_fence_after();
           const uint32_t a_stage = sIn + st * in_stage_bytes;
           for (int fr = 0; fr < 3; ++fr, ++w_cnt) {
@@ -185,8 +201,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
             const uint32_t ws = p.w_resident ? (uint32_t)(cb * 3 + fr) : w_cnt % (uint32_t)p.w_stages;
             const uint32_t wpar = p.w_resident ? 0u : (w_cnt / (uint32_t)p.w_stages) & 1u;
             if (!p.w_resident || i == 0) {
-              if (!ptx::mbar_wait_abortable(w_full + 8 * ws, wpar, abort_flag) ||
-                  !ptx::mbar_wait_cluster_abortable(w_peer + 8 * ws, wpar, abort_flag)) { okw = false; break; }
+              if (!ptx::mbar_wait_cluster_abortable(w_full + 8 * ws, wpar, abort_flag)) { okw = false; break; }
               ptx::tc_fence_after();
             }
 #pragma unroll
@@ -218,12 +233,12 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
     } else if (lane == 0) {
       // ---------------------------------------------------------------- relay (peer CTA) ----
       // Tells the leader when this CTA's stages are full.
-      const uint32_t lead_in_peer = ptx::map_to_cta(in_peer, 0), lead_w_peer = ptx::map_to_cta(w_peer, 0);
+      const uint32_t lead_in_peer = ptx::map_to_cta(in_full, 0), lead_w_peer = ptx::map_to_cta(w_full, 0);
       uint32_t in_cnt = 0, w_cnt = 0;
       bool okw = true;
       for (int i = 0; okw; ++i) {
-        int m_item, n_tile;
-        if (!item_of(i, m_item, n_tile)) break;
+        int m_item, n_tile, sub, parts;
+        if (!item_of(i, m_item, n_tile, sub, parts)) break;
         for (int cb = 0; cb < p.CB && okw; ++cb) {
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
           if (!ptx::mbar_wait_abortable(in_full + 8 * st, (in_cnt / (uint32_t)p.in_stages) & 1u, abort_flag)) { okw = false; break; }

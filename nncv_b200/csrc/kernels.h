@@ -77,6 +77,7 @@ struct Conv3x3Args {
   void* out = nullptr;
   int N = 0, H = 0, W = 0, C = 0, Kout = 0;
   int bn = 64, mt = 1, resident = 0;
+  int tail_split = 1;              // CTA-pair kernel: slice the items of a mostly empty last round by columns
   DType ab = kF16;
   int relu = 0;
   int sm_count = 0;
