@@ -56,21 +56,48 @@ class ClockSampler:
         self.proc = None
 
     def start(self):
+        """Starts nvidia-smi and a thread that collects its lines (NVML start-up can take longer than a
+        short timed region, so callers start it before the warm-up and wait for the first sample)."""
+        import threading
+        self.lines = []
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                           "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
+            return
+
+        def pump():
+            try:
+                for line in self.proc.stdout:
+                    self.lines.append(line)
+            except Exception:
+                pass
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def wait_ready(self, timeout=10.0):
+        t0 = time.perf_counter()
+        while self.proc is not None and not self.lines and time.perf_counter() - t0 < timeout:
+            time.sleep(0.005)
+
+    def mark(self):
+        """Samples before this point (start-up, warm-up) are dropped."""
+        self.skip = len(getattr(self, "lines", []))
+
+    def count(self):
+        return len(getattr(self, "lines", [])) - getattr(self, "skip", 0)
 
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-            out = ""
+        self.thread.join(timeout=2)
+        out = "".join(self.lines[getattr(self, "skip", 0):])
         sm, smax, reasons = [], [], set()
         for line in out.splitlines():
             f = [x.strip() for x in line.split(",")]
@@ -205,12 +232,16 @@ def run_ours(args):
 
     with torch.cuda.stream(stream):
         rt.set_stream(sptr, True)
-        for _ in range(max(args.warmup, 3)):
-            step_device()
-        barrier()
         sampler = ClockSampler(range(world)) if rank == 0 else None
         if sampler:
             sampler.start()
+        for _ in range(max(args.warmup, 3)):
+            step_device()
+        if sampler:
+            sampler.wait_ready()
+        barrier()
+        if sampler:
+            sampler.mark()
         l0 = rt.launch_count()
         ms_dev = timed(step_device, args.steps)
         launches = rt.launch_count() - l0
@@ -220,7 +251,24 @@ def run_ours(args):
         barrier()
         ms_e2e = timed(step_host, args.steps)
         barrier()
+        # Timed regions shorter than a few sampling periods (20 ms each) leave too few clock samples:
+        # keep running the same device step, untimed, until about ten periods have passed.
+        t_extra = time.perf_counter()
+        n_extra = 0
+        short = ms_dev + ms_e2e < 400.0   # both timed regions together, in ms
+        while world == 1 and short and sampler and sampler.count() < 10 and time.perf_counter() - t_extra < 0.25:
+            step_device()
+            torch.cuda.synchronize()
+            n_extra += 1
+        if world > 1:   # every rank runs the same number of extra steps (they contain a collective)
+            n_extra = min(2000, max(0, int(250.0 / max(ms_dev / args.steps, 0.05)))) if short else 0
+            for _ in range(n_extra):
+                step_device()
+            torch.cuda.synchronize()
+            barrier()
         clocks = sampler.stop() if sampler else None
+        if clocks is not None:
+            clocks["extra_untimed_steps_sampled"] = n_extra
 
         # per-kernel attribution of one step (events around every launch), after the timed regions
         prof = []
