@@ -43,8 +43,10 @@ struct PairParams {
   const float* shift;
   const uint16_t* residual;
   int* error_flag;
-  int T, P, Himg, CB, Kout, n_tiles, m_items;   // m_items of 256 slots
-  int box_rows, in_stages, w_stages;
+  int T, P, Himg, CB, Kout, n_tiles, m_items;   // m_items of mt * 256 slots
+  int mt;                    // sub-tiles of 256 slots per item: every weight stage feeds mt times the MMAs
+  int box_rows, n_boxes;     // a CTA's halo tile (mt * 128 + 2P + 2 rows) arrives as n_boxes TMA boxes
+  int in_stages, w_stages;
   int w_resident;            // all 3 * CB weight stages stay in shared memory (one Kout tile only)
   unsigned long long wpack_bytes;   // size of the packed weights (copies are range-checked against it)
   // Tail of the item list: the items of the last, partly filled round are split into tail_parts
@@ -54,11 +56,12 @@ struct PairParams {
   int relu, has_res, bf16;
 };
 
-template <int BNP>   // columns of the pair's tile: 64, 128 or 256
+template <int BNP, int MT>   // columns of the pair's tile (64, 128 or 256), sub-tiles of 256 slots per item
 __global__ void __launch_bounds__(kThreads, 1)
 conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_out,
                     const PairParams p) {
   constexpr int kBNPair = BNP;
+  constexpr int kMT = MT;
   constexpr int kWTile = (BNP / 2) * 128;          // this CTA's half of a weight tile
   constexpr int kWStage = kWGroup * kWTile;
   constexpr int kPackBN = BNP / 2 < 64 ? 64 : BNP / 2;   // N tile of the packed weights
@@ -67,7 +70,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
   __shared__ int s_abort;
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
-  const int in_stage_bytes = p.box_rows * 128;
+  const int in_stage_bytes = p.box_rows * p.n_boxes * 128;
   const int kb_total = 9 * p.CB;
   const uint32_t sIn = base;
   const uint32_t sW = sIn + (uint32_t)p.in_stages * in_stage_bytes;
@@ -101,7 +104,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
     ptx::prefetch_tensormap(&tm_out);
   }
   if (warp == 1) {
-    ptx::tmem_alloc_pair(tmem_slot, 2 * BNP < 32 ? 32 : 2 * BNP);
+    ptx::tmem_alloc_pair(tmem_slot, (uint32_t)(2 * BNP * MT));
     ptx::tmem_relinquish_pair();
   }
   ptx::tc_fence_before();
@@ -122,12 +125,13 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
     sub = 0; parts = 1;
     if (i >= full_rounds && p.tail_parts > 1) {
       if (i > full_rounds) return false;          // at most one slice per pair
-      parts = p.tail_parts;
-      w = p.tail_start + pair / parts;
-      sub = pair - (pair / parts) * parts;
+      parts = p.tail_parts;                       // 2 or 4
+      const int plog = parts == 2 ? 1 : 2;
+      w = p.tail_start + (pair >> plog);
+      sub = pair & (parts - 1);
     }
-    m_item = w / p.n_tiles;
-    n_tile = w - m_item * p.n_tiles;
+    if (p.n_tiles == 1) { m_item = w; n_tile = 0; }
+    else { m_item = w / p.n_tiles; n_tile = w - m_item * p.n_tiles; }
     return w < total_items;
   };
 
@@ -139,7 +143,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
       for (int i = 0; okw; ++i) {
         int m_item, n_tile, sub, parts;
         if (!item_of(i, m_item, n_tile, sub, parts)) break;
-        const int row0 = m_item * 256 + (int)rank * 128 - p.P - 1;
+        // the leader owns the first mt * 128 slots of the item, the peer the rest: sub-tile t is rows
+        // [t * 128, +128) of both CTAs' tiles
+        const int row0 = (m_item * 2 + (int)rank) * 128 * MT - p.P - 1;
         // this CTA's half of the item's columns, as rows of the packed N tiles
         const int ncols = BNP / parts;
         const int wrow = n_tile * BNP + sub * ncols + (int)rank * (ncols / 2);
@@ -149,7 +155,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
           if (!ptx::mbar_wait_cluster_abortable(in_empty + 8 * st, ((in_cnt / (uint32_t)p.in_stages) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
           ptx::mbar_arrive_expect_tx(in_full + 8 * st, (uint32_t)in_stage_bytes);
-          ptx::tma_load_2d(sIn + st * in_stage_bytes, &tm_in, cb * 64, row0, in_full + 8 * st);
+          for (int bx = 0; bx < p.n_boxes; ++bx)
+            ptx::tma_load_2d(sIn + st * in_stage_bytes + (uint32_t)(bx * p.box_rows) * 128u, &tm_in, cb * 64,
+                             row0 + bx * p.box_rows, in_full + 8 * st);
           ++in_cnt;
           if (p.w_resident && i > 0) continue;       // resident weights were loaded with the first item
           for (int fr = 0; fr < 3; ++fr, ++w_cnt) {   // one filter row (three taps) per weight stage
@@ -189,7 +197,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
         const uint32_t ab = acc_cnt & 1u;
         if (!ptx::mbar_wait_cluster_abortable(acc_empty + 8 * ab, ((acc_cnt >> 1) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
         ptx::tc_fence_after();
-        const uint32_t d = tmem_base + ab * kBNPair;
+        const uint32_t d = tmem_base + ab * (uint32_t)(kBNPair * MT);
         for (int cb = 0; cb < p.CB && okw; ++cb) {
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
           const uint32_t ipar = (in_cnt / (uint32_t)p.in_stages) & 1u;
@@ -205,14 +213,17 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
               ptx::tc_fence_after();
             }
 #pragma unroll
-            for (int s3 = 0; s3 < kWGroup; ++s3) {
-              const uint32_t a_lo = ptx::smem_desc_k128_lo(a_stage + (uint32_t)(fr * p.P + s3) * 128u);
-              const uint32_t b_lo = ptx::smem_desc_k128_lo(sW + ws * kWStage + s3 * kWTile);
+            for (int t = 0; t < MT; ++t) {   // the stage's three weight tiles serve every sub-tile
 #pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4)
-                ptx::umma_f16_pair(d, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
-                                   ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi), idesc,
-                                   (cb | fr | s3 | k4) != 0 ? 1u : 0u);
+              for (int s3 = 0; s3 < kWGroup; ++s3) {
+                const uint32_t a_lo = ptx::smem_desc_k128_lo(a_stage + (uint32_t)(t * 128 + fr * p.P + s3) * 128u);
+                const uint32_t b_lo = ptx::smem_desc_k128_lo(sW + ws * kWStage + s3 * kWTile);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4)
+                  ptx::umma_f16_pair(d + (uint32_t)(t * kBNPair), ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
+                                     ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi), idesc,
+                                     (cb | fr | s3 | k4) != 0 ? 1u : 0u);
+              }
             }
             if (!p.w_resident) {
               ptx::tc_commit_pair(w_empty + 8 * ws);
@@ -263,7 +274,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
   ptx::cluster_sync_all();   // the peer's shared memory and barriers stay valid until both are done
   if (warp == 1) {
     __syncwarp();
-    ptx::tmem_dealloc_pair(tmem_base, 2 * BNP < 32 ? 32 : 2 * BNP);
+    ptx::tmem_dealloc_pair(tmem_base, (uint32_t)(2 * BNP * MT));
   }
 }
 

@@ -372,9 +372,10 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
         Conv3x3Args a;
         a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
         a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.Kout = c->Kout; a.ab = c->dtype; a.relu = relu; a.bn = ch.bn;
+        a.mt = ch.mt;
         a.tail_split = ch.resident;   // for this kernel the field says whether the last round is sliced by columns
         a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
-        if (profile) prof_begin(7, flops, bytes, (int)M, c->Kout, c->C * 9, ch.bn, st);
+        if (profile) prof_begin(7, flops, bytes, (int)M, c->Kout, c->C * 9, ch.bn * 100 + ch.mt * 10 + ch.resident, st);
         ++g_launches;
         const cudaError_t e = launch_conv3x3_pair(a, st);
         if (profile) prof_end(st);
@@ -452,9 +453,12 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
             for (int mt : {1, 2, 4})
               if (c->Kout % bn == 0 && bn * mt <= 512) cand.push_back(ConvChoice{2, bn, mt, 0});
           for (int bn : {64, 128, 256})
-            if (c->Kout % bn == 0 && W <= 62) {   // CTA pairs, without and with the sliced last round
-              cand.push_back(ConvChoice{7, bn, 1, 0});
-              if (bn >= 128) cand.push_back(ConvChoice{7, bn, 1, 1});
+            if (c->Kout % bn == 0) {   // CTA pairs: sub-tiles per item, without and with the sliced last round
+              for (int mt : {1, 2, 4}) {
+                if (2 * bn * mt > 512) continue;
+                cand.push_back(ConvChoice{7, bn, mt, 0});
+                if (bn >= 128) cand.push_back(ConvChoice{7, bn, mt, 1});
+              }
             }
         }
         if (tc_ok) {

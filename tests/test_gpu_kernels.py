@@ -119,6 +119,9 @@ SV_CASES = [
     (4, 128, 28, 28, 128, (128, 1, 2)),   # N = 128, weights resident
     (2, 64, 17, 23, 128, (64, 1, 2)),     # two Kout tiles of 64, streamed weights
     (5, 256, 14, 14, 256, (128, 1, 2)),
+    (7, 256, 14, 14, 256, (128, 2, 2)),     # two sub-tiles of 256 slots per item, halo tile in two TMA boxes
+    (3, 64, 56, 56, 64, (64, 4, 2)),
+    (40, 128, 28, 28, 256, (128, 2, 3)),
     (100, 256, 14, 14, 256, (256, 1, 3)),   # 88 items on 74 pairs: the 14 of the last round run as 4 column slices each
     (84, 128, 14, 14, 256, (128, 1, 3)),    # 148 items: two full rounds, nothing to slice
     (90, 128, 14, 14, 256, (128, 1, 3)),    # 160 items: the last 12 run as two 64-column halves each
