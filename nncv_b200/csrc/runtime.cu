@@ -890,6 +890,12 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
   prof_begin(3, 0, aes * m.spec.fc_in * N * (h * w + 1.0), N * h * w, m.spec.fc_in, 0, 2, st);
   LAUNCH(launch_avgpool_nhwc(x, m.pooled.p, adt, N, h, w, m.spec.fc_in, lay(h, w), st));
   prof_end(st);
+  if (m.io_dt == adt && adt != kF32) {
+    // 16-bit logits wanted and computed in the same type: the FC epilogue rounds once, exactly as
+    // the fp32 -> io conversion kernel would, and that kernel is not launched
+    return conv_run(m.fc.get(), m.pooled.p, dense_layout(1, 1), m.logits_io.p, dense_layout(1, 1), N, 1, 1, nullptr,
+                    (const float*)m.fc_bias.p, nullptr, 0, adt, 1000, st);
+  }
   rc = conv_run(m.fc.get(), m.pooled.p, dense_layout(1, 1), m.logits32.p, dense_layout(1, 1), N, 1, 1, nullptr,
                 (const float*)m.fc_bias.p, nullptr, 0, kF32, 1000, st);
   if (rc) return rc;
