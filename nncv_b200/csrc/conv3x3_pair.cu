@@ -76,9 +76,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
   const uint32_t sW = sIn + (uint32_t)p.in_stages * in_stage_bytes;
   const uint32_t sStage = sW + (uint32_t)p.w_stages * kWStage;
   const uint32_t bars = sStage + 2 * kSlabBytes;
-  const uint32_t in_full = bars, in_empty = in_full + 8 * kMaxIn, in_peer = in_empty + 8 * kMaxIn;
-  const uint32_t w_full = in_peer + 8 * kMaxIn, w_empty = w_full + 8 * kMaxW, w_peer = w_empty + 8 * kMaxW;
-  const uint32_t acc_full = w_peer + 8 * kMaxW, acc_empty = acc_full + 16;
+  const uint32_t in_full = bars, in_empty = in_full + 8 * kMaxIn;
+  const uint32_t w_full = in_empty + 8 * kMaxIn, w_empty = w_full + 8 * kMaxW;
+  const uint32_t acc_full = w_empty + 8 * kMaxW, acc_empty = acc_full + 16;
   const uint32_t tmem_slot = acc_empty + 16;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,12 +88,10 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
     for (int i = 0; i < kMaxIn; ++i) {
       ptx::mbar_init(in_full + 8 * i, rank == 0 ? 2 : 1);   // leader: own copy + the peer's relay
       ptx::mbar_init(in_empty + 8 * i, 1);
-      ptx::mbar_init(in_peer + 8 * i, 1);
     }
     for (int i = 0; i < kMaxW; ++i) {
       ptx::mbar_init(w_full + 8 * i, rank == 0 ? 2 : 1);
       ptx::mbar_init(w_empty + 8 * i, 1);
-      ptx::mbar_init(w_peer + 8 * i, 1);
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(acc_full + 8 * i, 1);
@@ -244,7 +242,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
     } else if (lane == 0) {
       // ---------------------------------------------------------------- relay (peer CTA) ----
       // Tells the leader when this CTA's stages are full.
-      const uint32_t lead_in_peer = ptx::map_to_cta(in_full, 0), lead_w_peer = ptx::map_to_cta(w_full, 0);
+      const uint32_t lead_in_full = ptx::map_to_cta(in_full, 0), lead_w_full = ptx::map_to_cta(w_full, 0);
       uint32_t in_cnt = 0, w_cnt = 0;
       bool okw = true;
       for (int i = 0; okw; ++i) {
@@ -253,13 +251,13 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
         for (int cb = 0; cb < p.CB && okw; ++cb) {
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
           if (!ptx::mbar_wait_abortable(in_full + 8 * st, (in_cnt / (uint32_t)p.in_stages) & 1u, abort_flag)) { okw = false; break; }
-          ptx::mbar_arrive_remote(lead_in_peer + 8 * st);
+          ptx::mbar_arrive_remote(lead_in_full + 8 * st);
           ++in_cnt;
           if (p.w_resident && i > 0) continue;
           for (int fr = 0; fr < 3; ++fr, ++w_cnt) {
             const uint32_t ws = w_cnt % (uint32_t)p.w_stages;
             if (!ptx::mbar_wait_abortable(w_full + 8 * ws, (w_cnt / (uint32_t)p.w_stages) & 1u, abort_flag)) { okw = false; break; }
-            ptx::mbar_arrive_remote(lead_w_peer + 8 * ws);
+            ptx::mbar_arrive_remote(lead_w_full + 8 * ws);
           }
         }
       }

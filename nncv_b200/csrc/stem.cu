@@ -9,26 +9,30 @@
 // Input format: the NCHW image is first rewritten (nchw_to_stem_rows) as fp16 rows of
 // 4-channel pixels with 4 zero pixels on the left and >= 4 on the right:
 //     row(n, y) = [0 0 0 0 | p(0) ... p(W-1) | 0 0 0 0 ...],   p = (c0, c1, c2, 0),  8 bytes each.
-// With this layout the A operand of the implicit GEMM needs no im2col at all.  tcgen05.mma's
-// un-swizzled K-major operand layout addresses element (row i, 16-byte chunk j) at
-//     start + (i % 8) * 16 + (i / 8) * SBO + j * LBO .
+// With this layout the A operand of the implicit GEMM needs no im2col at all.  Two operand paths:
+//
+// Plain rows (SW = false; any shape up to 512 pixels wide).  tcgen05.mma's un-swizzled K-major
+// layout addresses element (row i, 16-byte chunk j) at  start + (i % 8) * 16 + (i / 8) * SBO + j * LBO.
 // Choosing SBO = 128 and LBO = 16 makes that  start + 16 * (i + j):  row i (output column x0+i)
-// reads the 16-byte chunks i, i+1, i+2, i+3 of the input row, i.e. the pixel pairs
-// 2x-4 .. 2x+3 -- exactly the 7 taps (plus one zero-weight tap in front) of a stride-2 window.
-// The rows of the operand overlap in memory; the tensor core only does address arithmetic.
-// One filter row is therefore K = 32 (two MMAs of K = 16), a conv output row of up to 128
-// pixels is 14 MMAs of 128 x 64 x 16, and every input row is brought into shared memory once
-// (bulk async copies of row pairs into a ring) and reused by the seven filter rows of four
-// output rows.
+// reads the chunks i .. i+3 of the input row, i.e. the pixels 2x-4 .. 2x+3 -- the 7 taps (plus one
+// zero-weight tap in front) of a stride-2 window.  The operand rows overlap in memory; the tensor
+// core only does address arithmetic.  One filter row is K = 32, a conv row 14 MMAs of
+// 128 x 64 x 16; input rows are bulk-copied once, in pairs, into a ring and reused by the seven
+// filter rows of four conv rows; two threads issue the MMAs of alternate conv rows.
+//
+// Swizzled pairs (SW = true; even H, conv row of at most 128 pixels).  Rows 2k and 2k+1 are stored
+// interleaved in 16-byte chunks, one tiled TMA copy through a tensor map with overlapping strides
+// lands each pair as a canonical swizzled [128 x 64] tile, and one thread multiplies it with the
+// weight blocks of the four conv rows it feeds at once (see the kernel's comments).
 //
 // Roles (11 warps, persistent over (image, band of pooled rows) items):
-//   warp 0   bulk-copies input rows into the ring; weights (28 KB) are resident.
-//   warps 1, 10  one thread each issues the MMAs of alternate conv rows into four TMEM accumulators.
-//   warps 2-9  read the accumulator, apply scale/shift, keep the vertical maximum of the three
-//            conv rows of a pooling window in registers, write one fp16 row per pooled row to
-//            shared memory, take the horizontal maximum there (clamped window = -inf padding),
-//            apply ReLU (it commutes with max) and store the pooled row, 16 bytes per thread,
-//            fully coalesced.
+//   warp 0   copies input rows / row pairs into the ring; the packed weights are resident.
+//   warp 1   issues MMAs (plain rows: together with warp 10, on alternate conv rows).
+//   warp 10  swizzled pairs: scout -- does the issuing lane's barrier waits up to four pairs ahead.
+//   warps 2-9  per pooled row: read the accumulators of two conv rows, apply scale/shift, keep the
+//            vertical maximum of the pooling window in registers, write one fp16 row to shared
+//            memory, take the horizontal maximum there (clamped window = -inf padding), apply
+//            ReLU (it commutes with max) and store the pooled row, 16 bytes per thread, coalesced.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -82,7 +86,6 @@ struct StemParams {
   int N, H, W, OH, OW, PH, PW;
   int row_bytes;            // RW * 8
   int w_bytes;              // bytes of packed weights the kernel keeps resident
-  int dbg;
   int slot_bytes;           // ring slot of one row pair (covers the junk rows of the last x tile)
   int x_tiles;              // ceil(OW / 128)
   int bands, band_rows;     // pooled rows per item
@@ -858,7 +861,6 @@ cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream) {
   p.slot_bytes = (slot + 127) & ~127;
   p.bf16 = a.ab == kBF16;
   p.w_bytes = kWBytes;
-  p.dbg = getenv("STEM_DBG") ? atoi(getenv("STEM_DBG")) : 0;
   // Swizzled variant: one x tile, even H (a row pair never straddles two images), and a tensor
   // map whose "output pixel" dimension advances 16 bytes under a 64-byte innermost extent.
   CUtensorMap tm_in;
