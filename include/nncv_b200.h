@@ -203,7 +203,8 @@ int nncv_b200_conv_run_fused(nncv_b200_conv* c, nncv_b200_conv* branch, const vo
 /* Force the tile configuration (N tile 64/128/256; algo 2: sub-tiles per CTA 1/2/4; resident: 1 =
  * weights resident in shared memory, 0 = streamed; algo 2 with Kout a multiple of bn: 2 = the
  * CTA-pair kernel on tcgen05.mma.cta_group::2 (bn columns per pair), 3 = the same with the items of
- * a mostly empty last round sliced by columns); bn = 0 restores the built-in choice.  A tuning
+ * a mostly empty last round sliced by columns; algo 0 with Kout a multiple of bn = 128 or 256:
+ * 2 = the per-tap kernel on CTA pairs); bn = 0 restores the built-in choice.  A tuning
  * and test hook with no counterpart in the reference. */
 int nncv_b200_conv_set_tile(nncv_b200_conv* c, int bn, int mt, int resident);
 

@@ -107,6 +107,7 @@ struct TconvArgs {
   int N = 0, H = 0, W = 0, C = 0, OH = 0, OW = 0, Kout = 0, R = 1, S = 1, stride = 1, pad = 0;
   Layout in_l{0, 0, 0}, out_l{0, 0, 0};
   int bn = 64, resident = 0;
+  int pair = 0;                    // CTA pairs (tcgen05.mma.cta_group::2): weights packed for N tile bn / 2
   DType ab = kF16, out_dtype = kF16;
   int relu = 0;
   int sm_count = 0;

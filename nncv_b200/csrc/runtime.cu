@@ -366,7 +366,8 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
   if (sv_ok || (c->algo == 0 && tc_ok)) {
     auto launch_choice = [&](const ConvChoice& ch, bool profile) -> int {
       const void* wpack = nullptr;
-      int rc = conv_prepare(c, ch.kernel == 7 ? (ch.bn / 2 < 64 ? 64 : ch.bn / 2) : ch.bn, st, &wpack);
+      // the CTA-pair kernels (7: shifted-view, 8: per-tap) read weights packed for half their N tile
+      int rc = conv_prepare(c, (ch.kernel == 7 || ch.kernel == 8) ? (ch.bn / 2 < 64 ? 64 : ch.bn / 2) : ch.bn, st, &wpack);
       if (rc) return rc;
       if (ch.kernel == 7) {   // CTA-pair shifted-view kernel
         Conv3x3Args a;
@@ -395,8 +396,9 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
       }
       TconvArgs a;
       a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
+      a.pair = ch.kernel == 8;
       if (fb) {
-        rc = conv_prepare(fb->conv, 128, st, &a.wpack2);
+        rc = conv_prepare(fb->conv, a.pair ? 64 : 128, st, &a.wpack2);
         if (rc) return rc;
         a.scale2 = fb->scale; a.shift2 = fb->shift; a.out2 = fb->out;
       }
@@ -404,7 +406,7 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
       a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.in_l = in_l; a.out_l = out_l;
       a.bn = ch.bn; a.resident = ch.resident; a.ab = c->dtype; a.out_dtype = out_dt; a.relu = relu;
       a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
-      if (profile) prof_begin(5, flops, bytes, (int)M, c->Kout, c->C * c->R * c->S, ch.bn * 10 + ch.resident, st);
+      if (profile) prof_begin(5, flops, bytes, (int)M, c->Kout, c->C * c->R * c->S, ch.bn * 10 + ch.resident + (a.pair ? 2 : 0), st);
       ++g_launches;
       const cudaError_t e = launch_tconv(a, st);
       if (profile) prof_end(st);
@@ -427,20 +429,27 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
       // room for two A stages only, too few copies in flight to cover the L2 latency (measured: 92 us
       // against 80 us on the 64 -> 128 channel block at batch 256)
       ch = ConvChoice{5, 128, 1, 0};
-    } else if (c->cfg3.bn) {
-      ch.bn = c->cfg3.bn; ch.mt = c->cfg3.mt > 0 ? c->cfg3.mt : 1; ch.resident = c->cfg3.resident;
-      if (c->cfg3.resident >= 2 && sv_ok) { ch.kernel = 7; ch.resident = c->cfg3.resident == 3; }   // forced CTA-pair kernel (3: sliced last round)
+    }
+    if (c->cfg3.bn) {
+      if (fb) {
+        if (c->cfg3.resident >= 2) ch.kernel = 8;   // forced: the fused launch on CTA pairs
+      } else {
+        ch.bn = c->cfg3.bn; ch.mt = c->cfg3.mt > 0 ? c->cfg3.mt : 1; ch.resident = c->cfg3.resident;
+        if (c->cfg3.resident >= 2 && sv_ok) { ch.kernel = 7; ch.resident = c->cfg3.resident == 3; }   // forced CTA-pair kernel (3: sliced last round)
+        if (c->cfg3.resident >= 2 && !sv_ok) { ch.kernel = 8; ch.resident = 0; }                      // per-tap kernel on CTA pairs
+      }
     } else if (g_autotune) {
-      const std::array<int, 5> key{N, H, W, residual ? 1 : 0, (int)out_dt};
+      const std::array<int, 5> key{N, H, W, (residual ? 1 : 0) + (fb ? 2 : 0), (int)out_dt};
       auto it = c->tuned.find(key);
       char ckey[192];
       snprintf(ckey, sizeof(ckey), "conv c%d k%d r%d s%d st%d p%d dt%d a%d n%d h%d w%d res%d o%d", c->Cpad, c->Kout, c->R, c->S,
-               c->stride, c->pad, (int)c->dtype, c->algo, N, H, W, residual ? 1 : 0, (int)out_dt);
+               c->stride, c->pad, (int)c->dtype, c->algo, N, H, W, (residual ? 1 : 0) + (fb ? 2 : 0), (int)out_dt);
       if (it == c->tuned.end()) {
         if (const std::string* v = g_tune_cache.find(ckey)) {
           ConvChoice m;
           if (sscanf(v->c_str(), "%d %d %d %d", &m.kernel, &m.bn, &m.mt, &m.resident) == 4 &&
-              ((m.kernel == 5 && tc_ok) || ((m.kernel == 2 || m.kernel == 7) && sv_ok)))
+              (((m.kernel == 5 || m.kernel == 8) && tc_ok) || ((m.kernel == 2 || m.kernel == 7) && sv_ok)) &&
+              (!fb || ((m.kernel == 5 || m.kernel == 8) && m.bn == 128 && !m.resident)))
             it = c->tuned.emplace(key, m).first;
         }
       }
@@ -461,10 +470,17 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
               }
             }
         }
-        if (tc_ok) {
+        if (fb) {   // the fused launch exists for N tile 128, streamed: one CTA or a pair
+          cand.clear();
+          cand.push_back(ConvChoice{5, 128, 1, 0});
+          cand.push_back(ConvChoice{8, 128, 1, 0});
+        } else if (tc_ok) {
           for (int bn : {64, 128}) cand.push_back(ConvChoice{5, bn, 1, 1});
           for (int bn : {64, 128, 256})
             if (bn <= c->Kout || bn == 64) cand.push_back(ConvChoice{5, bn, 1, 0});
+          if (out_dt != kF32)
+            for (int bn : {128, 256})
+              if (c->Kout % bn == 0) cand.push_back(ConvChoice{8, bn, 1, 0});   // CTA pairs
         }
         cudaEvent_t e0, e1;
         CU(cudaEventCreate(&e0));

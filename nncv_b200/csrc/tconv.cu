@@ -69,11 +69,17 @@ struct TcParams {
 // block: the same A tile coordinates, its own weight tile, and a second accumulator beside the
 // first.  Both results leave through the same epilogue (the second one with its own scale/shift,
 // no ReLU, no residual) into a second output tensor.
-template <int BN, bool RESIDENT, bool DUAL>
+// PAIR: two CTAs of a cluster work as one (tcgen05.mma.cta_group::2, M = 256): each loads the A tile
+// of its own 128 output pixels and HALF of every weight tile (BN/2 rows), one lane of the leader
+// issues MMAs that read both CTAs' shared memory, each CTA drains its own accumulator rows.  The
+// streamed kernel is bound by the L2->SM path (one A tile and one weight tile per 128 x BN x 64
+// block); halving the weight bytes per CTA is the point.  Barrier protocol as in conv3x3_pair.cu.
+template <int BN, bool RESIDENT, bool DUAL, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_out,
              const __grid_constant__ CUtensorMap tm_out2, const TcParams p) {
-  constexpr int WTILE = BN * 128;
+  static_assert(!PAIR || !RESIDENT, "the pair kernel streams its weights");
+  constexpr int WTILE = (PAIR ? BN / 2 : BN) * 128;   // this CTA's part of a weight tile
   constexpr int ACC_W = DUAL ? 2 * BN : BN;   // columns of one accumulator buffer
   constexpr int ACC_COLS = 2 * ACC_W;         // two accumulator buffers
   const int taps_x = p.taps + (DUAL ? 1 : 0); // taps per channel block in the pipeline
@@ -94,15 +100,16 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
   const uint32_t tmem_slot = w_full + 8;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? ptx::cluster_ctarank() : 0u;   // 0 = leader
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int i = 0; i < kMaxStages; ++i) {
-      ptx::mbar_init(full + 8 * i, 1);
+      ptx::mbar_init(full + 8 * i, (PAIR && rank == 0) ? 2 : 1);   // leader: own copies + the peer's relay
       ptx::mbar_init(empty + 8 * i, 1);
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(acc_full + 8 * i, 1);
-      ptx::mbar_init(acc_empty + 8 * i, kEpiThreads);
+      ptx::mbar_init(acc_empty + 8 * i, PAIR ? 2 : kEpiThreads);   // pair: one arrival per CTA
     }
     ptx::mbar_init(w_full, 1);
     ptx::mbar_fence_init();
@@ -111,11 +118,17 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
     if (DUAL) ptx::prefetch_tensormap(&tm_out2);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, ACC_COLS);
-    ptx::tmem_relinquish();
+    if (PAIR) {
+      ptx::tmem_alloc_pair(tmem_slot, ACC_COLS);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(tmem_slot, ACC_COLS);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if (PAIR) ptx::cluster_sync_all();   // both CTAs' barriers exist before anyone arrives remotely
   ptx::tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
   // The prologue above touched nothing the previous kernel of the stream writes; everything
@@ -126,9 +139,13 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
 
   // Resident weights pin a CTA to one Kout tile (blockIdx.y); otherwise the CTA strides over
   // (pixel tile, Kout tile) pairs with the Kout tiles of a pixel tile adjacent.
-  const int total_items = RESIDENT ? p.m_items : p.m_items * p.n_tiles;
+  // Pair: a work item is two consecutive pixel tiles (one per CTA) times one Kout tile; a tile past
+  // the end reads zeros and stores nothing.
+  const int m_units = PAIR ? (p.m_items + 1) / 2 : p.m_items;
+  const int total_items = RESIDENT ? m_units : m_units * p.n_tiles;
+  const int worker = PAIR ? (int)blockIdx.x >> 1 : (int)blockIdx.x, workers = PAIR ? (int)gridDim.x >> 1 : (int)gridDim.x;
   auto item_of = [&](int i, int& n0, int& oy0, int& ox0, int& n_tile) {
-    const int w = (int)blockIdx.x + i * (int)gridDim.x;
+    const int w = worker + i * workers;
     if (w >= total_items) return false;
     int m_item;
     if (RESIDENT) {
@@ -138,6 +155,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
       m_item = w / p.n_tiles;
       n_tile = w - m_item * p.n_tiles;
     }
+    if (PAIR) m_item = 2 * m_item + (int)rank;
     const int tx = m_item % p.tiles_x;
     const int t2 = m_item / p.tiles_x;
     const int ty = t2 % p.tiles_y;
@@ -173,13 +191,17 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
             const int gtap = tap < p.taps ? tap : p.taps / 2;   // the extra tap re-reads the centre tap's pixels
             const int r = gtap / p.S, s = gtap - r * p.S;
             const uint32_t st = cnt % (uint32_t)p.stages;
-            if (!ptx::mbar_wait_abortable(empty + 8 * st, ((cnt / (uint32_t)p.stages) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
+            const bool freed = PAIR ? ptx::mbar_wait_cluster_abortable(empty + 8 * st, ((cnt / (uint32_t)p.stages) & 1u) ^ 1u, abort_flag)
+                                    : ptx::mbar_wait_abortable(empty + 8 * st, ((cnt / (uint32_t)p.stages) & 1u) ^ 1u, abort_flag);
+            if (!freed) { okw = false; break; }
             ptx::mbar_arrive_expect_tx(full + 8 * st, (uint32_t)stage_bytes);
             const uint32_t dst = sRing + st * stage_bytes;
             ptx::tma_load_4d(dst, &tm_in, cb * 64, xb + s, yb + r, n0, full + 8 * st);
             if (!RESIDENT) {
-              const uint8_t* wsrc = (DUAL && tap == p.taps) ? p.wpack2 + ((size_t)n_tile * p.CB + cb) * WTILE
-                                                             : p.wpack + ((size_t)n_tile * KB + (size_t)tap * p.CB + cb) * WTILE;
+              // pair: the weights are packed for N tile BN/2; this CTA takes tile 2 * n_tile + rank
+              const int wt = PAIR ? 2 * n_tile + (int)rank : n_tile;
+              const uint8_t* wsrc = (DUAL && tap == p.taps) ? p.wpack2 + ((size_t)wt * p.CB + cb) * WTILE
+                                                             : p.wpack + ((size_t)wt * KB + (size_t)tap * p.CB + cb) * WTILE;
               ptx::bulk_g2s(dst + kABytes, wsrc, WTILE, full + 8 * st);
             }
           }
@@ -188,9 +210,30 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
       if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitProducer);
     }
   } else if (warp == 1) {
+    if (PAIR && rank != 0) {
+      // ---------------------------------------------------------------- relay (peer CTA) ----
+      // tells the leader when this CTA's stage is full
+      if (lane == 0) {
+        const uint32_t lead_full = ptx::map_to_cta(full, 0);
+        uint32_t cnt = 0;
+        bool okw = true;
+        for (int i = 0; okw; ++i) {
+          int n0, oy0, ox0, n_tile;
+          if (!item_of(i, n0, oy0, ox0, n_tile)) break;
+          const int KBX = taps_x * p.CB;
+          for (int kb = 0; kb < KBX; ++kb, ++cnt) {
+            const uint32_t st = cnt % (uint32_t)p.stages;
+            if (!ptx::mbar_wait_abortable(full + 8 * st, (cnt / (uint32_t)p.stages) & 1u, abort_flag)) { okw = false; break; }
+            ptx::mbar_arrive_remote(lead_full + 8 * st);
+          }
+        }
+        if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitMma);
+      }
+    } else
     // ------------------------------------------------------------------ MMA issuer ------
     if (lane == 0) {
-      const uint32_t idesc = ptx::umma_idesc(128, BN, p.bf16 ? 1 : 0);
+      const uint32_t idesc = ptx::umma_idesc(PAIR ? 256 : 128, BN, p.bf16 ? 1 : 0);
+      const uint32_t peer_empty = PAIR ? ptx::map_to_cta(empty, 1) : 0u, peer_acc_full = PAIR ? ptx::map_to_cta(acc_full, 1) : 0u;
       bool okw = true;
       if (RESIDENT) okw = ptx::mbar_wait_abortable(w_full, 0, abort_flag);
       uint32_t cnt = 0, acc_cnt = 0;
@@ -198,7 +241,9 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         int n0, oy0, ox0, n_tile;
         if (!item_of(i, n0, oy0, ox0, n_tile)) break;
         const uint32_t ab = acc_cnt & 1u;
-        if (!ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt >> 1) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
+        const bool drained = PAIR ? ptx::mbar_wait_cluster_abortable(acc_empty + 8 * ab, ((acc_cnt >> 1) & 1u) ^ 1u, abort_flag)
+                                  : ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt >> 1) & 1u) ^ 1u, abort_flag);
+        if (!drained) { okw = false; break; }
         ptx::tc_fence_after();
         const uint32_t d = tmem_base + ab * ACC_W;
         const int KBX = taps_x * p.CB;
@@ -206,21 +251,39 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
           const int cb = kb / taps_x, tap = kb - cb * taps_x;   // producer order: cb outer, tap inner
           const bool second = DUAL && tap == p.taps;
           const uint32_t st = cnt % (uint32_t)p.stages;
-          if (!ptx::mbar_wait_abortable(full + 8 * st, (cnt / (uint32_t)p.stages) & 1u, abort_flag)) { okw = false; break; }
+          const bool landed = PAIR ? ptx::mbar_wait_cluster_abortable(full + 8 * st, (cnt / (uint32_t)p.stages) & 1u, abort_flag)
+                                   : ptx::mbar_wait_abortable(full + 8 * st, (cnt / (uint32_t)p.stages) & 1u, abort_flag);
+          if (!landed) { okw = false; break; }
           ptx::tc_fence_after();
           const uint32_t a_addr = sRing + st * stage_bytes;
           const uint32_t a_lo = ptx::smem_desc_k128_lo(a_addr);
           const uint32_t b_lo = ptx::smem_desc_k128_lo(
               RESIDENT ? sW + (uint32_t)(second ? KB + cb : tap * p.CB + cb) * WTILE : a_addr + kABytes);
 #pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4)
-            ptx::umma_f16(second ? d + BN : d, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
-                          ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi), idesc,
-                          (second ? (cb | k4) : (cb | tap | k4)) != 0 ? 1u : 0u);
-          ptx::tc_commit(empty + 8 * st);
+          for (int k4 = 0; k4 < 4; ++k4) {
+            if (PAIR)
+              ptx::umma_f16_pair(second ? d + BN : d, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
+                                 ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi), idesc,
+                                 (second ? (cb | k4) : (cb | tap | k4)) != 0 ? 1u : 0u);
+            else
+              ptx::umma_f16(second ? d + BN : d, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
+                            ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi), idesc,
+                            (second ? (cb | k4) : (cb | tap | k4)) != 0 ? 1u : 0u);
+          }
+          if (PAIR) {
+            ptx::tc_commit_pair(empty + 8 * st);
+            ptx::tc_commit_pair(peer_empty + 8 * st);
+          } else {
+            ptx::tc_commit(empty + 8 * st);
+          }
         }
         if (!okw) break;
-        ptx::tc_commit(acc_full + 8 * ab);
+        if (PAIR) {
+          ptx::tc_commit_pair(acc_full + 8 * ab);
+          ptx::tc_commit_pair(peer_acc_full + 8 * ab);
+        } else {
+          ptx::tc_commit(acc_full + 8 * ab);
+        }
         ++acc_cnt;
       }
       if (!okw && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrWaitMma);
@@ -247,7 +310,8 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
       const int nimg = n0 + tnn, oy = oy0 + ti, ox = ox0 + tj;
       const bool valid = nimg < p.NB && oy < p.OH && ox < p.OW;
       const size_t pix = ((size_t)nimg * p.out_rows + oy + p.out_off) * p.out_pitch + ox + p.out_off;
-      const bool got = ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt >> 1) & 1u, abort_flag);
+      const bool got = PAIR ? ptx::mbar_wait_cluster_abortable(acc_full + 8 * ab, (acc_cnt >> 1) & 1u, abort_flag)
+                            : ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt >> 1) & 1u, abort_flag);
       if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; break; }
       ptx::tc_fence_after();
       for (int oi = 0; oi < (DUAL ? 2 : 1); ++oi)
@@ -277,9 +341,10 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         }
         __syncwarp();
         ptx::tmem_ld_wait();
-        if (sl == slabs - 1 && oi == (DUAL ? 1 : 0)) {
+        const bool last_slab = sl == slabs - 1 && oi == (DUAL ? 1 : 0);
+        if (last_slab) {
           ptx::tc_fence_before();
-          ptx::mbar_arrive(acc_empty + 8 * ab);
+          if (!PAIR) ptx::mbar_arrive(acc_empty + 8 * ab);   // pair: one arrival per CTA, after the barrier below
         }
         if (active) {
           float v[32];
@@ -358,6 +423,10 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         ptx::fence_proxy_async_smem();
         ptx::named_bar_sync(1, kEpiThreads);
         if (elected) {
+          if (PAIR && last_slab) {   // every thread of this CTA has read the accumulator: tell the leader
+            if (rank == 0) ptx::mbar_arrive(acc_empty + 8 * ab);
+            else ptx::mbar_arrive_remote(ptx::map_to_cta(acc_empty, 0) + 8 * ab);
+          }
           if (ncol < p.Kout)
             ptx::tma_store_4d((DUAL && oi) ? &tm_out2 : &tm_out, ncol, ox0 + p.out_off, oy0 + p.out_off, n0, sStage + sb * kSlabBytes);
           ptx::bulk_commit();
@@ -374,9 +443,11 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
 
   ptx::tc_fence_before();
   __syncthreads();
+  if (PAIR) ptx::cluster_sync_all();   // the peer's shared memory and barriers stay valid until both are done
   if (warp == 1) {
     __syncwarp();
-    ptx::tmem_dealloc(tmem_base, ACC_COLS);
+    if (PAIR) ptx::tmem_dealloc_pair(tmem_base, ACC_COLS);
+    else ptx::tmem_dealloc(tmem_base, ACC_COLS);
   }
 }
 
@@ -410,9 +481,9 @@ bool make_map4(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esz,
 
 constexpr size_t kSmemLimit = 227 * 1024;
 
-template <int BN, bool RESIDENT, bool DUAL = false>
+template <int BN, bool RESIDENT, bool DUAL = false, bool PAIR = false>
 cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
-  const size_t wtile = (size_t)BN * 128;
+  const size_t wtile = (size_t)(PAIR ? BN / 2 : BN) * 128;
   const int KB = p.taps * p.CB;
   const size_t fixed = 1024 + 2 * kSlabBytes + 512;
   const size_t stage = RESIDENT ? kABytes : kABytes + wtile;
@@ -436,7 +507,7 @@ cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
   CUtensorMap tm_out2 = tm_out;
   if (DUAL && !make_map4(&tm_out2, a.out2, dt, 2, a.Kout, ol.pitch, ol.img_rows, a.N, 64, p.tw, p.th, p.tn, 1, 1))
     return cudaErrorInvalidValue;
-  auto kern = tconv_kernel<BN, RESIDENT, DUAL>;
+  auto kern = tconv_kernel<BN, RESIDENT, DUAL, PAIR>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int sms = a.sm_count > 0 ? a.sm_count : 148;
@@ -446,6 +517,25 @@ cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
     if (gx < 1) gx = 1;
     if (gx > p.m_items) gx = p.m_items;
     grid = dim3(gx, p.n_tiles);
+  } else if (PAIR) {
+    const long long items = (long long)((p.m_items + 1) / 2) * p.n_tiles;
+    const long long pairs = sms / 2;
+    grid = dim3(2 * (unsigned)(items < pairs ? items : pairs), 1);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kern, tm_in, tm_out, tm_out2, p);
   } else {
     const long long items = (long long)p.m_items * p.n_tiles;
     grid = dim3((unsigned)(items < sms ? items : sms), 1);
@@ -513,6 +603,16 @@ cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream) {
   p.relu = a.relu; p.bf16 = a.ab == kBF16; p.out_f32 = a.out_dtype == kF32;
   p.stages = 0;
   if (p.residual && p.out_f32) return cudaErrorInvalidValue;
+  if (a.pair) {     // CTA pairs: a.wpack (and a.wpack2) packed for N tile bn / 2, streamed weights, 16-bit output
+    if (a.resident || p.out_f32 || (a.bn != 128 && a.bn != 256) || a.Kout % a.bn != 0) return cudaErrorInvalidValue;
+    if (a.wpack2) {
+      if (!a.out2 || a.bn != 128 || a.R != a.S || a.R % 2 == 0 || a.pad != a.R / 2 ||
+          (reinterpret_cast<uintptr_t>(a.wpack2) & 15) || (reinterpret_cast<uintptr_t>(a.out2) & 15))
+        return cudaErrorInvalidValue;
+      return launch_cfg<128, false, true, true>(a, p, stream);
+    }
+    return a.bn == 128 ? launch_cfg<128, false, false, true>(a, p, stream) : launch_cfg<256, false, false, true>(a, p, stream);
+  }
   if (a.wpack2) {   // fused 1x1 stride-s branch on the centre tap: odd square filter, pad = R/2, N tile 128 streamed
     if (!a.out2 || a.bn != 128 || p.out_f32 || a.R != a.S || a.R % 2 == 0 || a.pad != a.R / 2 ||
         a.Kout % 128 != 0 || (reinterpret_cast<uintptr_t>(a.wpack2) & 15) || (reinterpret_cast<uintptr_t>(a.out2) & 15))

@@ -245,9 +245,49 @@ def test_conv_winograd_fixture_closed_form():
     np.testing.assert_allclose(y, 3.6, rtol=1e-6)
 
 
+@pytest.mark.parametrize("case", [
+    # n, c, h, w, k, r, stride, pad, bn
+    (3, 64, 56, 56, 128, 3, 2, 1, 128),
+    (5, 128, 28, 28, 256, 3, 2, 1, 256),
+    (2, 256, 14, 14, 512, 3, 2, 1, 256),
+    (7, 128, 28, 28, 256, 1, 2, 0, 128),
+    (1, 64, 9, 13, 128, 3, 2, 1, 128),       # odd number of pixel tiles: the peer CTA's last tile is empty
+    (4, 64, 16, 16, 256, 3, 1, 1, 256),
+])
+@pytest.mark.parametrize("dtype,res", [(F16, False), (F16, True), (BF16, False)])
+def test_conv_per_tap_on_cta_pairs(case, dtype, res):
+    """The per-tap TMA kernel with tcgen05.mma.cta_group::2 (each CTA loads its own pixel tile and half
+    of every weight tile) against the oracle, and bit for bit against the single-CTA kernel."""
+    n, c, h, w, k, r, stride, pad, bn = case
+    g = _rng(n * 7 + c + h + k + r)
+    x = g.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = (g.standard_normal((k, c, r, r)) * np.sqrt(2.0 / (r * r * c))).astype(np.float32)
+    scale = g.uniform(0.5, 1.5, k).astype(np.float32)
+    shift = (g.standard_normal(k) * 0.1).astype(np.float32)
+    oh, ow = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - r) // stride + 1
+    rs = g.standard_normal((n, k, oh, ow)).astype(np.float32) if res else None
+    conv = G.Conv(wt, stride, pad, dtype)
+    try:
+        check(lib().nncv_b200_conv_set_tile(conv.h, bn, 1, 0))
+        y1, xq = conv.run(x, scale, shift, rs, True)
+        check(lib().nncv_b200_conv_set_tile(conv.h, bn, 1, 2))
+        y2, _ = conv.run(x, scale, shift, rs, True)
+    finally:
+        conv.close()
+    assert np.array_equal(y1, y2)
+    tdt = G.TORCH_DT[dtype]
+    ref = ob.conv2d(xq, torch.from_numpy(wt).to(tdt).float().numpy(), stride, pad, acc64=True)
+    ref = ref * scale[None, :, None, None] + shift[None, :, None, None]
+    if res:
+        ref = ref + torch.from_numpy(rs).to(tdt).float().numpy()
+    ref = np.where(ref > 0, ref, 0)
+    assert G.rel_l2(y2, ref) <= (TOL_16 if dtype == F16 else 8e-3)
+
+
 @pytest.mark.parametrize("shape", [(3, 64, 56, 56, 128), (2, 128, 28, 28, 256), (5, 256, 14, 14, 512), (1, 64, 9, 13, 128)])
 @pytest.mark.parametrize("dtype", [F16, BF16])
-def test_conv_fused_downsample(shape, dtype):
+@pytest.mark.parametrize("pair", [False, True])
+def test_conv_fused_downsample(shape, dtype, pair):
     """The 3x3 stride-2 conv and the 1x1 stride-2 downsample conv of a BasicBlock in one launch
     (Res18.mlir: convs on %padded_107 and %cst_62): equal to two separate launches bit for bit and
     to the oracle within the 16-bit tolerance."""
@@ -262,6 +302,7 @@ def test_conv_fused_downsample(shape, dtype):
     try:
         y3, xq = main.run(x, sc3, sh3, relu=True)
         y1, _ = branch.run(x, sc1, sh1, relu=False)
+        check(lib().nncv_b200_conv_set_tile(main.h, 128, 1, 2 if pair else 0))   # one CTA per tile, or CTA pairs
         X = G.dev(np.ascontiguousarray(x.transpose(0, 2, 3, 1)), dtype)
         oh, ow = (h + 2 - 3) // 2 + 1, (w + 2 - 3) // 2 + 1
         Y3 = torch.full((n, oh, ow, k), float("nan"), device="cuda", dtype=G.TORCH_DT[dtype])
