@@ -252,20 +252,14 @@ def run_ours(args):
         ms_e2e = timed(step_host, args.steps)
         barrier()
         # Timed regions shorter than a few sampling periods (20 ms each) leave too few clock samples:
-        # keep running the same device step, untimed, until about ten periods have passed.
-        t_extra = time.perf_counter()
-        n_extra = 0
-        short = ms_dev + ms_e2e < 400.0   # both timed regions together, in ms
-        while world == 1 and short and sampler and sampler.count() < 10 and time.perf_counter() - t_extra < 0.25:
+        # keep running the same device step, untimed, for a while.  The number of extra steps depends
+        # on the arguments only, never on a rank's own timings: every rank must run the same number
+        # of steps, they contain a collective.
+        n_extra = 0 if args.steps >= 200 else 200
+        for _ in range(n_extra):
             step_device()
-            torch.cuda.synchronize()
-            n_extra += 1
-        if world > 1:   # every rank runs the same number of extra steps (they contain a collective)
-            n_extra = min(2000, max(0, int(250.0 / max(ms_dev / args.steps, 0.05)))) if short else 0
-            for _ in range(n_extra):
-                step_device()
-            torch.cuda.synchronize()
-            barrier()
+        torch.cuda.synchronize()
+        barrier()
         clocks = sampler.stop() if sampler else None
         if clocks is not None:
             clocks["extra_untimed_steps_sampled"] = n_extra
