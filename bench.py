@@ -350,7 +350,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="global batch (the benchmark config uses 256)")
-    ap.add_argument("--layers", action="store_true", help="also dump per-launch records to gpurun_out/layers.json")
+    ap.add_argument("--layers", action="store_true", help="also dump the per-launch records of the profiling pass as JSON into the run's output folder")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -1,6 +1,6 @@
-"""Generates the committed fixtures under tests/golden/.  Run in the authoring container, where
-the nncv source tree is mounted at /root/reference (the GPU box has no such tree, so the tests
-read only the files this script wrote):
+"""Generates the committed fixtures under tests/golden/.  Run where the nncv source tree is
+available (its location is REF below; a GPU box has no such tree, so the tests read only the files
+this script wrote):
 
     python tests/golden/make_golden.py
 
