@@ -49,6 +49,16 @@ def test_no_gpu_means_loud_failure_not_cpu_fallback():
     with pytest.raises(_lib.NncvError):
         rt.forward(out, np.zeros((1, 3, 64, 64), np.float32), np.zeros(11699112, np.float32))
     assert (out == 5.0).all()
+    # the newer entry points fail the same way: plans cannot even be created without a device
+    w = np.zeros((128, 64, 3, 3), np.float32)
+    assert not L.nncv_b200_conv_create(w.ctypes.data, _lib.F32, 128, 64, 3, 3, 2, 1, _lib.F16, 0)
+    assert L.nncv_b200_last_status() == 3
+    rc = L.nncv_b200_conv_run_fused(None, None, None, None, None, 1, 8, 8, None, None, None, None, 0, None)
+    assert rc != 0
+    rc = L.nncv_b200_stem_pool(a.ctypes.data, _lib.F16, a.ctypes.data, _lib.F32, None, None, a.ctypes.data, _lib.F16,
+                               1, 8, 8, None)
+    assert rc == 3
+    assert L.nncv_b200_stem_variant(-1) == 0   # no stem launch has happened
 
 
 def test_missing_library_raises(monkeypatch):
