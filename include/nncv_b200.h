@@ -112,6 +112,20 @@ int nncv_b200_forward_device(nncv_memref2* dst, nncv_memref4* src, void* cuda_st
 int nncv_b200_set_stream(void* cuda_stream, int enable);
 int nncv_b200_last_status(void);
 const char* nncv_b200_last_error(void);
+/* Every wait inside the kernels is bounded; a wait that runs out (or a range check that refuses a
+ * copy) leaves a code in a status word on the device and the kernel returns.  _mlir_ciface_forward
+ * reads that word itself; after any of the calls that do not synchronise (nncv_b200_forward_device,
+ * nncv_b200_matmul, nncv_b200_matmul_noalloc, nncv_b200_conv_run, ...) synchronise the stream and
+ * call this: it reads and clears the word of the current device (and the one at the head of the
+ * fixed array of nncv_b200_matmul_noalloc) and returns NNCV_B200_OK, NNCV_B200_ETIMEOUT (codes 1-4:
+ * which role gave up is in the message) or NNCV_B200_ECUDA (code 5: refused copy).  The reference
+ * has no device and no counterpart (its errors are exit(-1), DnnModelLowering.cpp:222-230). */
+int nncv_b200_device_status(void);
+/* Failure-path self-test: launches one tiny kernel that waits on an mbarrier nobody arrives on,
+ * with a limit of 2^log2_clocks clocks (at most 2^24, a few milliseconds), then reports the
+ * time-out into the status word and returns; nothing faults and nothing hangs.  After a
+ * synchronise, nncv_b200_device_status() must answer NNCV_B200_ETIMEOUT and later calls must work. */
+int nncv_b200_selftest_wait_timeout(int log2_clocks, void* stream);
 /* Number of kernels of this library launched since load (for benchmark accounting). */
 long long nncv_b200_launch_count(void);
 
@@ -157,7 +171,7 @@ int nncv_b200_matmul(const void* A, const void* B, void* C, int M, int N, int K,
  * synchronisation a cudaMalloc implies.  The repacked B lives in a fixed array inside the library
  * image (NNCV_B200_NOALLOC_MAX_PACKED_BYTES plus a 256-byte header; every GPU that loads the
  * library holds it until the process exits), so this call makes no cudaMalloc, cudaFree or other
- * allocating call.  16-bit operands only (F16/BF16), K %% 8 == 0.  Problems whose packed B
+ * allocating call.  16-bit operands only (F16/BF16), K % 8 == 0.  Problems whose packed B
  * (about N*K*2 bytes, N and K rounded up to the tile) exceeds the array are rejected with
  * NNCV_B200_EINVAL and a message; use nncv_b200_matmul for those.
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
@@ -165,6 +179,8 @@ int nncv_b200_matmul(const void* A, const void* B, void* C, int M, int N, int K,
  * All calls share the one array, which keeps the previous call's contents: the status word in it
  * is cleared and the packed image rewritten in full at the start of every call, and two calls
  * that overlap on the GPU (different streams, no dependency) race on it -- order them.
+ * A bounded wait that runs out in this path is reported in the word at the head of the array:
+ * synchronise and ask nncv_b200_device_status().
  * No counterpart in the reference, which never uses a device. */
 #define NNCV_B200_NOALLOC_MAX_PACKED_BYTES (8u << 20)
 int nncv_b200_matmul_noalloc(const void* A, const void* B, void* C, int M, int N, int K, int ab_dtype,
@@ -175,7 +191,7 @@ int nncv_b200_matmul_noalloc(const void* A, const void* B, void* C, int M, int N
 typedef struct nncv_b200_conv nncv_b200_conv;
 /* weights: host or device [Kout,C,R,S] of w_dtype.  dtype: activation type (F16/BF16 -> tcgen05
  * implicit GEMM, F32 -> CUDA-core).  algo: 0 = implicit GEMM, A operand fetched by strided TMA
- * copies when C %% 64 == 0 and by a cp.async gather otherwise (any shape), 3 = always the gather
+ * copies when C % 64 == 0 and by a cp.async gather otherwise (any shape), 3 = always the gather
  * kernel, 1 = Winograd F(2x2,3x3) in three stages (input transform, 16 tcgen05 GEMMs, output
  * transform; same shape limits as algo 2; the counterpart of nncv's disabled F(6x6,3x3) rewrite,
  * OptimizeConv2dUsingWinograd.cpp:173-284), 2 = 3x3 stride-1 pad-1 implicit GEMM whose nine taps are shifted views of one

@@ -19,7 +19,7 @@ EXPORTS = [
     "_mlir_ciface_forward", "nncv_b200_load", "nncv_b200_load_blob", "nncv_b200_unload",
     "nncv_b200_forward_device", "nncv_b200_last_status", "nncv_b200_last_error",
     "nncv_b200_launch_count", "nncv_b200_set_stream", "nncv_b200_profile", "nncv_b200_profile_count",
-    "nncv_b200_profile_get",
+    "nncv_b200_profile_get", "nncv_b200_device_status", "nncv_b200_selftest_wait_timeout",
     "nncv_flat_array_read", "nncv_flat_array_free", "nncv_flat_array_count",
     "nncv_flat_array_indexer", "nncv_flat_array_data", "nncv_flat_array_wrapped",
     "nncv_flat_array_write",
@@ -63,6 +63,8 @@ def lib() -> ctypes.CDLL:
     L.nncv_b200_last_error.restype = c_char_p
     L.nncv_b200_launch_count.restype = c_longlong
     L.nncv_b200_set_stream.argtypes = [c_void_p, c_int]
+    L.nncv_b200_device_status.restype = c_int
+    L.nncv_b200_selftest_wait_timeout.argtypes = [c_int, c_void_p]
     L.nncv_b200_profile.argtypes = [c_int]
     L.nncv_b200_profile_count.restype = c_longlong
     L.nncv_b200_profile_get.argtypes = [c_longlong, POINTER(ProfRec)]

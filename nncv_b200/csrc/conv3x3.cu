@@ -52,22 +52,7 @@ constexpr int kResPrefetch = 5;  // slabs between the L2 prefetch of a residual 
 constexpr int kMaxInStages = 4;
 constexpr int kMaxWStages = 8;
 
-// Optional clock64() trace of CTA 0 (built only with -DNNCV_B200_TRACE; a tuning aid).
-#ifdef NNCV_B200_TRACE
-unsigned long long* g_c3_trace = nullptr;  // device buffer [3 roles][32 items][8 stamps]
-#define C3_TRACE(role, item, k)                                                          \
-  do {                                                                                   \
-    if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && (item) < 32)                     \
-      p.trace[((role) * 32 + (item)) * 8 + (k)] = (unsigned long long)clock64();          \
-  } while (0)
-#else
-#define C3_TRACE(role, item, k) \
-  do {                          \
-  } while (0)
-#endif
-
 struct C3Params {
-  unsigned long long* trace;
   const uint8_t* wpack;
   const float* scale;
   const float* shift;
@@ -111,6 +96,15 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
   const uint32_t w_full = in_empty + 8 * kMaxInStages, w_empty = w_full + 8 * kMaxWStages;
   const uint32_t acc_full = w_empty + 8 * kMaxWStages, acc_empty = acc_full + 16;
   const uint32_t tmem_slot = acc_empty + 16;
+  {
+    // the carve-up above must fit the dynamic shared memory of this launch: refuse to run otherwise
+    uint32_t dyn_bytes;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    if (tmem_slot + 4 > raw + dyn_bytes) {
+      if (threadIdx.x == 0 && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrBounds);
+      return;
+    }
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -181,9 +175,7 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         for (int cb = 0; cb < p.CB && okw; ++cb) {
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
           const uint32_t par = ((in_cnt / (uint32_t)p.in_stages) & 1u) ^ 1u;
-          C3_TRACE(0, i, 0);
           if (!ptx::mbar_wait_abortable(in_empty + 8 * st, par, abort_flag)) { okw = false; break; }
-          C3_TRACE(0, i, 1);
           ptx::mbar_arrive_expect_tx(in_full + 8 * st, (uint32_t)in_stage_bytes);
           for (int b = 0; b < p.in_boxes; ++b)
             ptx::tma_load_2d(sIn + st * in_stage_bytes + (uint32_t)b * p.box_rows * 128, &tm_in, cb * 64,
@@ -216,15 +208,12 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         int m_item, n_tile;
         if (!item_of(i, m_item, n_tile)) break;
         const uint32_t ab = acc_cnt % AB;
-        C3_TRACE(1, i, 0);
         if (!ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt / AB) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
-        C3_TRACE(1, i, 1);
         ptx::tc_fence_after();
         const uint32_t d_base = tmem_base + ab * (MT * BN);
         for (int cb = 0; cb < p.CB && okw; ++cb) {
           const uint32_t st = in_cnt % (uint32_t)p.in_stages;
           if (!ptx::mbar_wait_abortable(in_full + 8 * st, (in_cnt / (uint32_t)p.in_stages) & 1u, abort_flag)) { okw = false; break; }
-          if (cb == 0) C3_TRACE(1, i, 2);
           ptx::tc_fence_after();
           const uint32_t a_stage = sIn + st * in_stage_bytes;
           for (int tap = 0; tap < 9; ++tap) {
@@ -261,7 +250,6 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
           ptx::tc_commit(in_empty + 8 * st);
           ++in_cnt;
         }
-        C3_TRACE(1, i, 3);
         ptx::tc_commit(acc_full + 8 * ab);
         ++acc_cnt;
       }
@@ -315,7 +303,6 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       const int t = rem / SLABS, sl = rem - t * SLABS;
       const uint32_t sb = (uint32_t)j & 1u;
       const uint32_t ab = acc_cnt % AB;
-      if (elected) C3_TRACE(2, j, 0);
       // Everything that does not depend on the accumulator is issued before the waits: pad test,
       // per-channel scale/shift, and (below) the residual of the NEXT slab.
       const int q = q_tile + row;
@@ -333,10 +320,8 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       }
       bool got = true;
       if (rem == 0) got = ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt / AB) & 1u, abort_flag);
-      if (elected) C3_TRACE(2, j, 1);
       // all epilogue threads take the same exit: nobody is left alone at a named barrier
       if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; return false; }
-      if (elected) C3_TRACE(2, j, 2);
       ptx::tc_fence_after();
       const uint32_t srow = sStage + sb * kSlabBytes + (uint32_t)row * 128u;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + ab * (MT * BN) + t * BN + sl * 64;
@@ -369,7 +354,6 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         ptx::mbar_arrive(acc_empty + 8 * ab);
         ++acc_cnt;
       }
-      if (elected) C3_TRACE(2, j, 3);
       float v[32];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -412,16 +396,13 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         }
         asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
       }
-      if (elected) C3_TRACE(2, j, 4);
       ptx::fence_proxy_async_smem();
       ptx::named_bar_sync(1, kEpiThreads);
-      if (elected) C3_TRACE(2, j, 5);
       if (elected) {
         ptx::tma_store_2d(&tm_out, ncol, q_tile, sStage + sb * kSlabBytes);
         ptx::bulk_commit();
         ptx::bulk_wait_read<1>();  // the store that last read the other buffer has finished
       }
-      if (elected) C3_TRACE(2, j, 6);
       ptx::named_bar_sync(2, kEpiThreads);  // the other staging buffer is free for everyone
       return true;
     };
@@ -475,11 +456,6 @@ constexpr size_t kSmemLimit = 227 * 1024;
 template <int BN, int MT, bool RESIDENT>
 cudaError_t launch_cfg(const Conv3x3Args& a, cudaStream_t stream) {
   C3Params p;
-#ifdef NNCV_B200_TRACE
-  p.trace = g_c3_trace;
-#else
-  p.trace = nullptr;
-#endif
   p.wpack = static_cast<const uint8_t*>(a.wpack);
   p.scale = a.scale; p.shift = a.shift; p.error_flag = a.error_flag;
   p.residual = static_cast<const uint16_t*>(a.residual); p.Kout = a.Kout;
@@ -547,9 +523,6 @@ cudaError_t launch_cfg(const Conv3x3Args& a, cudaStream_t stream) {
 
 }  // namespace
 
-#ifdef NNCV_B200_TRACE
-extern "C" void nncv_b200_debug_set_trace(unsigned long long* dev_buf) { g_c3_trace = dev_buf; }
-#endif
 
 bool conv3x3_supported(int C, int Kout, int R, int S, int stride, int pad) {
   return R == 3 && S == 3 && stride == 1 && pad == 1 && C % 64 == 0 && Kout % 64 == 0 && C >= 64;

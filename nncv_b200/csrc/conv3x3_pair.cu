@@ -80,6 +80,15 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
   const uint32_t w_full = in_empty + 8 * kMaxIn, w_empty = w_full + 8 * kMaxW;
   const uint32_t acc_full = w_empty + 8 * kMaxW, acc_empty = acc_full + 16;
   const uint32_t tmem_slot = acc_empty + 16;
+  {
+    // the carve-up above must fit the dynamic shared memory of this launch: refuse to run otherwise
+    uint32_t dyn_bytes;
+    asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_bytes));
+    if (tmem_slot + 4 > raw + dyn_bytes) {
+      if (threadIdx.x == 0 && p.error_flag) atomicCAS(p.error_flag, 0, (int)kErrBounds);
+      return;
+    }
+  }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();   // 0 = leader

@@ -189,4 +189,7 @@ cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean
 cudaError_t launch_convert(const void* src, DType src_dt, void* dst, DType dst_dt, size_t n,
                            cudaStream_t stream);
 
+// ---- failure-path self-test: one bounded mbarrier wait that is left to run out ---------------
+cudaError_t launch_wait_selftest(int* error_flag, long long limit_clocks, cudaStream_t stream);
+
 }  // namespace nncv_b200

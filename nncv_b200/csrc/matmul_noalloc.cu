@@ -62,6 +62,18 @@ int setup_current_device(int* dev_out) {
 
 }  // namespace
 
+namespace nncv_b200 {
+// Status word at the head of the static array of device `dev` (0 when this path never ran
+// there); read with a 4-byte copy and cleared when non-zero.  Allocates nothing.
+int noalloc_read_status(int dev, int* flag) {
+  *flag = 0;
+  if (dev < 0 || dev >= kMaxDevices || !g_scratch_ptr[dev]) return 0;
+  if (cudaMemcpy(flag, g_scratch_ptr[dev], sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (*flag != 0 && cudaMemset(g_scratch_ptr[dev], 0, sizeof(int)) != cudaSuccess) return -1;
+  return 0;
+}
+}  // namespace nncv_b200
+
 extern "C" int nncv_b200_matmul_noalloc(const void* A, const void* B, void* C, int M, int N, int K,
                                         int ab_dtype, int c_dtype, const float* bias, int relu,
                                         void* stream) {

@@ -86,6 +86,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return true;
 }
 
+// The same bounded wait with a caller-chosen limit in clocks.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, long long limit_clocks) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait_suspend(bar, parity)) {
+    if (clock64() - t0 > limit_clocks) return false;
+  }
+  return true;
+}
+
 // ---------------------------------------------------------------- cp.async ------------
 // 16-byte global->shared copy; src_bytes == 0 writes zeros (used for padding / ragged rows).
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {

@@ -75,13 +75,18 @@ int internal_fail(int code, const char* fmt, ...) {
 }
 int internal_ok() { return ok(); }
 std::mutex& internal_mutex() { return g_mutex; }
+int noalloc_read_status(int dev, int* flag);   // matmul_noalloc.cu
 }  // namespace nncv_b200
 
 namespace {
 
 // =====================================================================================
-// device context
+// device contexts
 // =====================================================================================
+// One context per CUDA device, created the first time an entry point runs with that device
+// current and kept until the process exits.  Every entry point works on the context of the
+// calling thread's current device, so kernels always run on the GPU that owns their buffers.
+struct Model;
 struct Device {
   bool ready = false;
   int id = -1;
@@ -94,11 +99,14 @@ struct Device {
   int sm_count = 148;
   void* scratch = nullptr;     // grow-only scratch (packed B of nncv_b200_matmul)
   size_t scratch_bytes = 0;
+  Model* model = nullptr;      // the model replica living on this device
 };
-Device g_dev;
+constexpr int kMaxDevices = 64;
+Device* g_devices[kMaxDevices] = {};
+thread_local Device* t_dev = nullptr;   // context of the device current on this thread (set by device_init)
+#define g_dev (*t_dev)
 
 int device_init() {
-  if (g_dev.ready) return NNCV_B200_OK;
   int count = 0;
   cudaError_t e = cudaGetDeviceCount(&count);
   if (e != cudaSuccess || count == 0)
@@ -106,21 +114,40 @@ int device_init() {
                 cudaGetErrorString(e));
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return fail(NNCV_B200_ENODEVICE, "cudaGetDevice failed");
+  if (dev < 0 || dev >= kMaxDevices) return fail(NNCV_B200_ENODEVICE, "device index %d out of range", dev);
+  if (g_devices[dev] && g_devices[dev]->ready) {
+    t_dev = g_devices[dev];
+    return NNCV_B200_OK;
+  }
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess)
     return fail(NNCV_B200_ENODEVICE, "cudaGetDeviceProperties failed");
   if (prop.major != 10)
     return fail(NNCV_B200_ENODEVICE, "device %d is sm_%d%d; the kernels are built for sm_100a only",
                 dev, prop.major, prop.minor);
-  g_dev.id = dev;
-  g_dev.sm_count = prop.multiProcessorCount;
-  if (cudaStreamCreateWithFlags(&g_dev.stream, cudaStreamNonBlocking) != cudaSuccess)
+  if (!g_devices[dev]) g_devices[dev] = new Device();
+  Device& d = *g_devices[dev];
+  d.id = dev;
+  d.sm_count = prop.multiProcessorCount;
+  if (cudaStreamCreateWithFlags(&d.stream, cudaStreamNonBlocking) != cudaSuccess)
     return fail(NNCV_B200_ENODEVICE, "cudaStreamCreate failed");
-  if (cudaMalloc(&g_dev.error_flag, sizeof(int)) != cudaSuccess)
+  if (cudaMalloc(&d.error_flag, sizeof(int)) != cudaSuccess)
     return fail(NNCV_B200_ENOMEM, "cudaMalloc(error flag) failed");
-  cudaMemset(g_dev.error_flag, 0, sizeof(int));
-  g_dev.ready = true;
+  cudaMemset(d.error_flag, 0, sizeof(int));
+  d.ready = true;
+  t_dev = &d;
   return NNCV_B200_OK;
+}
+
+// Context of the calling thread's current device if one exists already (never creates one).
+Device* current_device_or_null() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (dev < 0 || dev >= kMaxDevices || !g_devices[dev] || !g_devices[dev]->ready) return nullptr;
+  return g_devices[dev];
 }
 
 int ensure_scratch(size_t bytes) {
@@ -172,15 +199,39 @@ void prof_clear() {
   g_prof.clear();
 }
 
-// Reads and clears the device-side status word; call after the stream has been synchronised.
-int check_kernel_status() {
+// Turns a non-zero device status word into a status code and message.
+int report_kernel_error(int flag, const char* where) {
+  switch (flag) {
+    case kErrWaitProducer:
+      return fail(NNCV_B200_ETIMEOUT, "%s: the copy-issuing role of a kernel gave up a bounded wait for a free stage (code 1)", where);
+    case kErrWaitLoader:
+      return fail(NNCV_B200_ETIMEOUT, "%s: the weight loader of a kernel gave up a bounded wait for a free stage (code 2)", where);
+    case kErrWaitMma:
+      return fail(NNCV_B200_ETIMEOUT, "%s: the MMA-issuing role of a kernel gave up a bounded wait for a full stage (code 3)", where);
+    case kErrWaitEpilogue:
+      return fail(NNCV_B200_ETIMEOUT, "%s: the epilogue of a kernel gave up a bounded wait for its accumulator (code 4)", where);
+    case kErrBounds:
+      return fail(NNCV_B200_ECUDA, "%s: a kernel refused a copy that would have left its buffer (range check, code 5)", where);
+    default:
+      return fail(NNCV_B200_ECUDA, "%s: a kernel left the unknown status word %d", where, flag);
+  }
+}
+
+// Reads (4-byte copy, cannot fault) and clears the device-side status word of the current
+// device; call after the stream has been synchronised.  *flag_out receives the raw word.
+int read_kernel_status(int* flag_out) {
   int flag = 0;
   CU(cudaMemcpy(&flag, g_dev.error_flag, sizeof(int), cudaMemcpyDeviceToHost));
-  if (flag != 0) {
-    cudaMemset(g_dev.error_flag, 0, sizeof(int));
-    return fail(NNCV_B200_ETIMEOUT, "a kernel gave up a bounded wait (code %d)", flag);
-  }
+  if (flag != 0) cudaMemset(g_dev.error_flag, 0, sizeof(int));
+  *flag_out = flag;
   return NNCV_B200_OK;
+}
+
+int check_kernel_status() {
+  int flag = 0;
+  int rc = read_kernel_status(&flag);
+  if (rc) return rc;
+  return flag ? report_kernel_error(flag, "forward") : NNCV_B200_OK;
 }
 
 bool is_device_ptr(const void* p) {
@@ -268,6 +319,7 @@ struct ConvChoice {
 struct nncv_b200_conv {
   int Kout = 0, C = 0, R = 1, S = 1, stride = 1, pad = 0;
   int Cpad = 0;
+  int device = -1;     // CUDA device the plan's buffers live on
   DType dtype = kF16;  // activation / operand type
   int algo = 0;
   // raw weights on the device, element strides for W[n][c][tap]
@@ -504,14 +556,20 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
             if (okl && t < ms) ms = t;
           }
           if (!okl) { cudaGetLastError(); continue; }
+          // A candidate that gave up (a bounded wait ran out, a range check refused a copy) leaves early
+          // and would look fastest: read the status word and never choose, keep or persist such a one.
+          int flag = 0;
+          if (read_kernel_status(&flag) != NNCV_B200_OK || flag != 0) continue;
           if (ms < best) { best = ms; best_ch = k; }
         }
         cudaEventDestroy(e0);
         cudaEventDestroy(e1);
         it = c->tuned.emplace(key, best_ch).first;
-        char cval[64];
-        snprintf(cval, sizeof(cval), "%d %d %d %d", best_ch.kernel, best_ch.bn, best_ch.mt, best_ch.resident);
-        g_tune_cache.put(ckey, cval);
+        if (best < 1e30f) {   // only a choice that was measured without a complaint goes to the cache file
+          char cval[64];
+          snprintf(cval, sizeof(cval), "%d %d %d %d", best_ch.kernel, best_ch.bn, best_ch.mt, best_ch.resident);
+          g_tune_cache.put(ckey, cval);
+        }
       }
       ch = it->second;
     }
@@ -623,7 +681,12 @@ struct Model {
   std::vector<std::unique_ptr<DevBuf>> acts;
   size_t act_next = 0;
 };
-std::unique_ptr<Model> g_model;
+void model_reset() {
+  if (t_dev && t_dev->model) {
+    delete t_dev->model;
+    t_dev->model = nullptr;
+  }
+}
 
 DType dt_from_width(size_t w) { return w == 4 ? kF32 : kF16; }
 
@@ -661,6 +724,7 @@ int model_build(int depth, const void* host_blob, size_t n_elements, size_t ele_
   for (auto& g : m->spec.groups) {
     auto c = std::make_unique<nncv_b200_conv>();
     c->Kout = g.cout; c->C = g.cin; c->R = g.k; c->S = g.k; c->stride = g.stride; c->pad = g.pad;
+    c->device = g_dev.id;
     c->dtype = m->act_dt;
     c->Cpad = m->act_dt == kF32 ? (g.cin + 3) / 4 * 4 : (g.cin + 7) / 8 * 8;
     if (m->act_dt != kF32 && conv3x3_supported(g.cin, g.cout, g.k, g.k, g.stride, g.pad)) c->algo = 2;
@@ -682,6 +746,7 @@ int model_build(int depth, const void* host_blob, size_t n_elements, size_t ele_
   // FC: weight [1000, fc_in] is already "[Kout][C]" (the forward's transpose generic,
   // Res18.mlir:617-620, is absorbed by reading it K-major); bias in fp32.
   m->fc = std::make_unique<nncv_b200_conv>();
+  m->fc->device = g_dev.id;
   m->fc->Kout = 1000; m->fc->C = m->spec.fc_in; m->fc->Cpad = m->spec.fc_in; m->fc->dtype = m->act_dt;
   m->fc->raw = at(m->spec.off_fc_w); m->fc->raw_dt = pdt;
   m->fc->sn = m->spec.fc_in; m->fc->sc = 1; m->fc->stap = 1;
@@ -690,7 +755,8 @@ int model_build(int depth, const void* host_blob, size_t n_elements, size_t ele_
   LAUNCH(launch_convert(at(m->spec.off_fc_b), pdt, m->fc_bias.p, kF32, 1000, st));
   CU(cudaStreamSynchronize(st));
   m->host_blob_id = host_blob;
-  g_model = std::move(m);
+  model_reset();
+  g_dev.model = m.release();
   return ok();
 }
 
@@ -703,7 +769,7 @@ int ensure_workspace(Model& m, int N, int H, int W) {
   const int h1 = (H + 6 - 7) / 2 + 1, w1 = (W + 6 - 7) / 2 + 1;
   const int h2 = (h1 + 2 - 3) / 2 + 1, w2 = (w1 + 2 - 3) / 2 + 1;
   if (h1 <= 0 || w1 <= 0 || h2 <= 0 || w2 <= 0) return fail(NNCV_B200_EINVAL, "input %dx%d too small", H, W);
-  if (g_dev.ready) cudaDeviceSynchronize();
+  cudaDeviceSynchronize();
   m.acts.clear();
   m.act_next = 0;
   int rc = 0;
@@ -861,6 +927,9 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
                   cudaEventElapsedTime(&ms_sep, e[0], e[1]);
                   cudaEventElapsedTime(&ms_fused, e[1], e[2]);
                 }
+                int flag = 0;
+                if (!rc) rc = read_kernel_status(&flag);
+                if (!rc && flag) rc = report_kernel_error(flag, "timing the fused downsample launch");
               }
               g_prof_on = was;
               for (auto& ev : e) cudaEventDestroy(ev);
@@ -960,7 +1029,7 @@ int forward_impl(nncv_memref2* dst, nncv_memref4* src, void* params, cudaStream_
                  bool device_only) {
   int rc = device_init();
   if (rc) return rc;
-  if (!g_model) {
+  if (!g_dev.model) {
     // Lazy plan from the blob descriptor: element count selects the network; the element type of
     // a bare descriptor is float (the only type the reference's -split-params writes,
     // SplitParamsFlatArray.cpp:144-147).
@@ -975,11 +1044,11 @@ int forward_impl(nncv_memref2* dst, nncv_memref4* src, void* params, cudaStream_
     if (rc) return rc;
   } else if (params) {
     auto* pd = static_cast<nncv_memref1*>(params);
-    if ((size_t)pd->sizes[0] != g_model->spec.total)
+    if ((size_t)pd->sizes[0] != g_dev.model->spec.total)
       return fail(NNCV_B200_EINVAL, "params hold %ld elements, the loaded model has %zu", (long)pd->sizes[0],
-                  g_model->spec.total);
+                  g_dev.model->spec.total);
   }
-  Model& m = *g_model;
+  Model& m = *g_dev.model;
   int N, H, W;
   if ((rc = check_src(src, &N, &H, &W))) return rc;
   bool allocated_here = false;
@@ -1178,7 +1247,9 @@ int nncv_b200_load(const char* net, const char* model_bin_path, const nncv_b200_
         return fail(NNCV_B200_EINVAL, "tensor %zu (%s) should hold %d batch-norm values", t + j, a->idx[t + j].name, g.cout);
   }
   const size_t ew = a->idx[0].eleWidth;
-  g_model.reset();
+  int rc = device_init();
+  if (rc) return rc;
+  model_reset();
   return model_build(depth, a->data.data(), (size_t)a->wrapped.sizes[0], ew, opts);
 }
 
@@ -1188,14 +1259,19 @@ int nncv_b200_load_blob(const char* net, const void* blob, size_t n_elements, si
   const int depth = depth_from_name(net);
   if (!depth) return fail(NNCV_B200_EINVAL, "net must be \"resnet18\" or \"resnet50\"");
   if (!blob) return fail(NNCV_B200_EINVAL, "blob is null");
-  g_model.reset();
+  int rc = device_init();
+  if (rc) return rc;
+  model_reset();
   return model_build(depth, blob, n_elements, ele_width, opts);
 }
 
 int nncv_b200_unload(void) {
   std::lock_guard<std::mutex> lk(g_mutex);
-  if (g_dev.ready) cudaDeviceSynchronize();
-  g_model.reset();
+  t_dev = current_device_or_null();
+  if (t_dev) {
+    cudaDeviceSynchronize();
+    model_reset();
+  }
   return ok();
 }
 
@@ -1206,7 +1282,9 @@ void _mlir_ciface_forward(nncv_memref2* dst, nncv_memref4* src, void* params) {
 
 int nncv_b200_forward_device(nncv_memref2* dst, nncv_memref4* src, void* cuda_stream) {
   std::lock_guard<std::mutex> lk(g_mutex);
-  if (!g_model) return fail(NNCV_B200_ENOMODEL, "no model loaded");
+  int rc = device_init();
+  if (rc) return rc;
+  if (!g_dev.model) return fail(NNCV_B200_ENOMODEL, "no model loaded on device %d", g_dev.id);
   return forward_impl(dst, src, nullptr, (cudaStream_t)cuda_stream, true);
 }
 
@@ -1221,7 +1299,7 @@ int nncv_b200_set_stream(void* cuda_stream, int enable) {
 
 int nncv_b200_profile(int enable) {
   std::lock_guard<std::mutex> lk(g_mutex);
-  if (g_dev.ready) cudaDeviceSynchronize();
+  if (current_device_or_null()) cudaDeviceSynchronize();
   prof_clear();
   g_prof_on = enable != 0;
   return ok();
@@ -1242,6 +1320,28 @@ int nncv_b200_profile_get(long long i, nncv_b200_prof_rec* out) {
   }
   out->kind = r.kind; out->M = r.M; out->N = r.N; out->K = r.K; out->bn = r.bn;
   out->flops = r.flops; out->bytes = r.bytes; out->ms = r.ms;
+  return ok();
+}
+
+int nncv_b200_device_status(void) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  int flag = 0;
+  if ((rc = read_kernel_status(&flag))) return rc;
+  if (flag) return report_kernel_error(flag, "device status");
+  if (noalloc_read_status(g_dev.id, &flag) != 0)
+    return fail(NNCV_B200_ECUDA, "device status: reading the status word of the fixed scratch array failed");
+  if (flag) return report_kernel_error(flag, "device status (nncv_b200_matmul_noalloc)");
+  return ok();
+}
+
+int nncv_b200_selftest_wait_timeout(int log2_clocks, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (log2_clocks < 0 || log2_clocks > 24) return fail(NNCV_B200_EINVAL, "selftest: log2_clocks must be in [0, 24]");
+  LAUNCH(launch_wait_selftest(g_dev.error_flag, 1LL << log2_clocks, (cudaStream_t)stream));
   return ok();
 }
 
@@ -1315,7 +1415,7 @@ nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout
     return nullptr;
   }
   auto c = std::make_unique<nncv_b200_conv>();
-  c->Kout = Kout; c->C = C; c->R = R; c->S = S; c->stride = stride; c->pad = pad;
+  c->Kout = Kout; c->C = C; c->R = R; c->S = S; c->stride = stride; c->pad = pad; c->device = g_dev.id;
   c->dtype = (DType)dtype; c->algo = algo == 3 ? 0 : algo; c->force_gather = algo == 3;
   c->Cpad = dtype == NNCV_B200_F32 ? (C + 3) / 4 * 4 : (C + 7) / 8 * 8;
   const size_t bytes = (size_t)Kout * C * R * S * dtype_size((DType)w_dtype);
@@ -1332,7 +1432,7 @@ nncv_b200_conv* nncv_b200_conv_create(const void* weights, int w_dtype, int Kout
 
 void nncv_b200_conv_destroy(nncv_b200_conv* c) {
   std::lock_guard<std::mutex> lk(g_mutex);
-  if (c && g_dev.ready) cudaDeviceSynchronize();
+  if (c && current_device_or_null()) cudaDeviceSynchronize();
   delete c;
 }
 
@@ -1342,7 +1442,10 @@ int nncv_b200_conv_run(nncv_b200_conv* c, const void* in, void* out, int N, int 
   std::lock_guard<std::mutex> lk(g_mutex);
   if (!c || !in || !out) return fail(NNCV_B200_EINVAL, "conv_run: null argument");
   cudaStream_t st = (cudaStream_t)stream;
-  int rc;
+  int rc = device_init();
+  if (rc) return rc;
+  if (c->device != g_dev.id)
+    return fail(NNCV_B200_EINVAL, "conv_run: the plan lives on device %d, the current device is %d", c->device, g_dev.id);
   if (c->algo == 2) {
     // The kernel works on shared-pad NHWC; this entry point takes dense NHWC, so convert on both
     // sides (the network executor keeps its activations in shared-pad form and skips this).
@@ -1414,6 +1517,9 @@ int nncv_b200_conv_run_fused(nncv_b200_conv* c, nncv_b200_conv* branch, const vo
   if (rc) return rc;
   if (!c || !branch || !in || !out || !out_branch) return fail(NNCV_B200_EINVAL, "conv_run_fused: null argument");
   if (N <= 0 || H <= 0 || W <= 0) return fail(NNCV_B200_EINVAL, "conv_run_fused: bad shape");
+  if (c->device != g_dev.id || branch->device != g_dev.id)
+    return fail(NNCV_B200_EINVAL, "conv_run_fused: the plans live on device %d / %d, the current device is %d", c->device,
+                branch->device, g_dev.id);
   if (!fused_branch_ok(*c, *branch))
     return fail(NNCV_B200_EINVAL, "conv_run_fused: needs an odd square filter with pad = R/2 and a 1x1 pad-0 branch of the "
                                   "same stride, channels and (multiple of 128) output channels, 16-bit, algo 0");

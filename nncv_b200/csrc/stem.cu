@@ -60,22 +60,7 @@ constexpr int kWBytes = 7 * 4096;   // packed weights: 7 filter rows x [64 x 32]
 constexpr int kWBytesSw = 4 * 8192; // swizzled variant: 4 filter-row pairs x [64 x 64] fp16
 constexpr int kSwSlot = 16384;      // swizzled variant: one row pair as a [128 pixels x 128 B] operand tile
 
-// Optional clock64() trace of CTA 0 (built only with -DNNCV_B200_TRACE; a tuning aid).
-#ifdef NNCV_B200_TRACE
-unsigned long long* g_stem_trace = nullptr;  // device buffer [2 roles][64 rows][8 stamps]
-#define ST_TRACE(role, idx, k)                                                            \
-  do {                                                                                    \
-    if (p.trace && blockIdx.x == 0 && (idx) < 64)                                          \
-      p.trace[((role) * 64 + (idx)) * 8 + (k)] = (unsigned long long)clock64();            \
-  } while (0)
-#else
-#define ST_TRACE(role, idx, k) \
-  do {                         \
-  } while (0)
-#endif
-
 struct StemParams {
-  unsigned long long* trace;
   const uint8_t* in_rows;   // [N][H][RW] pixels of 8 bytes
   const uint8_t* wpack;     // kWBytes
   const float* scale;
@@ -189,9 +174,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
         const uint8_t* img = p.in_rows + (size_t)n * p.H * p.row_bytes;
         for (int pk = ir0; pk <= ir1; ++pk, ++seq) {
           const uint32_t slot = seq % kRingSlots;
-          ST_TRACE(0, 32 + seq, 6);
           if (!ptx::mbar_wait_abortable(empty + 8 * slot, ((seq / kRingSlots) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
-          ST_TRACE(0, 32 + seq, 7);
           if (SW) {
             ptx::mbar_arrive_expect_tx(full + 8 * slot, (uint32_t)kSwSlot);
             ptx::tma_load_3d(sRing + slot * p.slot_bytes, &tm_in, 0, 0, n * (p.H >> 1) + pk, full + 8 * slot);
@@ -228,11 +211,9 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
         if (!item_of(i, n, p0, p1, y0, y1, ir0, ir1)) break;
         for (int pk = ir0; pk <= ir1 && okw; ++pk, ++seq) {
           const uint32_t slot = seq % kRingSlots;
-          ST_TRACE(0, seq, 0);
           // the scout warp has seen the pair's tile arrive, the epilogue move past pair seq - 8 and
           // the accumulator slots of the rows this pair starts come free
           if (!ptx::mbar_wait_abortable(go + 8 * (seq & 3u), (seq >> 2) & 1u, abort_flag)) { okw = false; break; }
-          ST_TRACE(0, seq, 5);
           ptx::tc_fence_after();
           const uint32_t a_lo = ring_lo + slot * (uint32_t)(kSwSlot >> 4);
           if (pk > ir0 && pk < ir1 && pk - 1 >= y0 && pk + 2 <= y1) {
@@ -240,7 +221,6 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
             // where the slots wrap), row pk+2 starts (N = 64, accumulate off at the first K step).
             const uint32_t c_lo = rc_base + (uint32_t)(pk - 1 - y0);
             const uint32_t cf = c_lo + 3;
-            ST_TRACE(0, seq, 1);
             const uint32_t s0 = c_lo % kAcc;
             if (s0 + 3 <= kAcc) {
 #pragma unroll
@@ -262,16 +242,13 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
             for (uint32_t k4 = 0; k4 < 4; ++k4)
               ptx::umma_f16(tmem_base + (cf % kAcc) * 64, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
                             ptx::desc_from_halves(w_lo + 3u * 512u + k4 * 2, ptx::kSmemDescK128Hi), idesc64, k4 > 0 ? 1u : 0u);
-            ST_TRACE(0, seq, 2);
             ptx::tc_commit(empty + 8 * slot);
-            ST_TRACE(0, seq, 3);
             continue;
           }
           const int lo = max(y0, pk - 1), hi = min(y1, pk + 2);
           // rows that get their first partial sum from this pair: all of them for the first pair
           // of the item, else only row pk + 2
           const int fresh_lo = (pk == ir0) ? lo : (pk + 2 <= y1 ? pk + 2 : hi + 1);
-          ST_TRACE(0, seq, 1);
           // rows [a, b] -> consecutive accumulator slots, in two pieces where the slot index wraps:
           // TMEM address, weight descriptor (low word) and instruction descriptor of each piece
           auto split = [&](int a, int b, uint32_t (&d)[2], uint32_t (&bl)[2], uint32_t (&id)[2]) -> int {
@@ -307,9 +284,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
                               ptx::desc_from_halves(bF[pc] + k4 * 2, ptx::kSmemDescK128Hi), iF[pc], k4 > 0 ? 1u : 0u);
             }
           }
-          ST_TRACE(0, seq, 2);
           ptx::tc_commit(empty + 8 * slot);
-          ST_TRACE(0, seq, 3);
         }
         rc_base += (uint32_t)(y1 - y0 + 1);
       }
@@ -381,7 +356,6 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
             if (!ptx::mbar_wait_abortable(full + 8 * (s % kRingSlots), (s / kRingSlots) & 1u, abort_flag)) { okw = false; break; }
           }
           if (!okw) break;
-          ST_TRACE(0, acc_cnt, 5);
           ptx::tc_fence_after();
           // shared-memory address of each filter row's input row (0 = zero padding row, skipped)
           uint32_t row_addr[7];
@@ -397,9 +371,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
           for (int xt = 0; xt < p.x_tiles && okw; ++xt, ++acc_cnt) {
             if ((acc_cnt & 1u) != issuer) continue;
             const uint32_t ab = acc_cnt % kAcc;
-            ST_TRACE(0, acc_cnt, 0);
             if (!ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt / kAcc) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
-            ST_TRACE(0, acc_cnt, 1);
             ptx::tc_fence_after();
             uint32_t accumulate = 0;
             {
@@ -416,9 +388,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
               }
             }
             }
-            ST_TRACE(0, acc_cnt, 2);
             ptx::tc_commit(acc_full + 8 * ab);
-            ST_TRACE(0, acc_cnt, 3);
           }
         }
         seq_base += (uint32_t)(ir1 - ir0 + 1);
@@ -528,9 +498,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
         const int ym = 2 * pr;                         // middle row of the window
         const bool has_bot = ym + 1 <= p.OH - 1;
         const int nrows = has_bot ? 2 : 1;
-        if (et == 0) ST_TRACE(1, acc_cnt, 0);
         if (!wait_accs(nrows * p.x_tiles, epi_seq_base + (uint32_t)(min(ir1, ym + nrows) - ir0))) { okw = false; break; }
-        if (et == 0) ST_TRACE(1, acc_cnt, 1);
         release_rows(ym + nrows - 1);
         const uint32_t vrow = sConv + (uint32_t)(pr & 1) * crow_bytes;
 #pragma unroll
@@ -559,9 +527,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
         }
         acc_cnt += (uint32_t)(nrows * p.x_tiles);
         has_prev = has_bot;
-        if (et == 0) ST_TRACE(1, acc_cnt - 1, 2);
         ptx::named_bar_sync(1, kEpiThreads);   // the vertical maxima of pooled row pr are in shared memory
-        if (et == 0) ST_TRACE(1, acc_cnt - 1, 3);
         {
           uint16_t* orow = p.out + ((size_t)((size_t)n * p.ol.img_rows + pr + p.ol.off) * p.ol.pitch + p.ol.off) * 64;
           for (int u = et; u < p.PW * 8; u += kEpiThreads) {
@@ -580,7 +546,6 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
             for (int h = 0; h < 4; ++h) m[h] = hmax(hmax(hmax(v[0][h], v[1][h]), v[2][h]), zero);   // ReLU after the max
             *reinterpret_cast<uint4*>(orow + (size_t)px * 64 + c * 8) = make_uint4(m[0], m[1], m[2], m[3]);
           }
-          if (et == 0) ST_TRACE(1, acc_cnt - 1, 4);
         }
         // the row of maxima two steps ahead reuses this buffer; every thread passes the barrier
         // of the next step (after its own pooling) before anyone writes it again
@@ -757,9 +722,6 @@ cudaError_t by_dt(DType t, F&& f) {
 
 }  // namespace
 
-#ifdef NNCV_B200_TRACE
-extern "C" void nncv_b200_debug_set_stem_trace(unsigned long long* dev_buf) { g_stem_trace = dev_buf; }
-#endif
 
 bool g_stem_force_plain = false;     // tests: keep the un-swizzled kernel
 int g_stem_last_variant = 0;         // which variant the last launch used
@@ -838,11 +800,6 @@ cudaError_t launch_pack_stem_weights(const void* w, DType w_dt, void* dst, DType
 cudaError_t launch_stem_pool(const StemArgs& a, cudaStream_t stream) {
   if (a.ab == kF32 || a.N <= 0 || a.H < 7 || a.W < 7) return cudaErrorInvalidValue;
   StemParams p;
-#ifdef NNCV_B200_TRACE
-  p.trace = g_stem_trace;
-#else
-  p.trace = nullptr;
-#endif
   p.in_rows = static_cast<const uint8_t*>(a.in_rows);
   p.wpack = static_cast<const uint8_t*>(a.wpack);
   p.scale = a.scale; p.shift = a.shift;

@@ -1,8 +1,8 @@
 """Generates the committed fixtures under tests/golden/.  Run where the nncv source tree is
-available (its location is REF below; a GPU box has no such tree, so the tests read only the files
-this script wrote):
+available (its location comes from the environment variable NNCV_REFERENCE; a GPU box has no such
+tree, so the tests read only the files this script wrote):
 
-    python tests/golden/make_golden.py
+    NNCV_REFERENCE=<nncv source tree> python tests/golden/make_golden.py
 
   res18_constants.json   shapes of the constants of tests/Nets/Res18.mlir:12-110, in order
   kat0_two_params.bin    the SplitParams known-answer weights (tests/SplitParams/getParams.py:15-29)
@@ -29,7 +29,9 @@ from oracle import binding as ob  # noqa: E402
 from nncv_b200.split_params import random_input, random_state_dict, to_flat_array  # noqa: E402
 import torch_ref  # noqa: E402
 
-REF = "/root/reference"
+REF = os.environ.get("NNCV_REFERENCE")
+if not REF or not os.path.isdir(REF):
+    raise SystemExit("set NNCV_REFERENCE to the nncv source tree")
 
 
 def constants():
