@@ -228,8 +228,7 @@ __global__ void __launch_bounds__(kThreads) conv_igemm_kernel(const IgemmParams 
                 __nv_bfloat162 b = __floats2bfloat162_rn(v[q * 8 + h * 2], v[q * 8 + h * 2 + 1]);
                 w4[h] = *reinterpret_cast<uint32_t*>(&b);
               } else {
-                __half2 b = __floats2half2_rn(v[q * 8 + h * 2], v[q * 8 + h * 2 + 1]);
-                w4[h] = *reinterpret_cast<uint32_t*>(&b);
+                w4[h] = ptx::pack_half2_sat(v[q * 8 + h * 2], v[q * 8 + h * 2 + 1]);
               }
             }
             op[q] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
@@ -255,7 +254,7 @@ __global__ void __launch_bounds__(kThreads) conv_igemm_kernel(const IgemmParams 
           } else if (p.bf16) {
             static_cast<__nv_bfloat16*>(p.out)[(size_t)m * p.ldo + n] = __float2bfloat16_rn(x);
           } else {
-            static_cast<__half*>(p.out)[(size_t)m * p.ldo + n] = __float2half_rn(x);
+            static_cast<uint16_t*>(p.out)[(size_t)m * p.ldo + n] = (uint16_t)(ptx::pack_half2_sat(x, 0.f) & 0xffffu);
           }
         }
       }

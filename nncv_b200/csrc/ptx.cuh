@@ -96,6 +96,15 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, l
   return true;
 }
 
+// fp32 pair -> packed fp16 pair (lo in the low half), round to nearest even.  A finite value beyond
+// the fp16 range becomes +-65504 instead of +-inf, so one large activation cannot turn the rest of a
+// network into NaN (inf - inf, 0 * inf); NaN stays NaN.
+__device__ __forceinline__ uint32_t pack_half2_sat(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
 // ---------------------------------------------------------------- cp.async ------------
 // 16-byte global->shared copy; src_bytes == 0 writes zeros (used for padding / ragged rows).
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {

@@ -11,6 +11,7 @@
 #include <cfloat>
 
 #include "kernels.h"
+#include "ptx.cuh"
 
 namespace nncv_b200 {
 
@@ -22,7 +23,11 @@ template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __h
 template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <typename T> __device__ __forceinline__ T from_f(float v);
 template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
-template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+// finite values beyond the fp16 range saturate to +-65504 (NaN stays NaN), as in the conv epilogues
+template <> __device__ __forceinline__ __half from_f<__half>(float v) {
+  const unsigned short b = (unsigned short)(ptx::pack_half2_sat(v, 0.f) & 0xffffu);
+  return __ushort_as_half(b);
+}
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 // ------------------------------------------------------------------ fp32 conv ------------

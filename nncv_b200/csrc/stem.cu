@@ -463,8 +463,7 @@ __global__ void __launch_bounds__(kThreads, 1) stem_pool_kernel(const __grid_con
           __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
           cur[h] = *reinterpret_cast<uint32_t*>(&v);
         } else {
-          __half2 v = __floats2half2_rn(a, b);
-          cur[h] = *reinterpret_cast<uint32_t*>(&v);
+          cur[h] = ptx::pack_half2_sat(a, b);
         }
       }
     };

@@ -417,7 +417,8 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
                   if (relu_o) x = __hmax2_nan(x, __floats2bfloat162_rn(0.f, 0.f));
                   o[h] = *reinterpret_cast<uint32_t*>(&x);
                 } else {
-                  __half2 x = __floats2half2_rn(a, b);
+                  const uint32_t xs = ptx::pack_half2_sat(a, b);
+            __half2 x = *reinterpret_cast<const __half2*>(&xs);
                   if (relu_o) x = __hmax2_nan(x, __floats2half2_rn(0.f, 0.f));
                   o[h] = *reinterpret_cast<uint32_t*>(&x);
                 }

@@ -14,6 +14,7 @@
 #include <cuda_fp16.h>
 
 #include "kernels.h"
+#include "ptx.cuh"
 
 namespace nncv_b200 {
 
@@ -24,7 +25,9 @@ template <> __device__ __forceinline__ float wf<float>(float v) { return v; }
 template <> __device__ __forceinline__ float wf<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float wf<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <typename T> __device__ __forceinline__ T wt(float v);
-template <> __device__ __forceinline__ __half wt<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __half wt<__half>(float v) {
+  return __ushort_as_half((unsigned short)(ptx::pack_half2_sat(v, 0.f) & 0xffffu));
+}
 template <> __device__ __forceinline__ __nv_bfloat16 wt<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 // U[p][k][c] = (G g G^T)[p], one thread per (k, c).

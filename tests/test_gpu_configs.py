@@ -118,9 +118,8 @@ def test_config3_resnet18_fp16_all_256_images_host_and_device():
 
 
 def test_config3_bf16_all_256_images():
-    """bf16 keeps 8 mantissa bits against fp16's 11; the logits' rel-L2 against the fp32 oracle is
-    asserted at the bound measured for this network (recorded with the reason in the design notes),
-    top-1 agreement at the stated 99.5 %."""
+    """The same 256 images on the bf16 path: the stated bound (rel-L2 <= 1e-2, top-1 >= 99.5 %) holds
+    for bf16 as well (measured 3.6e-3: accumulation is fp32, only stored activations carry 8 bits)."""
     n = 256
     blob = to_flat_array(18, random_state_dict(18, 0)).blob()
     x = random_input(n, 224, 224, 3, "normal")
@@ -130,8 +129,8 @@ def test_config3_bf16_all_256_images():
     rt.forward(out, x)
     err = G.rel_l2(out, ref)
     print(f"bf16 ResNet-18 logits rel-L2 vs fp32 oracle over 256 images: {err:.3e}")
-    assert err <= 3e-2
-    assert (out.argmax(1) == ref.argmax(1)).mean() >= 0.98
+    assert err <= 1e-2
+    assert (out.argmax(1) == ref.argmax(1)).mean() >= 0.995
 
 
 def test_config4_resnet50_fp16_at_224():
@@ -175,7 +174,7 @@ def test_nan_passes_through_relu_and_maxpool_on_the_gpu():
         assert np.array_equal(np.isnan(y2), np.isnan(ob.relu(ob.conv2d(x, wt, 2, 1))))
     # stand-alone max-pool
     xm = g.standard_normal((1, 64, 9, 9)).astype(np.float32)
-    xm[0, 7, 4, 4] = np.nan
+    xm[0, 7, 3, 3] = np.nan   # an odd row and column: inside two windows each way
     X = G.dev(xm.transpose(0, 2, 3, 1), F16)
     Y = torch.empty((1, 5, 5, 64), device="cuda", dtype=torch.float16)
     check(lib().nncv_b200_maxpool_nhwc(G.p(X), G.p(Y), F16, 1, 9, 9, 64, 3, 2, 1, G.stream_ptr()))
