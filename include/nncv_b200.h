@@ -83,7 +83,7 @@ typedef struct {
  * examples/Res18/main.cpp:18-23: the C-interface wrapper MLIR emits for @forward under
  * -wrap-c-interface (DnnModelLowering.cpp:769-771) with the split-params argument inserted as
  * function argument #1 (SplitParamsFlatArray.cpp:189-192).
- *   dst    [N,1000] logits, written in place at dst->aligned + dst->offset (strides honoured).
+ *   dst    [N,1000] logits (the output width of the loaded plan), written in place at dst->aligned + dst->offset (strides honoured).
  *          If dst->aligned is NULL the buffer is malloc'ed and the descriptor filled in.
  *   src    [N,3,H,W] dense NCHW.  N is taken from the descriptor at run time.
  *   params nncv_memref1* over the whole parameter blob (what MemRefFlatArray::get() returns,
@@ -96,12 +96,30 @@ void _mlir_ciface_forward(nncv_memref2* dst, nncv_memref4* src, void* params);
 
 /* Weight loading: the counterpart of `nncv-c -split-params` + MemRefFlatArray::read
  * (src/nncv/compiler/main.cpp:102-103, src/libnncv/DataType.cpp:48-87): parses the container,
- * checks it against the named network ("resnet18" or "resnet50"), uploads the blob once, folds
- * batch-norm into per-channel scale/shift and packs the conv/FC weights for the kernels. */
+ * checks it against the network's layer plan, uploads the blob once, folds batch-norm into
+ * per-channel scale/shift and packs the conv/FC weights for the kernels.
+ * net names the layer plan: "resnet18" / "resnet50" (built in; tensor order of
+ * tests/Nets/Res18.mlir:12-109), "plan:<text>", or the path of a plan file.  A plan is what nncv's
+ * lowering pipeline would have baked into the compiled object (DnnModelLowering.cpp:614-797: the op
+ * sequence of @forward; SplitParamsFlatArray.cpp:48-56: the element offset of every constant in
+ * the blob); `python -m nncv_b200.mlir_import model.mlir model.plan` writes one from the
+ * torch-mlir linalg module nncv-c takes as input.  Plan text, one node per line:
+ *   nncv_b200_plan 1
+ *   params <elements in the blob> out <output features>
+ *   conv id= in= res= cin= cout= k= stride= pad= relu= w= gamma= beta= mean= var=
+ *   maxpool id= in= k= stride= pad=        avgpool id= in=        fc id= in= cin= cout= w= b=
+ * (tensor 0 is the input; res = tensor added before the ReLU or -1; w, gamma, ... are element
+ * offsets into the blob; the FC node comes last and reads a global average pool). */
 int nncv_b200_load(const char* net, const char* model_bin_path, const nncv_b200_opts* opts);
 /* Same, from a blob already in host memory (tensors back to back in file order). */
 int nncv_b200_load_blob(const char* net, const void* blob, size_t n_elements, size_t ele_width,
                         const nncv_b200_opts* opts);
+/* Parses and validates a plan (same `net` argument as nncv_b200_load) without touching a device;
+ * reports the blob size it expects, its node count and output width. */
+int nncv_b200_plan_check(const char* net, size_t* n_params, int* n_nodes, int* out_features);
+/* The plan `net` names, as canonical plan text (the built-in networks included): copies at most
+ * cap - 1 bytes plus a terminator into buf and returns the full length, or -1 on error. */
+long long nncv_b200_plan_text(const char* net, char* buf, size_t cap);
 int nncv_b200_unload(void);
 /* Forward with an explicit CUDA stream and device-resident src/dst; does not synchronise.
  * The same computation as _mlir_ciface_forward without the host copies. */
@@ -128,6 +146,18 @@ int nncv_b200_device_status(void);
 int nncv_b200_selftest_wait_timeout(int log2_clocks, void* stream);
 /* Number of kernels of this library launched since load (for benchmark accounting). */
 long long nncv_b200_launch_count(void);
+
+/* Activation memory planning.  nncv's MemSolver (include/nncv/compiler/Optimizer/MemSolver.hpp:55-70:
+ * registerTensor(first op, last op, size) / solve() / getTotalConsumption(); known answer 124 in
+ * tests/MemSolver/test.cpp:17-37) assigns every tensor an offset in one block with "greedy by size
+ * for offset calculation".  nncv_b200_arena_plan is that planner: tensors whose [first_op, last_op]
+ * intervals (both ends included) intersect never overlap in memory; sizes are rounded up to `align`
+ * bytes (0 or 1: none).  Host only, needs no device.  The executor uses it for the activation
+ * tensors of a forward; nncv_b200_activation_bytes reports, after a forward, the size of the arena
+ * and what one private buffer per tensor would have taken. */
+int nncv_b200_arena_plan(size_t n, const int* first_op, const int* last_op, const size_t* size, size_t align,
+                         size_t* offset_out, size_t* total_out);
+int nncv_b200_activation_bytes(size_t* arena_bytes, size_t* unshared_bytes);
 
 /* Per-launch timing with CUDA events on the launching stream (off by default).  The reference
  * only has wall-clock timers around the whole forward (examples/Res18/main.cpp:95-99). */

@@ -20,6 +20,7 @@ EXPORTS = [
     "nncv_b200_forward_device", "nncv_b200_last_status", "nncv_b200_last_error",
     "nncv_b200_launch_count", "nncv_b200_set_stream", "nncv_b200_profile", "nncv_b200_profile_count",
     "nncv_b200_profile_get", "nncv_b200_device_status", "nncv_b200_selftest_wait_timeout",
+    "nncv_b200_arena_plan", "nncv_b200_activation_bytes", "nncv_b200_plan_check", "nncv_b200_plan_text",
     "nncv_flat_array_read", "nncv_flat_array_free", "nncv_flat_array_count",
     "nncv_flat_array_indexer", "nncv_flat_array_data", "nncv_flat_array_wrapped",
     "nncv_flat_array_write",
@@ -64,6 +65,12 @@ def lib() -> ctypes.CDLL:
     L.nncv_b200_launch_count.restype = c_longlong
     L.nncv_b200_set_stream.argtypes = [c_void_p, c_int]
     L.nncv_b200_device_status.restype = c_int
+    L.nncv_b200_arena_plan.argtypes = [c_size_t, POINTER(c_int), POINTER(c_int), POINTER(c_size_t), c_size_t,
+                                       POINTER(c_size_t), POINTER(c_size_t)]
+    L.nncv_b200_plan_text.argtypes = [c_char_p, ctypes.c_char_p, c_size_t]
+    L.nncv_b200_plan_text.restype = c_longlong
+    L.nncv_b200_plan_check.argtypes = [c_char_p, POINTER(c_size_t), POINTER(c_int), POINTER(c_int)]
+    L.nncv_b200_activation_bytes.argtypes = [POINTER(c_size_t), POINTER(c_size_t)]
     L.nncv_b200_selftest_wait_timeout.argtypes = [c_int, c_void_p]
     L.nncv_b200_profile.argtypes = [c_int]
     L.nncv_b200_profile_count.restype = c_longlong

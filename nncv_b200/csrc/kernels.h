@@ -5,6 +5,8 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+#include <vector>
+
 namespace nncv_b200 {
 
 enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
@@ -188,6 +190,15 @@ cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean
                            cudaStream_t stream);
 cudaError_t launch_convert(const void* src, DType src_dt, void* dst, DType dst_dt, size_t n,
                            cudaStream_t stream);
+
+// ---- activation arena planning (host only) ----------------------------------------------------
+struct ArenaTensor {
+  int first = 0, last = 0;   // ops that produce it / read it last, both included
+  size_t size = 0;           // bytes
+  size_t offset = 0;         // out: byte offset inside the arena
+};
+// Greedy by size for offset calculation; sizes are rounded up to `align`.  Returns the arena size.
+size_t arena_plan(std::vector<ArenaTensor>& tensors, size_t align);
 
 // ---- failure-path self-test: one bounded mbarrier wait that is left to run out ---------------
 cudaError_t launch_wait_selftest(int* error_flag, long long limit_clocks, cudaStream_t stream);

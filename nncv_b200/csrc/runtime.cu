@@ -594,71 +594,280 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
 }
 
 // =====================================================================================
-// network tables (tensor order of the params blob: tests/Nets/Res18.mlir:12-109)
+// layer plans
 // =====================================================================================
-struct Group {
-  int cin, cout, k, stride, pad;
-  size_t off_beta, off_gamma, off_var, off_mean, off_w;
+// A plan is the op sequence of @forward after the fusions nncv leaves to separate elementwise
+// generics (tests/Nets/Res18.mlir:118-629): conv + batch-norm (+ residual add) (+ ReLU) is one
+// node, then max-pool, global average pool and FC nodes.  Every parameter is named by its ELEMENT
+// offset inside the params blob, i.e. the running sum of the element counts of the constants before
+// it in module order, which is what -split-params bakes into the compiled object
+// (SplitParamsFlatArray.cpp:48-56,84-92).  Tensor 0 is the network input; node i produces tensor
+// `id`.  Built-in plans: ResNet-18 (constant order of Res18.mlir:12-109) and ResNet-50 (same rule,
+// torchvision v1.5 topology); any other plan arrives as text from the .mlir importer.
+struct PlanNode {
+  enum Kind { kConv = 0, kMaxPool = 1, kAvgPool = 2, kFc = 3 };
+  int kind = kConv;
+  int id = 0, in = 0, res = -1;    // tensor ids; res: residual added before the ReLU (conv only)
+  int cin = 0, cout = 0, k = 1, stride = 1, pad = 0, relu = 0;
+  int has_bn = 0;
+  size_t off_w = 0, off_gamma = 0, off_beta = 0, off_mean = 0, off_var = 0, off_b = 0;
+  // derived when the model is built
+  int conv_idx = -1;      // index into Model::convs
+  int branch = -1;        // node of a 1x1 conv on the same input that may ride along in this conv's launch
+  int fused_into = -1;    // the reverse link
+  int stem_pool = -1;     // conv: the max-pool node the fused stem kernel absorbs
+  int absorbed = 0;       // max-pool node computed by the stem kernel
 };
-struct NetSpec {
-  int depth = 0;
-  std::vector<Group> groups;  // forward order
-  int fc_in = 0;
-  size_t off_fc_b = 0, off_fc_w = 0, total = 0;
+struct Plan {
+  std::string name;
+  std::vector<PlanNode> nodes;   // forward order
+  size_t total = 0;              // elements in the params blob
+  int out_features = 0;
 };
 
-NetSpec build_spec(int depth) {
-  NetSpec s;
-  s.depth = depth;
-  auto add = [&](int cin, int cout, int k, int stride, int pad) {
-    s.groups.push_back(Group{cin, cout, k, stride, pad, 0, 0, 0, 0, 0});
-  };
+Plan builtin_plan(int depth) {
+  struct G { int cin, cout, k, stride, pad; size_t ob, og, ov, om, ow; };
+  std::vector<G> groups;
+  auto add = [&](int cin, int cout, int k, int stride, int pad) { groups.push_back(G{cin, cout, k, stride, pad, 0, 0, 0, 0, 0}); };
   add(3, 64, 7, 2, 3);
   const int widths[4] = {64, 128, 256, 512};
+  const int blocks50[4] = {3, 4, 6, 3};
   int cin = 64;
-  if (depth == 18) {
-    for (int l = 0; l < 4; ++l)
-      for (int b = 0; b < 2; ++b) {
-        const int stride = (b == 0 && l > 0) ? 2 : 1;
+  for (int l = 0; l < 4; ++l)
+    for (int b = 0; b < (depth == 18 ? 2 : blocks50[l]); ++b) {
+      const int stride = (b == 0 && l > 0) ? 2 : 1;
+      if (depth == 18) {
         add(cin, widths[l], 3, stride, 1);
         add(widths[l], widths[l], 3, 1, 1);
         if (b == 0 && l > 0) add(cin, widths[l], 1, 2, 0);
         cin = widths[l];
-      }
-    s.fc_in = 512;
-  } else {
-    const int blocks[4] = {3, 4, 6, 3};
-    for (int l = 0; l < 4; ++l)
-      for (int b = 0; b < blocks[l]; ++b) {
-        const int stride = (b == 0 && l > 0) ? 2 : 1;
+      } else {
         add(cin, widths[l], 1, 1, 0);
         add(widths[l], widths[l], 3, stride, 1);
         add(widths[l], widths[l] * 4, 1, 1, 0);
         if (b == 0) add(cin, widths[l] * 4, 1, stride, 0);
         cin = widths[l] * 4;
       }
-    s.fc_in = 2048;
-  }
+    }
+  const int fc_in = depth == 18 ? 512 : 2048;
+  Plan p;
+  p.name = depth == 18 ? "resnet18" : "resnet50";
   size_t off = 0;
-  s.off_fc_b = off; off += 1000;
-  s.off_fc_w = off; off += (size_t)1000 * s.fc_in;
-  for (int i = (int)s.groups.size() - 1; i >= 0; --i) {
-    Group& g = s.groups[i];
-    g.off_beta = off; off += g.cout;
-    g.off_gamma = off; off += g.cout;
-    g.off_var = off; off += g.cout;
-    g.off_mean = off; off += g.cout;
-    g.off_w = off; off += (size_t)g.cout * g.cin * g.k * g.k;
+  const size_t off_fc_b = off; off += 1000;
+  const size_t off_fc_w = off; off += (size_t)1000 * fc_in;
+  for (int i = (int)groups.size() - 1; i >= 0; --i) {   // params order: last group first
+    G& g = groups[i];
+    g.ob = off; off += g.cout;
+    g.og = off; off += g.cout;
+    g.ov = off; off += g.cout;
+    g.om = off; off += g.cout;
+    g.ow = off; off += (size_t)g.cout * g.cin * g.k * g.k;
   }
-  s.total = off;
-  return s;
+  p.total = off;
+  p.out_features = 1000;
+  int next_id = 1;
+  size_t gi = 0;
+  auto conv = [&](int in, int res, int relu) {
+    const G& g = groups[gi++];
+    PlanNode n;
+    n.kind = PlanNode::kConv; n.id = next_id++; n.in = in; n.res = res; n.relu = relu;
+    n.cin = g.cin; n.cout = g.cout; n.k = g.k; n.stride = g.stride; n.pad = g.pad; n.has_bn = 1;
+    n.off_w = g.ow; n.off_gamma = g.og; n.off_beta = g.ob; n.off_mean = g.om; n.off_var = g.ov;
+    p.nodes.push_back(n);
+    return n.id;
+  };
+  int x = conv(0, -1, 1);
+  {
+    PlanNode n;
+    n.kind = PlanNode::kMaxPool; n.id = next_id++; n.in = x; n.k = 3; n.stride = 2; n.pad = 1; n.cin = n.cout = 64;
+    p.nodes.push_back(n);
+    x = n.id;
+  }
+  for (int l = 0; l < 4; ++l)
+    for (int b = 0; b < (depth == 18 ? 2 : blocks50[l]); ++b) {
+      const bool has_ds = depth == 18 ? (b == 0 && l > 0) : (b == 0);
+      int t = conv(x, -1, 1);
+      if (depth == 50) t = conv(t, -1, 1);
+      // the last conv of the block comes before the downsample conv in the params order of the built-in
+      // nets (conv2/conv3, then downsample), but it needs the downsample result: emit the node after it
+      const size_t last_g = gi++;
+      int idn = x;
+      if (has_ds) idn = conv(x, -1, 0);
+      const size_t after = gi;
+      gi = last_g;
+      x = conv(t, idn, 1);
+      gi = after;
+    }
+  {
+    PlanNode n;
+    n.kind = PlanNode::kAvgPool; n.id = next_id++; n.in = x; n.cin = n.cout = fc_in;
+    p.nodes.push_back(n);
+    x = n.id;
+    PlanNode f;
+    f.kind = PlanNode::kFc; f.id = next_id++; f.in = x; f.cin = fc_in; f.cout = 1000; f.off_w = off_fc_w; f.off_b = off_fc_b;
+    p.nodes.push_back(f);
+  }
+  return p;
+}
+
+// Plan text: one node per line, "key=value" fields after the kind; '#' starts a comment.
+//   nncv_b200_plan 1
+//   params <elements> out <features>
+//   conv id=1 in=0 res=-1 cin=3 cout=64 k=7 stride=2 pad=3 relu=1 w=<off> gamma=<off> beta=<off> mean=<off> var=<off>
+//   maxpool id=2 in=1 k=3 stride=2 pad=1
+//   avgpool id=.. in=..
+//   fc id=.. in=.. cin=512 cout=1000 w=<off> b=<off>
+int parse_plan(const std::string& text, Plan* out) {
+  Plan p;
+  p.name = "plan";
+  size_t pos = 0;
+  bool header = false;
+  int line_no = 0;
+  while (pos < text.size()) {
+    size_t eol = text.find('\n', pos);
+    if (eol == std::string::npos) eol = text.size();
+    std::string line = text.substr(pos, eol - pos);
+    pos = eol + 1;
+    ++line_no;
+    const size_t hash = line.find('#');
+    if (hash != std::string::npos) line.resize(hash);
+    std::vector<std::string> tok;
+    {
+      size_t i = 0;
+      while (i < line.size()) {
+        while (i < line.size() && isspace((unsigned char)line[i])) ++i;
+        size_t j = i;
+        while (j < line.size() && !isspace((unsigned char)line[j])) ++j;
+        if (j > i) tok.push_back(line.substr(i, j - i));
+        i = j;
+      }
+    }
+    if (tok.empty()) continue;
+    if (tok[0] == "nncv_b200_plan") {
+      if (tok.size() < 2 || tok[1] != "1") return fail(NNCV_B200_EINVAL, "plan line %d: unknown plan version", line_no);
+      header = true;
+      continue;
+    }
+    if (!header) return fail(NNCV_B200_EINVAL, "plan line %d: the text does not start with \"nncv_b200_plan 1\"", line_no);
+    if (tok[0] == "params") {
+      if (tok.size() != 4 || tok[2] != "out") return fail(NNCV_B200_EINVAL, "plan line %d: expected \"params <n> out <features>\"", line_no);
+      p.total = strtoull(tok[1].c_str(), nullptr, 10);
+      p.out_features = atoi(tok[3].c_str());
+      continue;
+    }
+    PlanNode n;
+    if (tok[0] == "conv") n.kind = PlanNode::kConv;
+    else if (tok[0] == "maxpool") n.kind = PlanNode::kMaxPool;
+    else if (tok[0] == "avgpool") n.kind = PlanNode::kAvgPool;
+    else if (tok[0] == "fc") n.kind = PlanNode::kFc;
+    else return fail(NNCV_B200_EINVAL, "plan line %d: unknown node kind \"%s\"", line_no, tok[0].c_str());
+    for (size_t i = 1; i < tok.size(); ++i) {
+      const size_t eq = tok[i].find('=');
+      if (eq == std::string::npos) return fail(NNCV_B200_EINVAL, "plan line %d: field \"%s\" is not key=value", line_no, tok[i].c_str());
+      const std::string k = tok[i].substr(0, eq);
+      const long long v = strtoll(tok[i].c_str() + eq + 1, nullptr, 10);
+      if (k == "id") n.id = (int)v;
+      else if (k == "in") n.in = (int)v;
+      else if (k == "res") n.res = (int)v;
+      else if (k == "cin") n.cin = (int)v;
+      else if (k == "cout") n.cout = (int)v;
+      else if (k == "k") n.k = (int)v;
+      else if (k == "stride") n.stride = (int)v;
+      else if (k == "pad") n.pad = (int)v;
+      else if (k == "relu") n.relu = (int)v;
+      else if (k == "w") n.off_w = (size_t)v;
+      else if (k == "b") n.off_b = (size_t)v;
+      else if (k == "gamma") { n.off_gamma = (size_t)v; n.has_bn = 1; }
+      else if (k == "beta") n.off_beta = (size_t)v;
+      else if (k == "mean") n.off_mean = (size_t)v;
+      else if (k == "var") n.off_var = (size_t)v;
+      else return fail(NNCV_B200_EINVAL, "plan line %d: unknown field \"%s\"", line_no, k.c_str());
+    }
+    p.nodes.push_back(n);
+  }
+  if (!header || p.nodes.empty() || p.total == 0 || p.out_features <= 0)
+    return fail(NNCV_B200_EINVAL, "plan: header, params line or nodes missing");
+  *out = std::move(p);
+  return NNCV_B200_OK;
+}
+
+// Checks ids, shapes and parameter ranges of a plan and derives the fusion links.  `act16`: the
+// 16-bit tensor-core path (the fused stem and the fused downsample launch exist only there).
+int finalize_plan(Plan& p, bool act16) {
+  std::map<int, int> producer;   // tensor id -> node index
+  std::map<int, int> channels;   // tensor id -> channels
+  std::map<int, int> readers;    // tensor id -> number of reading nodes
+  channels[0] = 3;
+  for (size_t i = 0; i < p.nodes.size(); ++i) {
+    PlanNode& n = p.nodes[i];
+    if (n.id <= 0 || producer.count(n.id)) return fail(NNCV_B200_EINVAL, "plan: node %zu has a bad or repeated id %d", i, n.id);
+    if (!channels.count(n.in)) return fail(NNCV_B200_EINVAL, "plan: node %zu reads tensor %d before it exists", i, n.in);
+    ++readers[n.in];
+    const int cin = channels[n.in];
+    auto in_range = [&](size_t off, size_t cnt) { return off <= p.total && cnt <= p.total - off; };
+    if (n.kind == PlanNode::kConv) {
+      if (n.cin != cin || n.cout <= 0 || n.k <= 0 || n.stride <= 0 || n.pad < 0)
+        return fail(NNCV_B200_EINVAL, "plan: conv node %zu has %d input channels, its input tensor has %d", i, n.cin, cin);
+      if (!in_range(n.off_w, (size_t)n.cout * n.cin * n.k * n.k) ||
+          (n.has_bn && (!in_range(n.off_gamma, n.cout) || !in_range(n.off_beta, n.cout) || !in_range(n.off_mean, n.cout) ||
+                        !in_range(n.off_var, n.cout))))
+        return fail(NNCV_B200_EINVAL, "plan: conv node %zu names parameters outside the blob", i);
+      if (n.res >= 0) {
+        if (!channels.count(n.res) || channels[n.res] != n.cout)
+          return fail(NNCV_B200_EINVAL, "plan: conv node %zu adds tensor %d, which is missing or has other channels", i, n.res);
+        ++readers[n.res];
+      }
+      channels[n.id] = n.cout;
+    } else if (n.kind == PlanNode::kMaxPool) {
+      if (n.k <= 0 || n.stride <= 0 || n.pad < 0 || n.in == 0) return fail(NNCV_B200_EINVAL, "plan: bad max-pool node %zu", i);
+      n.cin = n.cout = cin;
+      channels[n.id] = cin;
+    } else if (n.kind == PlanNode::kAvgPool) {
+      if (n.in == 0) return fail(NNCV_B200_EINVAL, "plan: bad average-pool node %zu", i);
+      n.cin = n.cout = cin;
+      channels[n.id] = cin;
+    } else {
+      if (n.cin != cin || n.cout != p.out_features || i + 1 != p.nodes.size() || !in_range(n.off_w, (size_t)n.cout * n.cin) ||
+          !in_range(n.off_b, n.cout) || producer.count(n.in) == 0 || p.nodes[producer[n.in]].kind != PlanNode::kAvgPool)
+        return fail(NNCV_B200_EINVAL, "plan: the FC node must come last, read a global average pool and match the output size");
+      channels[n.id] = n.cout;
+    }
+    producer[n.id] = (int)i;
+  }
+  if (p.nodes.back().kind != PlanNode::kFc) return fail(NNCV_B200_EINVAL, "plan: the last node must be the FC layer");
+  if (!act16) return NNCV_B200_OK;
+  for (size_t i = 0; i < p.nodes.size(); ++i) {
+    PlanNode& a = p.nodes[i];
+    if (a.kind != PlanNode::kConv) continue;
+    // ResNet stem: 7x7 stride-2 pad-3 conv 3 -> 64 + BN + ReLU on the network input, read only by a 3x3 stride-2 pad-1 max-pool
+    if (a.in == 0 && a.cin == 3 && a.cout == 64 && a.k == 7 && a.stride == 2 && a.pad == 3 && a.relu && a.res < 0 && a.has_bn &&
+        readers[a.id] == 1 && i + 1 < p.nodes.size()) {
+      PlanNode& m = p.nodes[i + 1];
+      if (m.kind == PlanNode::kMaxPool && m.in == a.id && m.k == 3 && m.stride == 2 && m.pad == 1) {
+        a.stem_pool = (int)i + 1;
+        m.absorbed = 1;
+      }
+    }
+    // a 1x1 conv of the same stride on the same input may ride along as an extra tap (ResNet's downsample branch)
+    if (a.in != 0 && a.res < 0 && a.relu && (a.k & 1) && a.pad == a.k / 2 && a.k >= 3 && a.cout % 128 == 0 && a.cin % 64 == 0)
+      for (size_t j = i + 1; j < p.nodes.size() && j <= i + 3; ++j) {
+        PlanNode& b = p.nodes[j];
+        if (b.kind == PlanNode::kConv && b.in == a.in && b.k == 1 && b.pad == 0 && b.stride == a.stride && b.cout == a.cout &&
+            b.res < 0 && !b.relu && b.fused_into < 0) {
+          a.branch = (int)j;
+          b.fused_into = (int)i;
+          break;
+        }
+      }
+  }
+  return NNCV_B200_OK;
 }
 
 // =====================================================================================
 // model + executor
 // =====================================================================================
 struct Model {
-  NetSpec spec;
+  Plan plan;
   size_t ele_width = 4;      // params / io element width
   DType io_dt = kF32;        // element type of src / dst
   DType act_dt = kF16;       // activation / compute type
@@ -668,6 +877,7 @@ struct Model {
   std::vector<std::unique_ptr<nncv_b200_conv>> convs;
   std::vector<float*> scale, shift;
   std::unique_ptr<nncv_b200_conv> fc;
+  int stem_node = -1;        // conv node served by the fused stem + max-pool kernel, or -1
   const void* host_blob_id = nullptr;  // pointer identity of the blob the plan was built from
   // per-shape workspace
   int wsN = 0, wsH = 0, wsW = 0;
@@ -675,11 +885,31 @@ struct Model {
   DevBuf stem_rows, stem_w;  // fused stem (16-bit path): reformatted input rows, packed weights
   bool fused_stem = false;
   int stem_rows_paired = -1;  // layout the zeroed pad pixels of stem_rows belong to (-1: none yet)
-  // One buffer per activation tensor of the forward, handed out in call order.  Buffers are
-  // zeroed when created and never shared between tensors, so the pad slots of shared-pad
-  // tensors stay zero no matter which kernel writes the interior.
-  std::vector<std::unique_ptr<DevBuf>> acts;
+  // Activation tensors of one forward live in one arena.  The first forward of a shape walks the
+  // network once without launching anything (planning = true) to record every tensor's size, layout
+  // and usage interval in ops; offsets then come from arena_plan() (greedy by size, the scheme of
+  // nncv's MemSolver), applied per layout class: tensors share memory only with tensors of the same
+  // [rows, pitch, channels], so the zero pad slots of shared-pad tensors coincide and stay zero
+  // whichever kernel writes the interior (the arena is zeroed once when it is created).
+  struct ActRec {
+    size_t bytes;
+    std::array<int, 3> geom;   // rows per image, pitch, channels
+    int first, last;           // ops that write it first / read it last
+    size_t offset;
+  };
+  std::vector<ActRec> act_plan;
+  bool planning = false, planned = false;
+  int op_idx = 0;
+  DevBuf arena;
+  size_t act_bytes_unshared = 0;   // what one buffer per tensor would take
   size_t act_next = 0;
+  static constexpr uintptr_t kFakeBase = (uintptr_t)0x7A00000000000000ull;   // planning pass: stand-in pointers
+  void note_use(const void* p) {
+    const uintptr_t v = (uintptr_t)p;
+    if (!planning || v < kFakeBase) return;
+    const size_t i = (size_t)((v - kFakeBase) >> 8);
+    if (i < act_plan.size() && act_plan[i].last < op_idx) act_plan[i].last = op_idx;
+  }
 };
 void model_reset() {
   if (t_dev && t_dev->model) {
@@ -690,17 +920,14 @@ void model_reset() {
 
 DType dt_from_width(size_t w) { return w == 4 ? kF32 : kF16; }
 
-int model_build(int depth, const void* host_blob, size_t n_elements, size_t ele_width,
+int model_build(Plan plan, const void* host_blob, size_t n_elements, size_t ele_width,
                 const nncv_b200_opts* opts) {
   int rc = device_init();
   if (rc) return rc;
-  if (depth != 18 && depth != 50) return fail(NNCV_B200_EINVAL, "unknown network depth %d", depth);
   if (ele_width != 4 && ele_width != 2) return fail(NNCV_B200_EINVAL, "eleWidth must be 2 or 4");
   auto m = std::make_unique<Model>();
-  m->spec = build_spec(depth);
-  if (n_elements != m->spec.total)
-    return fail(NNCV_B200_EINVAL, "params hold %zu elements, resnet%d needs %zu", n_elements, depth,
-                m->spec.total);
+  if (n_elements != plan.total)
+    return fail(NNCV_B200_EINVAL, "params hold %zu elements, %s needs %zu", n_elements, plan.name.c_str(), plan.total);
   m->ele_width = ele_width;
   m->io_dt = dt_from_width(ele_width);
   int cd = opts ? opts->compute_dtype : -1;
@@ -708,6 +935,8 @@ int model_build(int depth, const void* host_blob, size_t n_elements, size_t ele_
   if (cd != NNCV_B200_F32 && cd != NNCV_B200_F16 && cd != NNCV_B200_BF16)
     return fail(NNCV_B200_EINVAL, "bad compute_dtype %d", cd);
   m->act_dt = (DType)cd;
+  if ((rc = finalize_plan(plan, m->act_dt != kF32))) return rc;
+  m->plan = std::move(plan);
   cudaStream_t st = g_dev.stream;
   rc = m->blob.reserve(n_elements * ele_width);
   if (rc) return rc;
@@ -717,42 +946,56 @@ int model_build(int depth, const void* host_blob, size_t n_elements, size_t ele_
   auto at = [&](size_t off) { return (const void*)(base + off * ele_width); };
 
   size_t nfold = 0;
-  for (auto& g : m->spec.groups) nfold += 2 * (size_t)g.cout;
-  rc = m->folded.reserve(nfold * sizeof(float));
+  for (auto& n : m->plan.nodes)
+    if (n.kind == PlanNode::kConv) nfold += 2 * (size_t)n.cout;
+  rc = m->folded.reserve(nfold * sizeof(float) + 16);
   if (rc) return rc;
   float* fp = (float*)m->folded.p;
-  for (auto& g : m->spec.groups) {
+  for (size_t i = 0; i < m->plan.nodes.size(); ++i) {
+    PlanNode& g = m->plan.nodes[i];
+    if (g.kind == PlanNode::kFc) {
+      // FC: weight [out, in] is already "[Kout][C]" (the forward's transpose generic,
+      // Res18.mlir:617-620, is absorbed by reading it K-major); bias in fp32.
+      if (g.cin % 8 != 0) return fail(NNCV_B200_EINVAL, "plan: FC input width %d must be a multiple of 8", g.cin);
+      m->fc = std::make_unique<nncv_b200_conv>();
+      m->fc->device = g_dev.id;
+      m->fc->Kout = g.cout; m->fc->C = g.cin; m->fc->Cpad = g.cin; m->fc->dtype = m->act_dt;
+      m->fc->raw = at(g.off_w); m->fc->raw_dt = pdt;
+      m->fc->sn = g.cin; m->fc->sc = 1; m->fc->stap = 1;
+      rc = m->fc_bias.reserve((size_t)g.cout * sizeof(float));
+      if (rc) return rc;
+      LAUNCH(launch_convert(at(g.off_b), pdt, m->fc_bias.p, kF32, (size_t)g.cout, st));
+      continue;
+    }
+    if (g.kind != PlanNode::kConv) continue;
     auto c = std::make_unique<nncv_b200_conv>();
     c->Kout = g.cout; c->C = g.cin; c->R = g.k; c->S = g.k; c->stride = g.stride; c->pad = g.pad;
     c->device = g_dev.id;
     c->dtype = m->act_dt;
     c->Cpad = m->act_dt == kF32 ? (g.cin + 3) / 4 * 4 : (g.cin + 7) / 8 * 8;
-    if (m->act_dt != kF32 && conv3x3_supported(g.cin, g.cout, g.k, g.k, g.stride, g.pad)) c->algo = 2;
+    if (m->act_dt != kF32 && g.in != 0 && conv3x3_supported(g.cin, g.cout, g.k, g.k, g.stride, g.pad)) c->algo = 2;
     c->raw = at(g.off_w); c->raw_dt = pdt;
     c->sn = (long long)g.cin * g.k * g.k; c->sc = (long long)g.k * g.k; c->stap = 1;
+    g.conv_idx = (int)m->convs.size();
     m->convs.push_back(std::move(c));
-    m->scale.push_back(fp);
-    m->shift.push_back(fp + g.cout);
-    LAUNCH(launch_bn_fold(at(g.off_gamma), at(g.off_beta), at(g.off_mean), at(g.off_var), pdt,
-                          g.cout, fp, fp + g.cout, st));
-    fp += 2 * g.cout;
+    if (g.has_bn) {
+      m->scale.push_back(fp);
+      m->shift.push_back(fp + g.cout);
+      LAUNCH(launch_bn_fold(at(g.off_gamma), at(g.off_beta), at(g.off_mean), at(g.off_var), pdt,
+                            g.cout, fp, fp + g.cout, st));
+      fp += 2 * g.cout;
+    } else {
+      m->scale.push_back(nullptr);
+      m->shift.push_back(nullptr);
+    }
+    if (g.stem_pool >= 0 && m->stem_node < 0) {
+      rc = m->stem_w.reserve(stem_wpack_bytes());
+      if (rc) return rc;
+      LAUNCH(launch_pack_stem_weights(at(g.off_w), pdt, m->stem_w.p, m->act_dt, st));
+      m->fused_stem = true;
+      m->stem_node = (int)i;
+    }
   }
-  if (m->act_dt != kF32) {
-    rc = m->stem_w.reserve(stem_wpack_bytes());
-    if (rc) return rc;
-    LAUNCH(launch_pack_stem_weights(at(m->spec.groups[0].off_w), pdt, m->stem_w.p, m->act_dt, st));
-    m->fused_stem = true;
-  }
-  // FC: weight [1000, fc_in] is already "[Kout][C]" (the forward's transpose generic,
-  // Res18.mlir:617-620, is absorbed by reading it K-major); bias in fp32.
-  m->fc = std::make_unique<nncv_b200_conv>();
-  m->fc->device = g_dev.id;
-  m->fc->Kout = 1000; m->fc->C = m->spec.fc_in; m->fc->Cpad = m->spec.fc_in; m->fc->dtype = m->act_dt;
-  m->fc->raw = at(m->spec.off_fc_w); m->fc->raw_dt = pdt;
-  m->fc->sn = m->spec.fc_in; m->fc->sc = 1; m->fc->stap = 1;
-  rc = m->fc_bias.reserve(1000 * sizeof(float));
-  if (rc) return rc;
-  LAUNCH(launch_convert(at(m->spec.off_fc_b), pdt, m->fc_bias.p, kF32, 1000, st));
   CU(cudaStreamSynchronize(st));
   m->host_blob_id = host_blob;
   model_reset();
@@ -760,50 +1003,71 @@ int model_build(int depth, const void* host_blob, size_t n_elements, size_t ele_
   return ok();
 }
 
-struct Shape { int h, w; };
-
 int ensure_workspace(Model& m, int N, int H, int W) {
   if (m.wsN == N && m.wsH == H && m.wsW == W) return NNCV_B200_OK;
   const size_t es = dtype_size(m.act_dt);
-  const int cpad0 = m.convs[0]->Cpad;
-  const int h1 = (H + 6 - 7) / 2 + 1, w1 = (W + 6 - 7) / 2 + 1;
-  const int h2 = (h1 + 2 - 3) / 2 + 1, w2 = (w1 + 2 - 3) / 2 + 1;
-  if (h1 <= 0 || w1 <= 0 || h2 <= 0 || w2 <= 0) return fail(NNCV_B200_EINVAL, "input %dx%d too small", H, W);
+  if (H < 1 || W < 1) return fail(NNCV_B200_EINVAL, "input %dx%d too small", H, W);
   cudaDeviceSynchronize();
-  m.acts.clear();
+  m.act_plan.clear();
+  m.planned = false;
   m.act_next = 0;
   int rc = 0;
+  const int of = m.plan.out_features;
   if ((rc = m.in_stage.reserve((size_t)N * 3 * H * W * m.ele_width))) return rc;
-  if (m.fused_stem && W <= 512) {
+  if (m.fused_stem && W <= 512 && H >= 7 && W >= 7) {
     if ((rc = m.stem_rows.reserve(stem_rows_bytes(N, H, W)))) return rc;
     CU(cudaMemset(m.stem_rows.p, 0, stem_rows_bytes(N, H, W)));   // the pad pixels of every row stay zero
     m.stem_rows_paired = (int)stem_paired_ok(H, W);
   } else {
+    const int cpad0 = m.act_dt == kF32 ? 4 : 8;
     if ((rc = m.in_nhwc.reserve((size_t)N * H * W * cpad0 * es))) return rc;
-    if ((rc = m.stem.reserve((size_t)N * h1 * w1 * 64 * es))) return rc;
   }
-  if ((rc = m.pooled.reserve((size_t)N * m.spec.fc_in * es))) return rc;
-  if ((rc = m.logits32.reserve((size_t)N * 1000 * sizeof(float)))) return rc;
-  if ((rc = m.logits_io.reserve((size_t)N * 1000 * m.ele_width))) return rc;
+  if ((rc = m.logits32.reserve((size_t)N * of * sizeof(float)))) return rc;
+  if ((rc = m.logits_io.reserve((size_t)N * of * m.ele_width))) return rc;
   m.wsN = N; m.wsH = H; m.wsW = W;
   return NNCV_B200_OK;
 }
 
-// Next activation buffer of the current forward ([N,h,w,c] in layout l); created and zeroed on
-// the first forward of a shape, reused afterwards.
+// Next activation tensor of the current forward ([N,h,w,c] in layout l).  Planning pass: records it
+// and hands out a stand-in pointer; afterwards: its place in the arena.
 int next_act(Model& m, int N, int h, int w, int c, Layout l, cudaStream_t st, void** out) {
   const size_t bytes = (size_t)layout_slots(l, N) * c * dtype_size(m.act_dt);
-  (void)h; (void)w;
-  if (m.act_next == m.acts.size()) {
-    auto b = std::make_unique<DevBuf>();
-    int rc = b->reserve(bytes);
-    if (rc) return rc;
-    CU(cudaMemsetAsync(b->p, 0, bytes, st));
-    m.acts.push_back(std::move(b));
+  (void)h; (void)w; (void)st;
+  if (m.planning) {
+    m.act_plan.push_back(Model::ActRec{bytes, {l.img_rows, l.pitch, c}, m.op_idx + 1, m.op_idx + 1, 0});
+    *out = (void*)(Model::kFakeBase + ((uintptr_t)(m.act_plan.size() - 1) << 8));
+    return NNCV_B200_OK;
   }
-  DevBuf& b = *m.acts[m.act_next++];
-  if (b.bytes < bytes) return fail(NNCV_B200_ECUDA, "activation plan changed under a fixed shape");
-  *out = b.p;
+  if (m.act_next >= m.act_plan.size() || m.act_plan[m.act_next].bytes != bytes)
+    return fail(NNCV_B200_ECUDA, "activation plan changed under a fixed shape");
+  *out = (char*)m.arena.p + m.act_plan[m.act_next++].offset;
+  return NNCV_B200_OK;
+}
+
+// Turns the tensors recorded by the planning pass into arena offsets and creates the arena.
+int finish_act_plan(Model& m) {
+  std::map<std::array<int, 3>, std::vector<size_t>> classes;
+  for (size_t i = 0; i < m.act_plan.size(); ++i) classes[m.act_plan[i].geom].push_back(i);
+  size_t base = 0, unshared = 0;
+  for (auto& kv : classes) {
+    std::vector<ArenaTensor> ts;
+    for (size_t i : kv.second) {
+      ArenaTensor t;
+      t.first = m.act_plan[i].first; t.last = m.act_plan[i].last; t.size = m.act_plan[i].bytes;
+      ts.push_back(t);
+      unshared += m.act_plan[i].bytes;
+    }
+    const size_t total = arena_plan(ts, 1024);
+    for (size_t k = 0; k < kv.second.size(); ++k) m.act_plan[kv.second[k]].offset = base + ts[k].offset;
+    base += total;
+  }
+  m.act_bytes_unshared = unshared;
+  if (base == 0) base = 1024;
+  cudaDeviceSynchronize();   // nothing may still be reading an older arena
+  int rc = m.arena.reserve(base);
+  if (rc) return rc;
+  CU(cudaMemset(m.arena.p, 0, m.arena.bytes));
+  m.planned = true;
   return NNCV_B200_OK;
 }
 
@@ -812,181 +1076,226 @@ int next_act(Model& m, int N, int h, int w, int c, Layout l, cudaStream_t st, vo
 int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cudaStream_t st) {
   int rc = ensure_workspace(m, N, H, W);
   if (rc) return rc;
+  if (!m.planned && !m.planning) {
+    // first forward of this shape: one walk that launches nothing records the activation tensors
+    m.planning = true;
+    m.act_plan.clear();
+    m.op_idx = 0;
+    rc = model_forward_device(m, src_dev, N, H, W, st);
+    m.planning = false;
+    if (rc) return rc;
+    if ((rc = finish_act_plan(m))) return rc;
+  }
   m.act_next = 0;
+  m.op_idx = 0;
+  // every launch site is one op; in the planning pass it only notes which tensors the op reads
+  auto begin_op = [&](std::initializer_list<const void*> reads) {
+    ++m.op_idx;
+    for (const void* q : reads) m.note_use(q);
+    return !m.planning;
+  };
   const DType adt = m.act_dt;
   const bool sp = adt != kF32;  // tensor-core path keeps block activations in shared-pad NHWC
   auto lay = [&](int h, int w) { return sp ? sp_layout(h, w) : dense_layout(h, w); };
-  size_t gi = 0;
   const double aes = (double)dtype_size(adt);
-  int h = H, w = W;
-  auto out_hw = [](int x, const nncv_b200_conv& c) { return (x + 2 * c.pad - c.R) / c.stride + 1; };
-  auto run = [&](size_t idx, const void* in, Layout il, void* out, Layout ol, int ih, int iw,
-                 const void* res, int relu) {
-    nncv_b200_conv& c = *m.convs[idx];
-    return conv_run(&c, in, il, out, ol, N, ih, iw, m.scale[idx], m.shift[idx], res, relu, adt, c.Kout, st);
+  struct Ten { void* p = nullptr; Layout l{0, 0, 0}; int h = 0, w = 0, c = 0; };
+  std::map<int, Ten> tens;   // tensor id -> where it lives in this forward
+  auto conv_of = [&](const PlanNode& n) -> nncv_b200_conv& { return *m.convs[n.conv_idx]; };
+  auto run = [&](const PlanNode& n, const Ten& in, const Ten& out, const void* res) {
+    nncv_b200_conv& c = conv_of(n);
+    if (!begin_op({in.p, res})) return (int)NNCV_B200_OK;
+    return conv_run(&c, in.p, in.l, out.p, out.l, N, in.h, in.w, m.scale[n.conv_idx], m.shift[n.conv_idx], res, n.relu, adt,
+                    c.Kout, st);
   };
-  void* x = nullptr;
-  if (m.fused_stem && W <= 512) {
-    // stem conv + BN + ReLU + max-pool in one kernel (Res18.mlir:118-151)
-    const int oh = out_hw(h, *m.convs[0]), ow = out_hw(w, *m.convs[0]);
-    const int ph = (oh + 2 - 3) / 2 + 1, pw = (ow + 2 - 3) / 2 + 1;
-    prof_begin(3, 0, (double)N * H * (3.0 * W * m.ele_width + stem_row_pixels(W) * 8.0), N * H * W, 3, 0, 3, st);
-    const bool paired = stem_paired_ok(H, W);
-    if (m.stem_rows_paired != (int)paired) {   // pad pixels sit elsewhere in the other layout
-      CU(cudaMemsetAsync(m.stem_rows.p, 0, stem_rows_bytes(N, H, W), st));
-      m.stem_rows_paired = (int)paired;
+  const bool stem_fused_here = m.fused_stem && W <= 512 && H >= 7 && W >= 7;
+  bool input_converted = false;
+  const int cpad0 = adt == kF32 ? 4 : 8;
+  for (size_t ni = 0; ni < m.plan.nodes.size(); ++ni) {
+    const PlanNode& n = m.plan.nodes[ni];
+    if (n.kind == PlanNode::kConv && n.in == 0 && stem_fused_here && (int)ni == m.stem_node) {
+      // stem conv + BN + ReLU + max-pool in one kernel (Res18.mlir:118-151)
+      const int oh = (H + 6 - 7) / 2 + 1, ow = (W + 6 - 7) / 2 + 1;
+      const int ph = (oh + 2 - 3) / 2 + 1, pw = (ow + 2 - 3) / 2 + 1;
+      if (ph <= 0 || pw <= 0) return fail(NNCV_B200_EINVAL, "input %dx%d too small", H, W);
+      const bool paired = stem_paired_ok(H, W);
+      if (begin_op({})) {
+        prof_begin(3, 0, (double)N * H * (3.0 * W * m.ele_width + stem_row_pixels(W) * 8.0), N * H * W, 3, 0, 3, st);
+        if (m.stem_rows_paired != (int)paired) {   // pad pixels sit elsewhere in the other layout
+          CU(cudaMemsetAsync(m.stem_rows.p, 0, stem_rows_bytes(N, H, W), st));
+          m.stem_rows_paired = (int)paired;
+        }
+        LAUNCH(launch_nchw_to_stem_rows(src_dev, m.io_dt, m.stem_rows.p, adt, N, H, W, true, paired, st));
+        prof_end(st);
+      }
+      Ten o;
+      o.l = lay(ph, pw); o.h = ph; o.w = pw; o.c = 64;
+      if ((rc = next_act(m, N, ph, pw, 64, o.l, st, &o.p))) return rc;
+      if (begin_op({})) {
+        StemArgs a;
+        a.in_rows = m.stem_rows.p; a.paired = paired; a.wpack = m.stem_w.p; a.scale = m.scale[n.conv_idx]; a.shift = m.shift[n.conv_idx];
+        a.out = o.p; a.out_l = o.l; a.N = N; a.H = H; a.W = W; a.ab = adt;
+        a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
+        prof_begin(4, 2.0 * N * oh * ow * 64.0 * 147.0,
+                   (double)N * H * stem_row_pixels(W) * 8.0 + 2.0 * N * ph * pw * 64.0, N * oh * ow, 64, 147, 64, st);
+        LAUNCH(launch_stem_pool(a, st));
+        prof_end(st);
+      }
+      tens[m.plan.nodes[n.stem_pool].id] = o;   // the pooled map; the conv's own output never exists
+      continue;
     }
-    LAUNCH(launch_nchw_to_stem_rows(src_dev, m.io_dt, m.stem_rows.p, adt, N, H, W, true, paired, st));
-    prof_end(st);
-    if ((rc = next_act(m, N, ph, pw, 64, lay(ph, pw), st, &x))) return rc;
-    StemArgs a;
-    a.in_rows = m.stem_rows.p; a.paired = paired; a.wpack = m.stem_w.p; a.scale = m.scale[0]; a.shift = m.shift[0];
-    a.out = x; a.out_l = lay(ph, pw); a.N = N; a.H = H; a.W = W; a.ab = adt;
-    a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
-    prof_begin(4, 2.0 * N * oh * ow * 64.0 * 147.0,
-               (double)N * H * stem_row_pixels(W) * 8.0 + 2.0 * N * ph * pw * 64.0, N * oh * ow, 64, 147, 64, st);
-    LAUNCH(launch_stem_pool(a, st));
-    prof_end(st);
-    h = ph; w = pw;
-    gi = 1;
-  } else {
-    // NCHW -> NHWC (channels padded), io type -> activation type
-    prof_begin(3, 0, (double)N * H * W * (3.0 * m.ele_width + m.convs[0]->Cpad * aes), N * H * W, 3, 0, 0, st);
-    LAUNCH(launch_nchw_to_nhwc(src_dev, m.io_dt, m.in_nhwc.p, adt, N, 3, H, W, m.convs[0]->Cpad, st));
-    prof_end(st);
-    // stem (Res18.mlir:118-143) and max-pool (:144-151)
-    {
-      const int oh = out_hw(h, *m.convs[gi]), ow = out_hw(w, *m.convs[gi]);
-      rc = run(gi, m.in_nhwc.p, dense_layout(h, w), m.stem.p, dense_layout(oh, ow), h, w, nullptr, 1);
-      if (rc) return rc;
-      h = oh; w = ow;
-      ++gi;
+    if (n.kind == PlanNode::kMaxPool && n.absorbed && stem_fused_here) continue;
+    Ten in;
+    if (n.in == 0) {
+      // NCHW -> NHWC (channels padded), io type -> activation type; once per forward
+      if (!input_converted) {
+        if (!m.in_nhwc.p || m.in_nhwc.bytes < (size_t)N * H * W * cpad0 * dtype_size(adt)) {
+          cudaDeviceSynchronize();
+          if ((rc = m.in_nhwc.reserve((size_t)N * H * W * cpad0 * dtype_size(adt)))) return rc;
+        }
+        if (begin_op({})) {
+          prof_begin(3, 0, (double)N * H * W * (3.0 * m.ele_width + cpad0 * aes), N * H * W, 3, 0, 0, st);
+          LAUNCH(launch_nchw_to_nhwc(src_dev, m.io_dt, m.in_nhwc.p, adt, N, 3, H, W, cpad0, st));
+          prof_end(st);
+        }
+        input_converted = true;
+      }
+      in.p = m.in_nhwc.p; in.l = dense_layout(H, W); in.h = H; in.w = W; in.c = 3;
+    } else {
+      auto it = tens.find(n.in);
+      if (it == tens.end()) return fail(NNCV_B200_EINVAL, "plan: tensor %d is read before it is written", n.in);
+      in = it->second;
     }
-    {
-      const int oh = (h + 2 - 3) / 2 + 1, ow = (w + 2 - 3) / 2 + 1;
-      if ((rc = next_act(m, N, oh, ow, 64, lay(oh, ow), st, &x))) return rc;
-      prof_begin(3, 0, aes * 64.0 * N * ((double)h * w + (double)oh * ow), N * h * w, 64, 0, 1, st);
-      LAUNCH(launch_maxpool_nhwc(m.stem.p, x, adt, N, h, w, 64, 3, 2, 1, dense_layout(h, w), lay(oh, ow), st));
-      prof_end(st);
-      h = oh; w = ow;
-    }
-  }
-  const int nb18[4] = {2, 2, 2, 2}, nb50[4] = {3, 4, 6, 3};
-  const int* nb = m.spec.depth == 18 ? nb18 : nb50;
-  for (int l = 0; l < 4; ++l) {
-    for (int b = 0; b < nb[l]; ++b) {
-      const bool has_ds = m.spec.depth == 18 ? (b == 0 && l > 0) : (b == 0);
-      int ch = h, cw = w;       // spatial size of the tensor flowing through the block body
-      const void* cur = x;
-      const int body = m.spec.depth == 18 ? 1 : 2;  // convs before the last one
-      void* ds_done = nullptr;   // output of the downsample branch when it ran fused with the first conv
-      void* ds_buf = nullptr;
-      for (int k = 0; k < body; ++k) {
-        nncv_b200_conv& c = *m.convs[gi];
-        const int oh = out_hw(ch, c), ow = out_hw(cw, c);
-        void* t = nullptr;
-        if ((rc = next_act(m, N, oh, ow, c.Kout, lay(oh, ow), st, &t))) return rc;
+    if (n.kind == PlanNode::kConv) {
+      if (n.fused_into >= 0 && tens.count(n.id) && tens[n.id].h < 0) {   // already computed beside its partner
+        tens[n.id].h = -tens[n.id].h;
+        continue;
+      }
+      nncv_b200_conv& c = conv_of(n);
+      const int oh = (in.h + 2 * c.pad - c.R) / c.stride + 1, ow = (in.w + 2 * c.pad - c.S) / c.stride + 1;
+      if (oh <= 0 || ow <= 0) return fail(NNCV_B200_EINVAL, "input %dx%d too small for the network", H, W);
+      Ten o;
+      if (n.fused_into >= 0 && tens.count(n.id)) {
+        o = tens[n.id];   // allocated beside its partner, which ran alone
+      } else {
+        o.l = lay(oh, ow); o.h = oh; o.w = ow; o.c = c.Kout;
+        if ((rc = next_act(m, N, oh, ow, c.Kout, o.l, st, &o.p))) return rc;
+      }
+      const void* res = nullptr;
+      if (n.res >= 0) {
+        auto it = tens.find(n.res);
+        if (it == tens.end() || it->second.h != oh || it->second.w != ow)
+          return fail(NNCV_B200_EINVAL, "plan: the residual of tensor %d does not have its shape", n.id);
+        res = it->second.p;
+      }
+      bool done = false;
+      if (n.branch >= 0 && sp && fused_branch_ok(c, conv_of(m.plan.nodes[n.branch]))) {
         // BasicBlock: the 3x3 stride-2 conv and the 1x1 stride-2 downsample conv read the same tensor
-        const size_t ds_idx = gi + (size_t)body + 1;
-        bool fuse = false;
-        if (k == 0 && has_ds && body == 1 && sp && ds_idx < m.convs.size() && fused_branch_ok(c, *m.convs[ds_idx])) {
-          if ((rc = next_act(m, N, oh, ow, c.Kout, lay(oh, ow), st, &ds_buf))) return rc;
-          FusedBranch fb{m.convs[ds_idx].get(), m.scale[ds_idx], m.shift[ds_idx], ds_buf};
-          fuse = c.Kout <= 128;   // one Kout tile: the input is read once for both convolutions
-          if (g_autotune) {
-            // time both ways once per shape: one fused launch against the two tuned separate ones
-            const std::array<int, 3> key{N, ch, cw};
-            auto it = c.fuse_tuned.find(key);
-            char fkey[128];
-            snprintf(fkey, sizeof(fkey), "fuse c%d k%d r%d st%d dt%d n%d h%d w%d", c.Cpad, c.Kout, c.R, c.stride, (int)c.dtype, N, ch, cw);
-            if (it == c.fuse_tuned.end()) {
-              if (const std::string* v = g_tune_cache.find(fkey)) it = c.fuse_tuned.emplace(key, *v == "1").first;
-            }
-            if (it == c.fuse_tuned.end()) {
-              cudaEvent_t e[3];
-              for (auto& ev : e) CU(cudaEventCreate(&ev));
-              const bool was = g_prof_on;
-              g_prof_on = false;
-              auto both = [&](bool fused) -> int {
-                if (fused)
-                  return conv_run(&c, cur, lay(ch, cw), t, lay(oh, ow), N, ch, cw, m.scale[gi], m.shift[gi], nullptr, 1,
-                                  adt, c.Kout, st, &fb);
-                int r = run(gi, cur, lay(ch, cw), t, lay(oh, ow), ch, cw, nullptr, 1);
-                return r ? r : run(ds_idx, cur, lay(ch, cw), ds_buf, lay(oh, ow), ch, cw, nullptr, 0);
-              };
-              rc = both(false);            // also lets each separate conv pick its own kernel
-              if (!rc) rc = both(true);
-              float ms_sep = 0.f, ms_fused = 0.f;
-              if (!rc) {
-                cudaEventRecord(e[0], st);
-                for (int rep = 0; rep < 3 && !rc; ++rep) rc = both(false);
-                cudaEventRecord(e[1], st);
-                for (int rep = 0; rep < 3 && !rc; ++rep) rc = both(true);
-                cudaEventRecord(e[2], st);
-                if (!rc && cudaEventSynchronize(e[2]) == cudaSuccess) {
-                  cudaEventElapsedTime(&ms_sep, e[0], e[1]);
-                  cudaEventElapsedTime(&ms_fused, e[1], e[2]);
-                }
-                int flag = 0;
-                if (!rc) rc = read_kernel_status(&flag);
-                if (!rc && flag) rc = report_kernel_error(flag, "timing the fused downsample launch");
+        const PlanNode& bn = m.plan.nodes[n.branch];
+        Ten d;
+        d.l = lay(oh, ow); d.h = oh; d.w = ow; d.c = c.Kout;
+        if ((rc = next_act(m, N, oh, ow, c.Kout, d.l, st, &d.p))) return rc;
+        FusedBranch fb{&conv_of(bn), m.scale[bn.conv_idx], m.shift[bn.conv_idx], d.p};
+        bool fuse = c.Kout <= 128 && !m.planning;   // one Kout tile: the input is read once for both convolutions
+        if (g_autotune && !m.planning) {
+          // time both ways once per shape: one fused launch against the two tuned separate ones
+          const std::array<int, 3> key{N, in.h, in.w};
+          auto it = c.fuse_tuned.find(key);
+          char fkey[128];
+          snprintf(fkey, sizeof(fkey), "fuse c%d k%d r%d st%d dt%d n%d h%d w%d", c.Cpad, c.Kout, c.R, c.stride, (int)c.dtype, N, in.h, in.w);
+          if (it == c.fuse_tuned.end()) {
+            if (const std::string* v = g_tune_cache.find(fkey)) it = c.fuse_tuned.emplace(key, *v == "1").first;
+          }
+          if (it == c.fuse_tuned.end()) {
+            cudaEvent_t e[3];
+            for (auto& ev : e) CU(cudaEventCreate(&ev));
+            const bool was = g_prof_on;
+            g_prof_on = false;
+            auto both = [&](bool fused) -> int {
+              if (fused)
+                return conv_run(&c, in.p, in.l, o.p, o.l, N, in.h, in.w, m.scale[n.conv_idx], m.shift[n.conv_idx], nullptr, 1,
+                                adt, c.Kout, st, &fb);
+              int r = run(n, in, o, nullptr);
+              return r ? r : run(bn, in, d, nullptr);
+            };
+            rc = both(false);            // also lets each separate conv pick its own kernel
+            if (!rc) rc = both(true);
+            float ms_sep = 0.f, ms_fused = 0.f;
+            if (!rc) {
+              cudaEventRecord(e[0], st);
+              for (int rep = 0; rep < 3 && !rc; ++rep) rc = both(false);
+              cudaEventRecord(e[1], st);
+              for (int rep = 0; rep < 3 && !rc; ++rep) rc = both(true);
+              cudaEventRecord(e[2], st);
+              if (!rc && cudaEventSynchronize(e[2]) == cudaSuccess) {
+                cudaEventElapsedTime(&ms_sep, e[0], e[1]);
+                cudaEventElapsedTime(&ms_fused, e[1], e[2]);
               }
-              g_prof_on = was;
-              for (auto& ev : e) cudaEventDestroy(ev);
-              if (rc) return rc;
-              it = c.fuse_tuned.emplace(key, ms_fused > 0.f && ms_fused < ms_sep).first;
-              g_tune_cache.put(fkey, it->second ? "1" : "0");
+              int flag = 0;
+              if (!rc) rc = read_kernel_status(&flag);
+              if (!rc && flag) rc = report_kernel_error(flag, "timing the fused downsample launch");
             }
-            fuse = it->second;
-          }
-          if (fuse) {
-            rc = conv_run(&c, cur, lay(ch, cw), t, lay(oh, ow), N, ch, cw, m.scale[gi], m.shift[gi], nullptr, 1, adt,
-                          c.Kout, st, &fb);
+            g_prof_on = was;
+            for (auto& ev : e) cudaEventDestroy(ev);
             if (rc) return rc;
-            ds_done = ds_buf;
+            it = c.fuse_tuned.emplace(key, ms_fused > 0.f && ms_fused < ms_sep).first;
+            g_tune_cache.put(fkey, it->second ? "1" : "0");
           }
+          fuse = it->second;
         }
-        if (!fuse && (rc = run(gi, cur, lay(ch, cw), t, lay(oh, ow), ch, cw, nullptr, 1))) return rc;
-        cur = t; ch = oh; cw = ow;
-        ++gi;
-      }
-      const size_t last_idx = gi++;
-      nncv_b200_conv& cl = *m.convs[last_idx];
-      const int oh = out_hw(ch, cl), ow = out_hw(cw, cl);
-      const void* identity = x;
-      if (has_ds) {  // BN(conv1x1(identity)) (Res18.mlir:297-311)
-        void* ds = ds_done;
-        if (!ds) {
-          ds = ds_buf;
-          if (!ds && (rc = next_act(m, N, oh, ow, cl.Kout, lay(oh, ow), st, &ds))) return rc;
-          if ((rc = run(gi, x, lay(h, w), ds, lay(oh, ow), h, w, nullptr, 0))) return rc;
+        if (fuse) {
+          begin_op({in.p});
+          rc = conv_run(&c, in.p, in.l, o.p, o.l, N, in.h, in.w, m.scale[n.conv_idx], m.shift[n.conv_idx], nullptr, 1, adt,
+                        c.Kout, st, &fb);
+          if (rc) return rc;
+          d.h = -d.h;   // marks the branch's tensor as already computed
+          done = true;
         }
-        ++gi;
-        identity = ds;
+        tens[bn.id] = d;
       }
-      // last conv of the block: BN, + identity, ReLU (Res18.mlir:180-203)
-      void* y = nullptr;
-      if ((rc = next_act(m, N, oh, ow, cl.Kout, lay(oh, ow), st, &y))) return rc;
-      if ((rc = run(last_idx, cur, lay(ch, cw), y, lay(oh, ow), ch, cw, identity, 1))) return rc;
-      x = y; h = oh; w = ow;
+      if (!done && (rc = run(n, in, o, res))) return rc;
+      tens[n.id] = o;
+    } else if (n.kind == PlanNode::kMaxPool) {
+      const int oh = (in.h + 2 * n.pad - n.k) / n.stride + 1, ow = (in.w + 2 * n.pad - n.k) / n.stride + 1;
+      if (oh <= 0 || ow <= 0) return fail(NNCV_B200_EINVAL, "input %dx%d too small for the network", H, W);
+      Ten o;
+      o.l = lay(oh, ow); o.h = oh; o.w = ow; o.c = in.c;
+      if ((rc = next_act(m, N, oh, ow, in.c, o.l, st, &o.p))) return rc;
+      if (begin_op({in.p})) {
+        prof_begin(3, 0, aes * in.c * N * ((double)in.h * in.w + (double)oh * ow), N * in.h * in.w, in.c, 0, 1, st);
+        LAUNCH(launch_maxpool_nhwc(in.p, o.p, adt, N, in.h, in.w, in.c, n.k, n.stride, n.pad, in.l, o.l, st));
+        prof_end(st);
+      }
+      tens[n.id] = o;
+    } else if (n.kind == PlanNode::kAvgPool) {
+      // global average pool (Res18.mlir:606-614) -> dense [N, C]
+      Ten o;
+      o.l = dense_layout(1, 1); o.h = 1; o.w = 1; o.c = in.c;
+      if ((rc = next_act(m, N, 1, 1, in.c, o.l, st, &o.p))) return rc;
+      if (begin_op({in.p})) {
+        prof_begin(3, 0, aes * in.c * N * (in.h * in.w + 1.0), N * in.h * in.w, in.c, 0, 2, st);
+        LAUNCH(launch_avgpool_nhwc(in.p, o.p, adt, N, in.h, in.w, in.c, in.l, st));
+        prof_end(st);
+      }
+      tens[n.id] = o;
+    } else {
+      // FC (Res18.mlir:617-628)
+      const int of = m.plan.out_features;
+      if (!begin_op({in.p})) return NNCV_B200_OK;   // the planning pass ends with the last reader of an activation tensor
+      if (m.io_dt == adt && adt != kF32) {
+        // 16-bit logits wanted and computed in the same type: the FC epilogue rounds once, exactly as
+        // the fp32 -> io conversion kernel would, and that kernel is not launched
+        return conv_run(m.fc.get(), in.p, dense_layout(1, 1), m.logits_io.p, dense_layout(1, 1), N, 1, 1, nullptr,
+                        (const float*)m.fc_bias.p, nullptr, 0, adt, of, st);
+      }
+      rc = conv_run(m.fc.get(), in.p, dense_layout(1, 1), m.logits32.p, dense_layout(1, 1), N, 1, 1, nullptr,
+                    (const float*)m.fc_bias.p, nullptr, 0, kF32, of, st);
+      if (rc) return rc;
+      if (m.io_dt != kF32)
+        LAUNCH(launch_convert(m.logits32.p, kF32, m.logits_io.p, m.io_dt, (size_t)N * of, st));
+      return NNCV_B200_OK;
     }
   }
-  // global average pool (Res18.mlir:606-614) and FC (:617-628)
-  prof_begin(3, 0, aes * m.spec.fc_in * N * (h * w + 1.0), N * h * w, m.spec.fc_in, 0, 2, st);
-  LAUNCH(launch_avgpool_nhwc(x, m.pooled.p, adt, N, h, w, m.spec.fc_in, lay(h, w), st));
-  prof_end(st);
-  if (m.io_dt == adt && adt != kF32) {
-    // 16-bit logits wanted and computed in the same type: the FC epilogue rounds once, exactly as
-    // the fp32 -> io conversion kernel would, and that kernel is not launched
-    return conv_run(m.fc.get(), m.pooled.p, dense_layout(1, 1), m.logits_io.p, dense_layout(1, 1), N, 1, 1, nullptr,
-                    (const float*)m.fc_bias.p, nullptr, 0, adt, 1000, st);
-  }
-  rc = conv_run(m.fc.get(), m.pooled.p, dense_layout(1, 1), m.logits32.p, dense_layout(1, 1), N, 1, 1, nullptr,
-                (const float*)m.fc_bias.p, nullptr, 0, kF32, 1000, st);
-  if (rc) return rc;
-  if (m.io_dt != kF32)
-    LAUNCH(launch_convert(m.logits32.p, kF32, m.logits_io.p, m.io_dt, (size_t)N * 1000, st));
-  return NNCV_B200_OK;
+  return fail(NNCV_B200_EINVAL, "plan: no FC node produced the output");
 }
 
 int check_src(const nncv_memref4* src, int* N, int* H, int* W) {
@@ -1004,23 +1313,23 @@ int check_src(const nncv_memref4* src, int* N, int* H, int* W) {
   return NNCV_B200_OK;
 }
 
-int check_dst(nncv_memref2* dst, int N, size_t ele_width, bool* allocated_here) {
+int check_dst(nncv_memref2* dst, int N, int of, size_t ele_width, bool* allocated_here) {
   *allocated_here = false;
   if (!dst) return fail(NNCV_B200_EINVAL, "dst descriptor is null");
   if (!dst->aligned) {
     // MLIR convention: the callee allocates the result memref.
-    void* p = malloc((size_t)N * 1000 * ele_width);
+    void* p = malloc((size_t)N * of * ele_width);
     if (!p) return fail(NNCV_B200_ENOMEM, "malloc of the result buffer failed");
     dst->allocated = dst->aligned = p;
     dst->offset = 0;
-    dst->sizes[0] = N; dst->sizes[1] = 1000;
-    dst->strides[0] = 1000; dst->strides[1] = 1;
+    dst->sizes[0] = N; dst->sizes[1] = of;
+    dst->strides[0] = of; dst->strides[1] = 1;
     *allocated_here = true;
     return NNCV_B200_OK;
   }
-  if (dst->sizes[0] != N || dst->sizes[1] != 1000)
-    return fail(NNCV_B200_EINVAL, "dst must be [%d,1000], got [%ld,%ld]", N, (long)dst->sizes[0], (long)dst->sizes[1]);
-  if (dst->strides[1] != 1 || dst->strides[0] < 1000)
+  if (dst->sizes[0] != N || dst->sizes[1] != of)
+    return fail(NNCV_B200_EINVAL, "dst must be [%d,%d], got [%ld,%ld]", N, of, (long)dst->sizes[0], (long)dst->sizes[1]);
+  if (dst->strides[1] != 1 || dst->strides[0] < of)
     return fail(NNCV_B200_EINVAL, "dst rows must be contiguous (strides %ld,%ld)", (long)dst->strides[0], (long)dst->strides[1]);
   return NNCV_B200_OK;
 }
@@ -1037,22 +1346,23 @@ int forward_impl(nncv_memref2* dst, nncv_memref4* src, void* params, cudaStream_
     if (!pd || !pd->aligned) return fail(NNCV_B200_ENOMODEL, "no model loaded and params is null");
     const size_t n = (size_t)pd->sizes[0];
     int depth = 0;
-    if (n == build_spec(18).total) depth = 18;
-    else if (n == build_spec(50).total) depth = 50;
+    if (n == builtin_plan(18).total) depth = 18;
+    else if (n == builtin_plan(50).total) depth = 50;
     else return fail(NNCV_B200_ENOMODEL, "params hold %zu elements: neither resnet18 nor resnet50", n);
-    rc = model_build(depth, (const char*)pd->aligned + pd->offset * 4, n, 4, nullptr);
+    rc = model_build(builtin_plan(depth), (const char*)pd->aligned + pd->offset * 4, n, 4, nullptr);
     if (rc) return rc;
   } else if (params) {
     auto* pd = static_cast<nncv_memref1*>(params);
-    if ((size_t)pd->sizes[0] != g_dev.model->spec.total)
+    if ((size_t)pd->sizes[0] != g_dev.model->plan.total)
       return fail(NNCV_B200_EINVAL, "params hold %ld elements, the loaded model has %zu", (long)pd->sizes[0],
-                  g_dev.model->spec.total);
+                  g_dev.model->plan.total);
   }
   Model& m = *g_dev.model;
   int N, H, W;
   if ((rc = check_src(src, &N, &H, &W))) return rc;
   bool allocated_here = false;
-  if ((rc = check_dst(dst, N, m.ele_width, &allocated_here))) return rc;
+  const int of = m.plan.out_features;
+  if ((rc = check_dst(dst, N, of, m.ele_width, &allocated_here))) return rc;
   const size_t ew = m.ele_width;
   const char* sp = (const char*)src->aligned + src->offset * (intptr_t)ew;
   char* dp = (char*)dst->aligned + dst->offset * (intptr_t)ew;
@@ -1090,8 +1400,8 @@ int forward_impl(nncv_memref2* dst, nncv_memref4* src, void* params, cudaStream_
     if (chunks > 1) CU(cudaStreamWaitEvent(st, g_dev.copy_done[c], 0));
     if ((rc = model_forward_device(m, src_d, Nc, H, W, st))) return rc;
     const void* logits = m.io_dt == kF32 ? m.logits32.p : m.logits_io.p;
-    CU(cudaMemcpy2DAsync(dp + (size_t)c * Nc * dst->strides[0] * ew, (size_t)dst->strides[0] * ew, logits, 1000 * ew,
-                         1000 * ew, (size_t)Nc, dst_dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, st));
+    CU(cudaMemcpy2DAsync(dp + (size_t)c * Nc * dst->strides[0] * ew, (size_t)dst->strides[0] * ew, logits, (size_t)of * ew,
+                         (size_t)of * ew, (size_t)Nc, dst_dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, st));
   }
   if (device_only) return ok();
   CU(cudaStreamSynchronize(st));
@@ -1099,11 +1409,22 @@ int forward_impl(nncv_memref2* dst, nncv_memref4* src, void* params, cudaStream_
   return ok();
 }
 
-int depth_from_name(const char* net) {
-  if (!net) return 0;
-  if (!strcmp(net, "resnet18")) return 18;
-  if (!strcmp(net, "resnet50")) return 50;
-  return 0;
+// "resnet18" / "resnet50": the built-in plans; "plan:<text>": a plan given inline; anything else:
+// the path of a plan file (what nncv_b200.mlir_import writes from a torch-mlir linalg module).
+int plan_from_name(const char* net, Plan* out) {
+  if (!net || !*net) return fail(NNCV_B200_EINVAL, "net is null or empty");
+  if (!strcmp(net, "resnet18")) { *out = builtin_plan(18); return NNCV_B200_OK; }
+  if (!strcmp(net, "resnet50")) { *out = builtin_plan(50); return NNCV_B200_OK; }
+  std::string text;
+  if (!strncmp(net, "plan:", 5)) {
+    text = net + 5;
+  } else {
+    std::ifstream f(net, std::ifstream::binary);
+    if (!f.good())
+      return fail(NNCV_B200_EINVAL, "net must be \"resnet18\", \"resnet50\", \"plan:<text>\" or the path of a plan file (cannot open %s)", net);
+    text.assign(std::istreambuf_iterator<char>(f), std::istreambuf_iterator<char>());
+  }
+  return parse_plan(text, out);
 }
 
 }  // namespace
@@ -1223,46 +1544,116 @@ int nncv_flat_array_write(const char* path, size_t n, const nncv_memref_indexer*
 // model API
 // =====================================================================================
 int nncv_b200_load(const char* net, const char* model_bin_path, const nncv_b200_opts* opts) {
-  const int depth = depth_from_name(net);
-  if (!depth) { std::lock_guard<std::mutex> lk(g_mutex); return fail(NNCV_B200_EINVAL, "net must be \"resnet18\" or \"resnet50\""); }
+  Plan plan;
+  {
+    std::lock_guard<std::mutex> lk(g_mutex);
+    int rc = plan_from_name(net, &plan);
+    if (rc) return rc;
+  }
   nncv_flat_array* a = nncv_flat_array_read(model_bin_path);
   if (!a) return g_status;
   std::lock_guard<std::mutex> lk(g_mutex);
   std::unique_ptr<nncv_flat_array> hold(a);
-  const NetSpec spec = build_spec(depth);
-  // shape check against the documented tensor order
-  const size_t expect = 2 + 5 * spec.groups.size();
-  if (a->idx.size() != expect)
-    return fail(NNCV_B200_EINVAL, "%s holds %zu tensors, %s needs %zu", model_bin_path, a->idx.size(), net, expect);
-  size_t t = 2;
-  for (int i = (int)spec.groups.size() - 1; i >= 0; --i, t += 5) {
-    const Group& g = spec.groups[i];
-    const nncv_memref_indexer& w = a->idx[t + 4];
-    if (w.dims != 4 || (int)w.shape[0] != g.cout || (int)w.shape[1] != g.cin || (int)w.shape[2] != g.k ||
-        (int)w.shape[3] != g.k)
-      return fail(NNCV_B200_EINVAL, "tensor %zu (%s) is not the %dx%dx%dx%d conv weight the plan expects",
-                  t + 4, w.name, g.cout, g.cin, g.k, g.k);
-    for (int j = 0; j < 4; ++j)
-      if (indexer_elems(a->idx[t + j]) != (size_t)g.cout)
-        return fail(NNCV_B200_EINVAL, "tensor %zu (%s) should hold %d batch-norm values", t + j, a->idx[t + j].name, g.cout);
+  // every parameter the plan names must start at a tensor of the file and have that tensor's size
+  // (element offset of tensor i = sum of the element counts before it, SplitParamsFlatArray.cpp:48-56)
+  std::map<size_t, size_t> at_off;   // element offset -> tensor index
+  {
+    size_t off = 0;
+    for (size_t i = 0; i < a->idx.size(); ++i) {
+      at_off.emplace(off, i);
+      off += indexer_elems(a->idx[i]);
+    }
+    if (off != plan.total)
+      return fail(NNCV_B200_EINVAL, "%s holds %zu elements, %s needs %zu", model_bin_path, off, plan.name.c_str(), plan.total);
+  }
+  auto tensor_at = [&](size_t off, size_t elems, const char* what, const PlanNode& n) -> const nncv_memref_indexer* {
+    auto it = at_off.find(off);
+    if (it == at_off.end() || indexer_elems(a->idx[it->second]) != elems) {
+      fail(NNCV_B200_EINVAL, "the %s of node %d (offset %zu, %zu elements) is not a tensor of %s", what, n.id, off, elems,
+           model_bin_path);
+      return nullptr;
+    }
+    return &a->idx[it->second];
+  };
+  for (const PlanNode& n : plan.nodes) {
+    if (n.kind == PlanNode::kConv) {
+      const nncv_memref_indexer* w = tensor_at(n.off_w, (size_t)n.cout * n.cin * n.k * n.k, "conv weight", n);
+      if (!w) return g_status;
+      if (w->dims != 4 || (int)w->shape[0] != n.cout || (int)w->shape[1] != n.cin || (int)w->shape[2] != n.k || (int)w->shape[3] != n.k)
+        return fail(NNCV_B200_EINVAL, "tensor %s is not the %dx%dx%dx%d conv weight the plan expects", w->name, n.cout, n.cin, n.k, n.k);
+      if (n.has_bn)
+        for (size_t off : {n.off_gamma, n.off_beta, n.off_mean, n.off_var})
+          if (!tensor_at(off, (size_t)n.cout, "batch-norm vector", n)) return g_status;
+    } else if (n.kind == PlanNode::kFc) {
+      if (!tensor_at(n.off_w, (size_t)n.cout * n.cin, "FC weight", n) || !tensor_at(n.off_b, (size_t)n.cout, "FC bias", n))
+        return g_status;
+    }
   }
   const size_t ew = a->idx[0].eleWidth;
   int rc = device_init();
   if (rc) return rc;
   model_reset();
-  return model_build(depth, a->data.data(), (size_t)a->wrapped.sizes[0], ew, opts);
+  return model_build(std::move(plan), a->data.data(), (size_t)a->wrapped.sizes[0], ew, opts);
+}
+
+long long nncv_b200_plan_text(const char* net, char* buf, size_t cap) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  Plan plan;
+  if (plan_from_name(net, &plan)) return -1;
+  std::string t = "nncv_b200_plan 1\nparams " + std::to_string(plan.total) + " out " + std::to_string(plan.out_features) + "\n";
+  char line[512];
+  for (const PlanNode& n : plan.nodes) {
+    if (n.kind == PlanNode::kConv) {
+      snprintf(line, sizeof(line), "conv id=%d in=%d res=%d cin=%d cout=%d k=%d stride=%d pad=%d relu=%d w=%zu", n.id, n.in, n.res,
+               n.cin, n.cout, n.k, n.stride, n.pad, n.relu, n.off_w);
+      t += line;
+      if (n.has_bn) {
+        snprintf(line, sizeof(line), " gamma=%zu beta=%zu mean=%zu var=%zu", n.off_gamma, n.off_beta, n.off_mean, n.off_var);
+        t += line;
+      }
+    } else if (n.kind == PlanNode::kMaxPool) {
+      snprintf(line, sizeof(line), "maxpool id=%d in=%d k=%d stride=%d pad=%d", n.id, n.in, n.k, n.stride, n.pad);
+      t += line;
+    } else if (n.kind == PlanNode::kAvgPool) {
+      snprintf(line, sizeof(line), "avgpool id=%d in=%d", n.id, n.in);
+      t += line;
+    } else {
+      snprintf(line, sizeof(line), "fc id=%d in=%d cin=%d cout=%d w=%zu b=%zu", n.id, n.in, n.cin, n.cout, n.off_w, n.off_b);
+      t += line;
+    }
+    t += "\n";
+  }
+  if (buf && cap) {
+    const size_t k = t.size() < cap - 1 ? t.size() : cap - 1;
+    memcpy(buf, t.data(), k);
+    buf[k] = 0;
+  }
+  ok();
+  return (long long)t.size();
+}
+
+int nncv_b200_plan_check(const char* net, size_t* n_params, int* n_nodes, int* out_features) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  Plan plan;
+  int rc = plan_from_name(net, &plan);
+  if (rc) return rc;
+  if ((rc = finalize_plan(plan, true))) return rc;
+  if (n_params) *n_params = plan.total;
+  if (n_nodes) *n_nodes = (int)plan.nodes.size();
+  if (out_features) *out_features = plan.out_features;
+  return ok();
 }
 
 int nncv_b200_load_blob(const char* net, const void* blob, size_t n_elements, size_t ele_width,
                         const nncv_b200_opts* opts) {
   std::lock_guard<std::mutex> lk(g_mutex);
-  const int depth = depth_from_name(net);
-  if (!depth) return fail(NNCV_B200_EINVAL, "net must be \"resnet18\" or \"resnet50\"");
-  if (!blob) return fail(NNCV_B200_EINVAL, "blob is null");
-  int rc = device_init();
+  Plan plan;
+  int rc = plan_from_name(net, &plan);
   if (rc) return rc;
+  if (!blob) return fail(NNCV_B200_EINVAL, "blob is null");
+  if ((rc = device_init())) return rc;
   model_reset();
-  return model_build(depth, blob, n_elements, ele_width, opts);
+  return model_build(std::move(plan), blob, n_elements, ele_width, opts);
 }
 
 int nncv_b200_unload(void) {
@@ -1320,6 +1711,30 @@ int nncv_b200_profile_get(long long i, nncv_b200_prof_rec* out) {
   }
   out->kind = r.kind; out->M = r.M; out->N = r.N; out->K = r.K; out->bn = r.bn;
   out->flops = r.flops; out->bytes = r.bytes; out->ms = r.ms;
+  return ok();
+}
+
+int nncv_b200_arena_plan(size_t n, const int* first_op, const int* last_op, const size_t* size, size_t align,
+                         size_t* offset_out, size_t* total_out) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if ((n && (!first_op || !last_op || !size || !offset_out)) || !total_out)
+    return fail(NNCV_B200_EINVAL, "arena_plan: null argument");
+  std::vector<ArenaTensor> ts(n);
+  for (size_t i = 0; i < n; ++i) {
+    if (first_op[i] > last_op[i]) return fail(NNCV_B200_EINVAL, "arena_plan: tensor %zu ends before it starts", i);
+    ts[i].first = first_op[i]; ts[i].last = last_op[i]; ts[i].size = size[i];
+  }
+  *total_out = arena_plan(ts, align);
+  for (size_t i = 0; i < n; ++i) offset_out[i] = ts[i].offset;
+  return ok();
+}
+
+int nncv_b200_activation_bytes(size_t* arena_bytes, size_t* unshared_bytes) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  Device* d = current_device_or_null();
+  if (!d || !d->model || !d->model->planned) return fail(NNCV_B200_ENOMODEL, "no forward has run on this device yet");
+  if (arena_bytes) *arena_bytes = d->model->arena.bytes;
+  if (unshared_bytes) *unshared_bytes = d->model->act_bytes_unshared;
   return ok();
 }
 

@@ -11,6 +11,8 @@ tree, so the tests read only the files this script wrote):
                          (fp32 and fp64 accumulation) and from PyTorch CPU
   res18_fp32_n4_64.npz   same at N=4, 64x64 (small case)
   res50_fp32_n2_64.npz   ResNet-50, N=2, 64x64
+  res18_from_mlir.plan   the layer plan nncv_b200.mlir_import reads out of tests/Nets/Res18.mlir
+                         (tests/Nets/Res18-half.mlir, the f16 module, gives the same plan: asserted)
 """
 import ctypes
 import json
@@ -74,9 +76,20 @@ def logits(depth, n, hw, name):
     np.savez_compressed(os.path.join(HERE, name), oracle_f32=o32, oracle_f64acc=o64, torch_cpu=tr)
 
 
+def plans():
+    from nncv_b200 import mlir_import
+    mlir_import.import_mlir_file(os.path.join(REF, "tests/Nets/Res18.mlir")).write(os.path.join(HERE, "res18_from_mlir.plan"))
+    half = mlir_import.import_mlir_file(os.path.join(REF, "tests/Nets/Res18-half.mlir"))
+    assert half.to_text() == open(os.path.join(HERE, "res18_from_mlir.plan")).read()
+
+
 if __name__ == "__main__":
+    if sys.argv[1:] == ["plans"]:
+        plans()
+        raise SystemExit(0)
     constants()
     kat0()
     logits(18, 1, 256, "res18_fp32_n1_256.npz")
     logits(18, 4, 64, "res18_fp32_n4_64.npz")
     logits(50, 2, 64, "res50_fp32_n2_64.npz")
+    plans()
