@@ -97,7 +97,7 @@ def test_activation_arena_is_smaller_than_private_buffers_and_survives_shape_cha
         rt.forward(o, x)
         a, u = ctypes.c_size_t(), ctypes.c_size_t()
         assert lib().nncv_b200_activation_bytes(ctypes.byref(a), ctypes.byref(u)) == 0
-        assert 0 < a.value <= 0.72 * u.value       # three live tensors per stage instead of five
+        assert 0 < a.value <= 0.8 * u.value        # three or four live tensors per stage instead of five
         if (n, hw) in outs:
             assert np.array_equal(outs[(n, hw)], o)   # re-planned arena, same logits bit for bit
         outs[(n, hw)] = o
