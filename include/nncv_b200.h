@@ -76,7 +76,14 @@ enum { NNCV_B200_F32 = 0, NNCV_B200_F16 = 1, NNCV_B200_BF16 = 2 };
 typedef struct {
   int compute_dtype; /* NNCV_B200_F32 (CUDA-core fp32 path), _F16 or _BF16 (tcgen05 path);
                         -1 = follow the params file: eleWidth 4 -> F32, 2 -> F16 */
-  int reserved[7];
+  unsigned device_mask; /* 0: the model lives on the current CUDA device only.  Otherwise bit d set =
+                        a replica of the weights on device d (the current device must be among them):
+                        _mlir_ciface_forward then cuts a batch that lies in HOST memory into
+                        contiguous slices, one per device, and every device writes its logits rows
+                        straight into the caller's buffer (one host thread per extra device; no
+                        exchange between devices).  Device-resident tensors are processed by the
+                        current device alone. */
+  int reserved[6];
 } nncv_b200_opts;
 
 /* ---- the drop-in boundary --------------------------------------------------------------
@@ -139,6 +146,15 @@ const char* nncv_b200_last_error(void);
  * which role gave up is in the message) or NNCV_B200_ECUDA (code 5: refused copy).  The reference
  * has no device and no counterpart (its errors are exit(-1), DnnModelLowering.cpp:222-230). */
 int nncv_b200_device_status(void);
+/* The slice [lo, hi) of a batch of n images that part `rank` of `world` processes (the first
+ * n % world parts get one image more): the rule of the multi-device fan-out. */
+int nncv_b200_shard_range(int n, int rank, int world, int* lo, int* hi);
+/* Host-side self-test of the fan-out machinery, needs no device: runs a stand-in job for every
+ * part of [0, n) on the same worker threads and with the same join and error hand-over as the
+ * multi-device forward, records each part's slice in lo_out/hi_out (parts entries), counts the
+ * parts that ran on another thread than the caller's, and makes part `fail_rank` (or none: -1)
+ * fail: the call must then return that part's status with its message, after all parts finished. */
+int nncv_b200_selftest_fanout(int n, int parts, int fail_rank, int* lo_out, int* hi_out, int* thread_differs);
 /* Failure-path self-test: launches one tiny kernel that waits on an mbarrier nobody arrives on,
  * with a limit of 2^log2_clocks clocks (at most 2^24, a few milliseconds), then reports the
  * time-out into the status word and returns; nothing faults and nothing hangs.  After a

@@ -21,6 +21,7 @@ EXPORTS = [
     "nncv_b200_launch_count", "nncv_b200_set_stream", "nncv_b200_profile", "nncv_b200_profile_count",
     "nncv_b200_profile_get", "nncv_b200_device_status", "nncv_b200_selftest_wait_timeout",
     "nncv_b200_arena_plan", "nncv_b200_activation_bytes", "nncv_b200_plan_check", "nncv_b200_plan_text",
+    "nncv_b200_shard_range", "nncv_b200_selftest_fanout",
     "nncv_flat_array_read", "nncv_flat_array_free", "nncv_flat_array_count",
     "nncv_flat_array_indexer", "nncv_flat_array_data", "nncv_flat_array_wrapped",
     "nncv_flat_array_write",
@@ -38,7 +39,7 @@ class ProfRec(ctypes.Structure):
 
 
 class Opts(ctypes.Structure):
-    _fields_ = [("compute_dtype", c_int), ("reserved", c_int * 7)]
+    _fields_ = [("compute_dtype", c_int), ("device_mask", ctypes.c_uint), ("reserved", c_int * 6)]
 
 
 _lib = None
@@ -67,6 +68,8 @@ def lib() -> ctypes.CDLL:
     L.nncv_b200_device_status.restype = c_int
     L.nncv_b200_arena_plan.argtypes = [c_size_t, POINTER(c_int), POINTER(c_int), POINTER(c_size_t), c_size_t,
                                        POINTER(c_size_t), POINTER(c_size_t)]
+    L.nncv_b200_shard_range.argtypes = [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]
+    L.nncv_b200_selftest_fanout.argtypes = [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int)]
     L.nncv_b200_plan_text.argtypes = [c_char_p, ctypes.c_char_p, c_size_t]
     L.nncv_b200_plan_text.restype = c_longlong
     L.nncv_b200_plan_check.argtypes = [c_char_p, POINTER(c_size_t), POINTER(c_int), POINTER(c_int)]

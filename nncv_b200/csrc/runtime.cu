@@ -8,6 +8,10 @@
 
 #include <algorithm>
 #include <array>
+#include <atomic>
+#include <condition_variable>
+#include <functional>
+#include <thread>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -32,7 +36,7 @@ namespace {
 thread_local int g_status = NNCV_B200_OK;
 thread_local char g_msg[512] = "";
 std::mutex g_mutex;
-long long g_launches = 0;
+std::atomic<long long> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
   g_status = code;
@@ -100,6 +104,7 @@ struct Device {
   void* scratch = nullptr;     // grow-only scratch (packed B of nncv_b200_matmul)
   size_t scratch_bytes = 0;
   Model* model = nullptr;      // the model replica living on this device
+  std::vector<int> group;      // devices that hold a replica of this device's model (itself first), or empty
 };
 constexpr int kMaxDevices = 64;
 Device* g_devices[kMaxDevices] = {};
@@ -177,10 +182,11 @@ struct ProfRec {
 bool g_autotune = getenv("NNCV_B200_AUTOTUNE") ? atoi(getenv("NNCV_B200_AUTOTUNE")) != 0 : true;
 bool g_force_gather = false;  // tuning/test hook: route algo-0 convs through the gather kernel
 bool g_prof_on = false;
+int g_prof_dev = -1;            // records are taken on this device only (worker threads of a fan-out skip them)
 std::vector<ProfRec> g_prof;
 
 void prof_begin(int kind, double flops, double bytes, int M, int N, int K, int bn, cudaStream_t st) {
-  if (!g_prof_on) return;
+  if (!g_prof_on || !t_dev || t_dev->id != g_prof_dev) return;
   ProfRec r{kind, flops, bytes, M, N, K, bn, nullptr, nullptr, -1.0f};
   cudaEventCreate(&r.e0);
   cudaEventCreate(&r.e1);
@@ -188,7 +194,7 @@ void prof_begin(int kind, double flops, double bytes, int M, int N, int K, int b
   g_prof.push_back(r);
 }
 void prof_end(cudaStream_t st) {
-  if (!g_prof_on || g_prof.empty()) return;
+  if (!g_prof_on || g_prof.empty() || !t_dev || t_dev->id != g_prof_dev) return;
   cudaEventRecord(g_prof.back().e1, st);
 }
 void prof_clear() {
@@ -294,13 +300,19 @@ struct TuneCache {
       fclose(f);
     }
   }
+  std::mutex mu;   // the replicas of a multi-device model tune concurrently, each on its own thread
+  // Entries are never erased or overwritten with another value, and std::map nodes do not move:
+  // the returned pointer stays valid.
   const std::string* find(const std::string& k) {
+    std::lock_guard<std::mutex> lk(mu);
     load();
     auto it = kv.find(k);
     return it == kv.end() ? nullptr : &it->second;
   }
   void put(const std::string& k, const std::string& v) {
+    std::lock_guard<std::mutex> lk(mu);
     load();
+    if (kv.count(k)) return;
     kv[k] = v;
     if (path.empty()) return;
     if (FILE* f = fopen(path.c_str(), "a")) {
@@ -1334,6 +1346,55 @@ int check_dst(nncv_memref2* dst, int N, int of, size_t ele_width, bool* allocate
   return NNCV_B200_OK;
 }
 
+// One device's share of a forward: images [sp, sp + N images) -> logits rows at dp (row pitch
+// dst_stride elements).  Runs on the calling thread's current device (g_dev), on stream st;
+// synchronises and reads the device status word unless device_only.
+int forward_slice(Model& m, const char* sp, bool src_dev, char* dp, bool dst_dev, size_t dst_stride, int N, int H, int W,
+                  cudaStream_t st, bool device_only) {
+  int rc;
+  const size_t ew = m.ele_width;
+  const int of = m.plan.out_features;
+  const size_t img_bytes = (size_t)3 * H * W * ew;
+  // Host input, large batch: run the batch as two halves so that the host->device copy of the
+  // second half overlaps the forward of the first (copies on their own stream, ordered by events).
+  // Four parts were slower at batch 256 (2.48 ms against 2.27 ms): four forwards of 64 images take
+  // longer than two of 128, and the kernels, not the copy, are then the longer leg.
+  const int chunks = (!src_dev && !device_only && N >= 128 && N % 2 == 0) ? 2 : 1;
+  const int Nc = N / chunks;
+  if ((rc = ensure_workspace(m, Nc, H, W))) return rc;
+  if (!src_dev && (rc = m.in_stage.reserve((size_t)N * img_bytes))) return rc;
+  if (chunks > 1) {
+    if (!g_dev.copy_stream) {
+      CU(cudaStreamCreateWithFlags(&g_dev.copy_stream, cudaStreamNonBlocking));
+      for (auto& e : g_dev.copy_done) CU(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
+    // the copy stream must not overwrite the staging buffer before earlier work on `st` has read it
+    CU(cudaEventRecord(g_dev.copy_done[4], st));
+    CU(cudaStreamWaitEvent(g_dev.copy_stream, g_dev.copy_done[4], 0));
+    for (int c = 0; c < chunks; ++c) {
+      CU(cudaMemcpyAsync((char*)m.in_stage.p + (size_t)c * Nc * img_bytes, sp + (size_t)c * Nc * img_bytes,
+                         (size_t)Nc * img_bytes, cudaMemcpyHostToDevice, g_dev.copy_stream));
+      CU(cudaEventRecord(g_dev.copy_done[c], g_dev.copy_stream));
+    }
+  } else if (!src_dev) {
+    CU(cudaMemcpyAsync(m.in_stage.p, sp, (size_t)N * img_bytes, cudaMemcpyHostToDevice, st));
+  }
+  for (int c = 0; c < chunks; ++c) {
+    const void* src_d = src_dev ? (const void*)sp : (const void*)((char*)m.in_stage.p + (size_t)c * Nc * img_bytes);
+    if (chunks > 1) CU(cudaStreamWaitEvent(st, g_dev.copy_done[c], 0));
+    if ((rc = model_forward_device(m, src_d, Nc, H, W, st))) return rc;
+    const void* logits = m.io_dt == kF32 ? m.logits32.p : m.logits_io.p;
+    CU(cudaMemcpy2DAsync(dp + (size_t)c * Nc * dst_stride * ew, dst_stride * ew, logits, (size_t)of * ew,
+                         (size_t)of * ew, (size_t)Nc, dst_dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, st));
+  }
+  if (device_only) return ok();
+  CU(cudaStreamSynchronize(st));
+  if ((rc = check_kernel_status())) return rc;
+  return ok();
+}
+
+int forward_fanout(const char* sp, char* dp, size_t dst_stride, int N, int H, int W);
+
 int forward_impl(nncv_memref2* dst, nncv_memref4* src, void* params, cudaStream_t user_stream,
                  bool device_only) {
   int rc = device_init();
@@ -1370,43 +1431,128 @@ int forward_impl(nncv_memref2* dst, nncv_memref4* src, void* params, cudaStream_
   if (device_only && (!src_dev || !dst_dev))
     return fail(NNCV_B200_EINVAL, "nncv_b200_forward_device needs device-resident src and dst");
   cudaStream_t st = device_only ? user_stream : (g_dev.user_stream_set ? g_dev.user_stream : g_dev.stream);
+  // several devices hold a replica (nncv_b200_opts.device_mask at load) and the tensors are in host
+  // memory: every device takes a contiguous slice of the batch
+  if (!device_only && !src_dev && !dst_dev && g_dev.group.size() > 1 && N > 1)
+    return forward_fanout(sp, dp, (size_t)dst->strides[0], N, H, W);
+  return forward_slice(m, sp, src_dev, dp, dst_dev, (size_t)dst->strides[0], N, H, W, st, device_only);
+}
+
+// =====================================================================================
+// batch fan-out over the devices of one process
+// =====================================================================================
+// Images are independent, so a batch in host memory is cut into contiguous slices, one per device
+// that holds a replica of the model; each device copies its slice in, runs the forward and copies
+// its logits rows straight into the caller's buffer -- there is no exchange between devices, hence
+// no collective.  One persistent host thread per extra device issues that device's work (its launch
+// sequence would otherwise queue behind the other devices' on one thread); the calling thread serves
+// the first device of the group.  nncv itself is single-device (include/nncv/compiler/Utils/
+// PlatformCtx.hpp:140-144 warns when the GPU count is not 1).
+
+// Slice [lo, hi) of n items owned by part `rank` of `world`: the first n % world parts get one more.
+void shard_range(int n, int rank, int world, int* lo, int* hi) {
+  const int base = n / world, extra = n % world;
+  *lo = rank * base + (rank < extra ? rank : extra);
+  *hi = *lo + base + (rank < extra ? 1 : 0);
+}
+
+struct Worker {
+  std::thread th;
+  std::mutex mu;
+  std::condition_variable cv;
+  std::function<int()> job;
+  bool has_job = false, done = false, quit = false;
+  int rc = 0;
+  std::string msg;
+  void loop() {
+    std::unique_lock<std::mutex> lk(mu);
+    for (;;) {
+      cv.wait(lk, [&] { return has_job || quit; });
+      if (quit) return;
+      std::function<int()> j = std::move(job);
+      has_job = false;
+      lk.unlock();
+      const int r = j();
+      lk.lock();
+      rc = r;
+      msg = r ? g_msg : "";    // the status text lives in this thread's own buffer: hand it over
+      done = true;
+      cv.notify_all();
+    }
+  }
+  void submit(std::function<int()> j) {
+    std::lock_guard<std::mutex> lk(mu);
+    job = std::move(j);
+    has_job = true;
+    done = false;
+    cv.notify_all();
+  }
+  int wait(std::string* m) {
+    std::unique_lock<std::mutex> lk(mu);
+    cv.wait(lk, [&] { return done; });
+    *m = msg;
+    return rc;
+  }
+};
+// One worker per slot, created on first use and kept for the life of the process (threads parked
+// on a condition variable); slot i serves the (i+1)-th device of a group.
+// The workers are never destroyed: a parked thread must not see its mutex go away at process exit.
+Worker& worker(size_t i) {
+  static std::vector<Worker*>* workers = new std::vector<Worker*>();
+  while (workers->size() <= i) {
+    Worker* w = new Worker();
+    workers->push_back(w);
+    w->th = std::thread([w] { w->loop(); });
+    w->th.detach();
+  }
+  return *(*workers)[i];
+}
+
+// Runs job(rank, lo, hi) for every part of [0, n): parts 1.. on worker threads, part 0 on the calling
+// thread, then joins them all.  The first failure (lowest rank) becomes this thread's status; every
+// part runs to its end either way, so no work is left in flight behind an error.
+int run_parts(int n, int parts, const std::function<int(int, int, int)>& job) {
+  if (parts > n) parts = n;
+  if (parts < 1) parts = 1;
+  for (int r = 1; r < parts; ++r) {
+    int lo, hi;
+    shard_range(n, r, parts, &lo, &hi);
+    worker((size_t)r - 1).submit([=, &job] { return job(r, lo, hi); });
+  }
+  int lo0, hi0;
+  shard_range(n, 0, parts, &lo0, &hi0);
+  int rc0 = job(0, lo0, hi0);
+  std::string msg0 = rc0 ? g_msg : "";
+  int first_rc = rc0, first_rank = 0;
+  std::string first_msg = msg0;
+  for (int r = 1; r < parts; ++r) {
+    std::string m;
+    const int rc = worker((size_t)r - 1).wait(&m);
+    if (rc && !first_rc) { first_rc = rc; first_rank = r; first_msg = m; }
+  }
+  if (first_rc) return fail(first_rc, "part %d of %d: %s", first_rank, parts, first_msg.c_str());
+  return NNCV_B200_OK;
+}
+
+int forward_fanout(const char* sp, char* dp, size_t dst_stride, int N, int H, int W) {
+  Device& primary = g_dev;
+  const std::vector<int> group = primary.group;
+  const size_t ew = primary.model->ele_width;
   const size_t img_bytes = (size_t)3 * H * W * ew;
-  // Host input, large batch: run the batch as two halves so that the host->device copy of the
-  // second half overlaps the forward of the first (copies on their own stream, ordered by events).
-  // Four parts were slower at batch 256 (2.48 ms against 2.27 ms): four forwards of 64 images take
-  // longer than two of 128, and the kernels, not the copy, are then the longer leg.
-  const int chunks = (!src_dev && !device_only && N >= 128 && N % 2 == 0) ? 2 : 1;
-  const int Nc = N / chunks;
-  if ((rc = ensure_workspace(m, Nc, H, W))) return rc;
-  if (!src_dev && (rc = m.in_stage.reserve((size_t)N * img_bytes))) return rc;
-  if (chunks > 1) {
-    if (!g_dev.copy_stream) {
-      CU(cudaStreamCreateWithFlags(&g_dev.copy_stream, cudaStreamNonBlocking));
-      for (auto& e : g_dev.copy_done) CU(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
-    }
-    // the copy stream must not overwrite the staging buffer before earlier work on `st` has read it
-    CU(cudaEventRecord(g_dev.copy_done[4], st));
-    CU(cudaStreamWaitEvent(g_dev.copy_stream, g_dev.copy_done[4], 0));
-    for (int c = 0; c < chunks; ++c) {
-      CU(cudaMemcpyAsync((char*)m.in_stage.p + (size_t)c * Nc * img_bytes, sp + (size_t)c * Nc * img_bytes,
-                         (size_t)Nc * img_bytes, cudaMemcpyHostToDevice, g_dev.copy_stream));
-      CU(cudaEventRecord(g_dev.copy_done[c], g_dev.copy_stream));
-    }
-  } else if (!src_dev) {
-    CU(cudaMemcpyAsync(m.in_stage.p, sp, (size_t)N * img_bytes, cudaMemcpyHostToDevice, st));
-  }
-  for (int c = 0; c < chunks; ++c) {
-    const void* src_d = src_dev ? (const void*)sp : (const void*)((char*)m.in_stage.p + (size_t)c * Nc * img_bytes);
-    if (chunks > 1) CU(cudaStreamWaitEvent(st, g_dev.copy_done[c], 0));
-    if ((rc = model_forward_device(m, src_d, Nc, H, W, st))) return rc;
-    const void* logits = m.io_dt == kF32 ? m.logits32.p : m.logits_io.p;
-    CU(cudaMemcpy2DAsync(dp + (size_t)c * Nc * dst->strides[0] * ew, (size_t)dst->strides[0] * ew, logits, (size_t)of * ew,
-                         (size_t)of * ew, (size_t)Nc, dst_dev ? cudaMemcpyDeviceToDevice : cudaMemcpyDeviceToHost, st));
-  }
-  if (device_only) return ok();
-  CU(cudaStreamSynchronize(st));
-  if ((rc = check_kernel_status())) return rc;
-  return ok();
+  auto job = [&, sp, dp](int rank, int lo, int hi) -> int {
+    if (hi <= lo) return (int)NNCV_B200_OK;
+    if (cudaSetDevice(group[(size_t)rank]) != cudaSuccess) return fail(NNCV_B200_ECUDA, "cudaSetDevice(%d) failed", group[(size_t)rank]);
+    int rc = device_init();
+    if (rc) return rc;
+    if (!g_dev.model) return fail(NNCV_B200_ENOMODEL, "device %d holds no replica of the model", g_dev.id);
+    cudaStream_t st = (rank == 0 && g_dev.user_stream_set) ? g_dev.user_stream : g_dev.stream;
+    return forward_slice(*g_dev.model, sp + (size_t)lo * img_bytes, false, dp + (size_t)lo * dst_stride * ew, false, dst_stride,
+                         hi - lo, H, W, st, false);
+  };
+  const int rc = run_parts(N, (int)group.size(), job);
+  cudaSetDevice(primary.id);
+  t_dev = &primary;
+  return rc;
 }
 
 // "resnet18" / "resnet50": the built-in plans; "plan:<text>": a plan given inline; anything else:
@@ -1425,6 +1571,50 @@ int plan_from_name(const char* net, Plan* out) {
     text.assign(std::istreambuf_iterator<char>(f), std::istreambuf_iterator<char>());
   }
   return parse_plan(text, out);
+}
+
+// Builds the model on the current device, or -- opts->device_mask set -- a replica on every listed
+// device (the current one must be among them and serves the first slice of every batch).
+int load_group(const Plan& plan, const void* blob, size_t n_elements, size_t ew, const nncv_b200_opts* opts) {
+  const unsigned mask = opts ? opts->device_mask : 0u;
+  int rc = device_init();
+  if (rc) return rc;
+  Device* primary = t_dev;
+  // replicas of an earlier multi-device load go away with the model they belong to
+  for (int d : std::vector<int>(primary->group)) {
+    if (d == primary->id || d < 0 || d >= kMaxDevices || !g_devices[d]) continue;
+    if (cudaSetDevice(d) == cudaSuccess) {
+      cudaDeviceSynchronize();
+      t_dev = g_devices[d];
+      model_reset();
+    }
+  }
+  cudaSetDevice(primary->id);
+  t_dev = primary;
+  primary->group.clear();
+  model_reset();
+  if (mask == 0 || mask == (1u << primary->id)) return model_build(plan, blob, n_elements, ew, opts);
+  if (!(mask & (1u << primary->id)))
+    return fail(NNCV_B200_EINVAL, "device_mask 0x%x does not include the current device %d", mask, primary->id);
+  int count = 0;
+  cudaGetDeviceCount(&count);
+  std::vector<int> group{primary->id};
+  for (int d = 0; d < 32; ++d)
+    if ((mask & (1u << d)) && d != primary->id) {
+      if (d >= count) return fail(NNCV_B200_EINVAL, "device_mask 0x%x names device %d, this process sees %d", mask, d, count);
+      group.push_back(d);
+    }
+  for (int d : group) {
+    if (cudaSetDevice(d) != cudaSuccess) { rc = fail(NNCV_B200_ECUDA, "cudaSetDevice(%d) failed", d); break; }
+    if ((rc = device_init())) break;
+    model_reset();
+    if ((rc = model_build(plan, blob, n_elements, ew, opts))) break;
+  }
+  cudaSetDevice(primary->id);
+  t_dev = primary;
+  if (rc) return rc;
+  primary->group = group;
+  return ok();
 }
 
 }  // namespace
@@ -1590,10 +1780,7 @@ int nncv_b200_load(const char* net, const char* model_bin_path, const nncv_b200_
     }
   }
   const size_t ew = a->idx[0].eleWidth;
-  int rc = device_init();
-  if (rc) return rc;
-  model_reset();
-  return model_build(std::move(plan), a->data.data(), (size_t)a->wrapped.sizes[0], ew, opts);
+  return load_group(plan, a->data.data(), (size_t)a->wrapped.sizes[0], ew, opts);
 }
 
 long long nncv_b200_plan_text(const char* net, char* buf, size_t cap) {
@@ -1651,15 +1838,25 @@ int nncv_b200_load_blob(const char* net, const void* blob, size_t n_elements, si
   int rc = plan_from_name(net, &plan);
   if (rc) return rc;
   if (!blob) return fail(NNCV_B200_EINVAL, "blob is null");
-  if ((rc = device_init())) return rc;
-  model_reset();
-  return model_build(std::move(plan), blob, n_elements, ele_width, opts);
+  return load_group(plan, blob, n_elements, ele_width, opts);
 }
 
 int nncv_b200_unload(void) {
   std::lock_guard<std::mutex> lk(g_mutex);
   t_dev = current_device_or_null();
   if (t_dev) {
+    Device* primary = t_dev;
+    for (int d : std::vector<int>(primary->group)) {   // replicas on the other devices of a multi-device load
+      if (d == primary->id || d < 0 || d >= kMaxDevices || !g_devices[d]) continue;
+      if (cudaSetDevice(d) == cudaSuccess) {
+        cudaDeviceSynchronize();
+        t_dev = g_devices[d];
+        model_reset();
+      }
+    }
+    cudaSetDevice(primary->id);
+    t_dev = primary;
+    primary->group.clear();
     cudaDeviceSynchronize();
     model_reset();
   }
@@ -1690,8 +1887,10 @@ int nncv_b200_set_stream(void* cuda_stream, int enable) {
 
 int nncv_b200_profile(int enable) {
   std::lock_guard<std::mutex> lk(g_mutex);
-  if (current_device_or_null()) cudaDeviceSynchronize();
+  Device* pd = current_device_or_null();
+  if (pd) cudaDeviceSynchronize();
   prof_clear();
+  g_prof_dev = pd ? pd->id : 0;
   g_prof_on = enable != 0;
   return ok();
 }
@@ -1736,6 +1935,31 @@ int nncv_b200_activation_bytes(size_t* arena_bytes, size_t* unshared_bytes) {
   if (arena_bytes) *arena_bytes = d->model->arena.bytes;
   if (unshared_bytes) *unshared_bytes = d->model->act_bytes_unshared;
   return ok();
+}
+
+int nncv_b200_shard_range(int n, int rank, int world, int* lo, int* hi) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (n < 0 || world <= 0 || rank < 0 || rank >= world || !lo || !hi) return fail(NNCV_B200_EINVAL, "shard_range: bad argument");
+  shard_range(n, rank, world, lo, hi);
+  return ok();
+}
+
+int nncv_b200_selftest_fanout(int n, int parts, int fail_rank, int* lo_out, int* hi_out, int* thread_differs) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  if (n < 0 || parts < 1 || parts > 64 || !lo_out || !hi_out) return fail(NNCV_B200_EINVAL, "selftest_fanout: bad argument");
+  for (int i = 0; i < parts; ++i) lo_out[i] = hi_out[i] = -1;
+  const std::thread::id me = std::this_thread::get_id();
+  std::atomic<int> others{0};
+  auto job = [&](int rank, int lo, int hi) -> int {
+    lo_out[rank] = lo;
+    hi_out[rank] = hi;
+    if (std::this_thread::get_id() != me) ++others;
+    if (rank == fail_rank) return fail(NNCV_B200_ETIMEOUT, "injected failure on part %d", rank);
+    return (int)NNCV_B200_OK;
+  };
+  const int rc = run_parts(n, parts, job);
+  if (thread_differs) *thread_differs = others.load();
+  return rc ? rc : ok();
 }
 
 int nncv_b200_device_status(void) {

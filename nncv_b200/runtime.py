@@ -21,16 +21,20 @@ def _ptr(t) -> int:
     return t.data_ptr()  # torch tensor
 
 
-def load(net: str, model_bin: str, compute_dtype: int = -1) -> None:
-    """`-split-params` weight loading: parse, upload, fold BN, pack (include/nncv_b200.h)."""
+def load(net: str, model_bin: str, compute_dtype: int = -1, device_mask: int = 0) -> None:
+    """`-split-params` weight loading: parse, upload, fold BN, pack (include/nncv_b200.h).
+    device_mask: replicas on several devices of this process (bit d = device d), batches in host
+    memory are then split over them."""
     o = Opts()
     o.compute_dtype = compute_dtype
+    o.device_mask = device_mask
     check(lib().nncv_b200_load(net.encode(), model_bin.encode(), ctypes.byref(o)))
 
 
-def load_blob(net: str, blob: np.ndarray, compute_dtype: int = -1) -> None:
+def load_blob(net: str, blob: np.ndarray, compute_dtype: int = -1, device_mask: int = 0) -> None:
     o = Opts()
     o.compute_dtype = compute_dtype
+    o.device_mask = device_mask
     blob = np.ascontiguousarray(blob)
     check(lib().nncv_b200_load_blob(net.encode(), blob.ctypes.data, blob.size, blob.itemsize, ctypes.byref(o)))
 
