@@ -298,6 +298,38 @@ int nncv_b200_nchw_to_nhwc(const void* in, int in_dtype, void* out, int out_dtyp
 int nncv_b200_bn_fold(const void* gamma, const void* beta, const void* mean, const void* var,
                       int dtype, int C, float* scale, float* shift, void* stream);
 
+/* ---- operators of nncv's mobile / detection fixtures (memory-bound; NHWC, device pointers) ----
+ * Activations, as the fixtures spell them:
+ *   RELU          cmpf ugt x, 0 ; select                         (tests/Nets/ReLU.mlir:8-13)
+ *   HARD_SIGMOID  max(0, min(1, (x + 3) / 6))                    (tests/Nets/MobileNetV3.mlir:345-377)
+ *   HARD_SWISH    x * hard_sigmoid(x)
+ *   SIGMOID       1 / (1 + exp(-x))                              (tests/Nets/Yolov5s.mlir:158-164)
+ *   SILU          x * sigmoid(x)                                 (Yolov5s.mlir:158-169)                  */
+enum { NNCV_B200_ACT_NONE = 0, NNCV_B200_ACT_RELU = 1, NNCV_B200_ACT_HARD_SIGMOID = 2, NNCV_B200_ACT_HARD_SWISH = 3,
+       NNCV_B200_ACT_SIGMOID = 4, NNCV_B200_ACT_SILU = 5 };
+/* linalg.depthwise_conv_2d_nchw_chw (MobileNetV3.mlir:301,426,486) + folded batch-norm scale/shift
+ * (fp32 [C] or NULL) + activation in one kernel.  in [N,H,W,C], weights [C,R,S] (the fixture's
+ * collapsed tensor<CxRxS>; fp32, or fp16 when dtype is F16), out [N,OH,OW,C]; C a multiple of 8
+ * (16-bit) or 4 (fp32). */
+int nncv_b200_depthwise_conv_nhwc(const void* in, const void* weights, int w_dtype, const float* scale, const float* shift,
+                                  void* out, int dtype, int N, int H, int W, int C, int R, int S, int stride, int pad, int act,
+                                  void* stream);
+/* Elementwise activation over n elements (n a multiple of 8 / 4); in == out allowed. */
+int nncv_b200_activation(const void* in, void* out, int dtype, size_t n, int act, void* stream);
+/* Squeeze-and-excitation (MobileNetV3.mlir:319-383): gate[N,C] = hard_sigmoid(w2 * relu(w1 * pooled + b1) + b2)
+ * with pooled [N,C] (from nncv_b200_avgpool_nhwc), w1 [Cr,C], b1 [Cr], w2 [C,Cr], b2 [C] in fp32
+ * (the two 1x1 convolutions on [N,C,1,1] of the fixture); then out = in * gate broadcast over pixels. */
+int nncv_b200_se_gate(const void* pooled, const float* w1, const float* b1, const float* w2, const float* b2, void* gate,
+                      int dtype, int N, int C, int Cr, void* stream);
+int nncv_b200_scale_channels_nhwc(const void* in, const void* gate, void* out, int dtype, int N, int HW, int C, void* stream);
+/* tensor.concat dim(1) (Yolov5s.mlir:276,445,837): out[p, :] = in_0[p, :] ++ in_1[p, :] ++ ... for
+ * `pixels` = N*H*W pixels; up to 8 inputs, every channel count a multiple of 8 / 4. */
+int nncv_b200_concat_channels_nhwc(const void* const* inputs, const int* channels, int n_inputs, void* out, int dtype,
+                                   long long pixels, void* stream);
+/* Nearest-neighbour 2x upsampling (Yolov5s.mlir:876-884: tensor.extract at floordivsi(index, 2)):
+ * in [N,H,W,C] -> out [N,2H,2W,C]. */
+int nncv_b200_upsample2x_nhwc(const void* in, void* out, int dtype, int N, int H, int W, int C, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

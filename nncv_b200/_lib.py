@@ -22,6 +22,8 @@ EXPORTS = [
     "nncv_b200_profile_get", "nncv_b200_device_status", "nncv_b200_selftest_wait_timeout",
     "nncv_b200_arena_plan", "nncv_b200_activation_bytes", "nncv_b200_plan_check", "nncv_b200_plan_text",
     "nncv_b200_shard_range", "nncv_b200_selftest_fanout",
+    "nncv_b200_depthwise_conv_nhwc", "nncv_b200_activation", "nncv_b200_se_gate", "nncv_b200_scale_channels_nhwc",
+    "nncv_b200_concat_channels_nhwc", "nncv_b200_upsample2x_nhwc",
     "nncv_flat_array_read", "nncv_flat_array_free", "nncv_flat_array_count",
     "nncv_flat_array_indexer", "nncv_flat_array_data", "nncv_flat_array_wrapped",
     "nncv_flat_array_write",
@@ -68,6 +70,12 @@ def lib() -> ctypes.CDLL:
     L.nncv_b200_device_status.restype = c_int
     L.nncv_b200_arena_plan.argtypes = [c_size_t, POINTER(c_int), POINTER(c_int), POINTER(c_size_t), c_size_t,
                                        POINTER(c_size_t), POINTER(c_size_t)]
+    L.nncv_b200_depthwise_conv_nhwc.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 11 + [c_void_p]
+    L.nncv_b200_activation.argtypes = [c_void_p, c_void_p, c_int, c_size_t, c_int, c_void_p]
+    L.nncv_b200_se_gate.argtypes = [c_void_p] * 6 + [c_int] * 4 + [c_void_p]
+    L.nncv_b200_scale_channels_nhwc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    L.nncv_b200_concat_channels_nhwc.argtypes = [POINTER(c_void_p), POINTER(c_int), c_int, c_void_p, c_int, c_longlong, c_void_p]
+    L.nncv_b200_upsample2x_nhwc.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
     L.nncv_b200_shard_range.argtypes = [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]
     L.nncv_b200_selftest_fanout.argtypes = [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int)]
     L.nncv_b200_plan_text.argtypes = [c_char_p, ctypes.c_char_p, c_size_t]

@@ -191,6 +191,18 @@ cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean
 cudaError_t launch_convert(const void* src, DType src_dt, void* dst, DType dst_dt, size_t n,
                            cudaStream_t stream);
 
+// ---- memory-bound operators of the mobile / detection fixtures (NHWC, 16-byte accesses) --------
+enum Activation : int { kActNone = 0, kActRelu = 1, kActHardSigmoid = 2, kActHardSwish = 3, kActSigmoid = 4, kActSilu = 5 };
+// depthwise conv, weights [C][R*S] (fp32, or fp16 with fp16 activations), folded batch-norm, activation
+cudaError_t launch_depthwise(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
+                             int N, int H, int W, int C, int R, int S, int stride, int pad, int act, cudaStream_t st);
+cudaError_t launch_activation(const void* x, void* y, DType dt, size_t n, int act, cudaStream_t st);
+cudaError_t launch_scale_channels(const void* x, const void* gate, void* y, DType dt, int N, long long HW, int C, cudaStream_t st);
+cudaError_t launch_se_gate(const void* pooled, const float* w1, const float* b1, const float* w2, const float* b2, void* gate,
+                           DType dt, int N, int C, int Cr, cudaStream_t st);
+cudaError_t launch_concat(const void* const* in, const int* channels, int n_in, void* out, DType dt, long long pixels, cudaStream_t st);
+cudaError_t launch_upsample2x(const void* in, void* out, DType dt, int N, int H, int W, int C, cudaStream_t st);
+
 // ---- activation arena planning (host only) ----------------------------------------------------
 struct ArenaTensor {
   int first = 0, last = 0;   // ops that produce it / read it last, both included

@@ -2233,6 +2233,96 @@ int nncv_b200_nchw_to_nhwc(const void* in, int in_dtype, void* out, int out_dtyp
   return ok();
 }
 
+int nncv_b200_depthwise_conv_nhwc(const void* in, const void* weights, int w_dtype, const float* scale, const float* shift,
+                                  void* out, int dtype, int N, int H, int W, int C, int R, int S, int stride, int pad, int act,
+                                  void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!in || !weights || !out || N <= 0 || H <= 0 || W <= 0 || C <= 0 || R <= 0 || S <= 0 || stride <= 0 || pad < 0 || dtype < 0 ||
+      dtype > 2 || act < 0 || act > 5)
+    return fail(NNCV_B200_EINVAL, "depthwise_conv: bad argument");
+  if (launch_depthwise(in, weights, (DType)w_dtype, scale, shift, out, (DType)dtype, N, H, W, C, R, S, stride, pad, act,
+                       (cudaStream_t)stream) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NNCV_B200_EINVAL, "depthwise_conv: C must be a multiple of %d, weights fp32 (or fp16 with fp16 activations), output not empty",
+                16 / (int)dtype_size((DType)dtype));
+  }
+  ++g_launches;
+  return ok();
+}
+
+int nncv_b200_activation(const void* in, void* out, int dtype, size_t n, int act, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!in || !out || dtype < 0 || dtype > 2 || act < 0 || act > 5) return fail(NNCV_B200_EINVAL, "activation: bad argument");
+  if (n == 0) return ok();
+  if (launch_activation(in, out, (DType)dtype, n, act, (cudaStream_t)stream) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NNCV_B200_EINVAL, "activation: the element count must be a multiple of %d", 16 / (int)dtype_size((DType)dtype));
+  }
+  ++g_launches;
+  return ok();
+}
+
+int nncv_b200_se_gate(const void* pooled, const float* w1, const float* b1, const float* w2, const float* b2, void* gate,
+                      int dtype, int N, int C, int Cr, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!pooled || !w1 || !w2 || !gate || N <= 0 || C <= 0 || Cr <= 0 || dtype < 0 || dtype > 2)
+    return fail(NNCV_B200_EINVAL, "se_gate: bad argument");
+  if (launch_se_gate(pooled, w1, b1, w2, b2, gate, (DType)dtype, N, C, Cr, (cudaStream_t)stream) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NNCV_B200_EINVAL, "se_gate: C + Cr must fit 48 KB of shared memory as floats");
+  }
+  ++g_launches;
+  return ok();
+}
+
+int nncv_b200_scale_channels_nhwc(const void* in, const void* gate, void* out, int dtype, int N, int HW, int C, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!in || !gate || !out || N <= 0 || HW <= 0 || C <= 0 || dtype < 0 || dtype > 2)
+    return fail(NNCV_B200_EINVAL, "scale_channels: bad argument");
+  if (launch_scale_channels(in, gate, out, (DType)dtype, N, HW, C, (cudaStream_t)stream) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NNCV_B200_EINVAL, "scale_channels: C must be a multiple of %d", 16 / (int)dtype_size((DType)dtype));
+  }
+  ++g_launches;
+  return ok();
+}
+
+int nncv_b200_concat_channels_nhwc(const void* const* inputs, const int* channels, int n_inputs, void* out, int dtype,
+                                   long long pixels, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!inputs || !channels || !out || pixels <= 0 || dtype < 0 || dtype > 2) return fail(NNCV_B200_EINVAL, "concat: bad argument");
+  if (launch_concat(inputs, channels, n_inputs, out, (DType)dtype, pixels, (cudaStream_t)stream) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NNCV_B200_EINVAL, "concat: 1 to 8 inputs, every channel count a multiple of %d, pointers 16-byte aligned",
+                16 / (int)dtype_size((DType)dtype));
+  }
+  ++g_launches;
+  return ok();
+}
+
+int nncv_b200_upsample2x_nhwc(const void* in, void* out, int dtype, int N, int H, int W, int C, void* stream) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int rc = device_init();
+  if (rc) return rc;
+  if (!in || !out || N <= 0 || H <= 0 || W <= 0 || C <= 0 || dtype < 0 || dtype > 2) return fail(NNCV_B200_EINVAL, "upsample2x: bad argument");
+  if (launch_upsample2x(in, out, (DType)dtype, N, H, W, C, (cudaStream_t)stream) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(NNCV_B200_EINVAL, "upsample2x: C must be a multiple of %d", 16 / (int)dtype_size((DType)dtype));
+  }
+  ++g_launches;
+  return ok();
+}
+
 int nncv_b200_bn_fold(const void* gamma, const void* beta, const void* mean, const void* var,
                       int dtype, int C, float* scale, float* shift, void* stream) {
   std::lock_guard<std::mutex> lk(g_mutex);

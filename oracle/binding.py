@@ -48,6 +48,14 @@ def oracle() -> ctypes.CDLL:
         L.nncv_oracle_avgpool_global.restype = None
         L.nncv_oracle_matmul.argtypes = [_f32p, _f32p, _f32p, c_int, c_int, c_int, c_void_p, c_int, c_int]
         L.nncv_oracle_matmul.restype = None
+        L.nncv_oracle_depthwise_conv_nchw_chw.argtypes = [_f32p, _f32p, _f32p] + [c_int] * 9
+        L.nncv_oracle_depthwise_conv_nchw_chw.restype = None
+        L.nncv_oracle_activation.argtypes = [_f32p, c_size_t, c_int]
+        L.nncv_oracle_activation.restype = None
+        L.nncv_oracle_concat_channels.argtypes = [ctypes.POINTER(c_void_p), ctypes.POINTER(c_int), c_int, _f32p, c_int, c_long]
+        L.nncv_oracle_concat_channels.restype = None
+        L.nncv_oracle_upsample2x.argtypes = [_f32p, _f32p, c_int, c_int, c_int, c_int]
+        L.nncv_oracle_upsample2x.restype = None
         L.nncv_oracle_resnet_param_count.argtypes = [c_int]
         L.nncv_oracle_resnet_param_count.restype = c_size_t
         L.nncv_oracle_resnet_forward.argtypes = [c_int, _f32p, c_int, c_int, c_int, _f32p, c_size_t, _f32p, c_int]
@@ -114,6 +122,51 @@ def matmul(a, b, bias=None, relu=False, acc64=False) -> np.ndarray:
         bp = bias.ctypes.data
     oracle().nncv_oracle_matmul(a, b, c, m, n, k, bp, int(relu), int(acc64))
     return c
+
+
+ACT = {"none": 0, "relu": 1, "hard_sigmoid": 2, "hard_swish": 3, "sigmoid": 4, "silu": 5}
+
+
+def depthwise_conv2d(x, w, stride=1, pad=0, acc64=False) -> np.ndarray:
+    """x [N,C,H,W], w [C,R,S] (linalg.depthwise_conv_2d_nchw_chw)."""
+    x, w = _c(x), _c(w)
+    n, c, h, wd = x.shape
+    c2, r, s = w.shape
+    assert c == c2
+    oh, ow = (h + 2 * pad - r) // stride + 1, (wd + 2 * pad - s) // stride + 1
+    y = np.empty((n, c, oh, ow), np.float32)
+    oracle().nncv_oracle_depthwise_conv_nchw_chw(x, w, y, n, c, h, wd, r, s, stride, pad, int(acc64))
+    return y
+
+
+def activation(x, kind: str) -> np.ndarray:
+    y = _c(x).copy()
+    oracle().nncv_oracle_activation(y, y.size, ACT[kind])
+    return y
+
+
+def se_gate(pooled, w1, b1, w2, b2) -> np.ndarray:
+    """Squeeze-and-excitation gate from the pooled map: the two 1x1 convs on [N,C,1,1] of the fixture are matmuls."""
+    hid = matmul(pooled, np.ascontiguousarray(_c(w1).T), b1, relu=True)
+    return activation(matmul(hid, np.ascontiguousarray(_c(w2).T), b2), "hard_sigmoid")
+
+
+def concat_channels(xs) -> np.ndarray:
+    xs = [_c(x) for x in xs]
+    n, _, h, w = xs[0].shape
+    chans = (c_int * len(xs))(*[x.shape[1] for x in xs])
+    ptrs = (c_void_p * len(xs))(*[x.ctypes.data for x in xs])
+    y = np.empty((n, sum(x.shape[1] for x in xs), h, w), np.float32)
+    oracle().nncv_oracle_concat_channels(ptrs, chans, len(xs), y, n, h * w)
+    return y
+
+
+def upsample2x(x) -> np.ndarray:
+    x = _c(x)
+    n, c, h, w = x.shape
+    y = np.empty((n, c, 2 * h, 2 * w), np.float32)
+    oracle().nncv_oracle_upsample2x(x, y, n, c, h, w)
+    return y
 
 
 def resnet_forward(depth: int, x, blob, acc64=False) -> np.ndarray:

@@ -12,6 +12,8 @@
 //   * tests/Nets/Pool2DMax.mlir:3-9          max-pool with -inf initial value
 //   * tests/SplitParams/data.mlir:4-12       two chained convs (known-answer case)
 //   * tests/MatMulOptimization/MatMulDeafult.mlir:6-9   linalg.matmul
+//   * tests/Nets/MobileNetV3.mlir:301,345-383  depthwise conv, hard-sigmoid / hard-swish, squeeze-and-excitation
+//   * tests/Nets/Yolov5s.mlir:158-169,276,876-884  sigmoid / SiLU, channel concat, nearest 2x upsampling
 // The arithmetic of those ops lives in upstream MLIR/LLVM ("18git", not vendored in nncv and
 // not pinned), so the semantics followed here are the linalg named-op definitions as the
 // fixtures instantiate them; the accumulation order per output element is the one of nncv's
@@ -309,6 +311,83 @@ static Net build_net(int depth) {
   net.total = off;
   return net;
 }
+
+// linalg.depthwise_conv_2d_nchw_chw (MobileNetV3.mlir:301): y[n,c,oy,ox] = sum_{r,s} x[n,c,oy*st+r-p,ox*st+s-p] * w[c,r,s],
+// zero padding (the tensor.pad before it, :292-296), running sum over r then s.
+void nncv_oracle_depthwise_conv_nchw_chw(const float* x, const float* w, float* y, int N, int C, int H, int W, int R, int S,
+                                         int stride, int pad, int acc64) {
+  const int OH = (H + 2 * pad - R) / stride + 1, OW = (W + 2 * pad - S) / stride + 1;
+#pragma omp parallel for schedule(static)
+  for (long nc = 0; nc < (long)N * C; ++nc) {
+    const int c = (int)(nc % C);
+    const float* xi = x + (size_t)nc * H * W;
+    const float* wc = w + (size_t)c * R * S;
+    float* yo = y + (size_t)nc * OH * OW;
+    for (int oy = 0; oy < OH; ++oy)
+      for (int ox = 0; ox < OW; ++ox) {
+        float a32 = 0.0f;
+        double a64 = 0.0;
+        for (int r = 0; r < R; ++r) {
+          const int iy = oy * stride - pad + r;
+          for (int q = 0; q < S; ++q) {
+            const int ix = ox * stride - pad + q;
+            const float v = (iy < 0 || iy >= H || ix < 0 || ix >= W) ? 0.0f : xi[(size_t)iy * W + ix];
+            if (acc64) a64 += (double)v * (double)wc[r * S + q];
+            else a32 += v * wc[r * S + q];
+          }
+        }
+        yo[(size_t)oy * OW + ox] = acc64 ? (float)a64 : a32;
+      }
+  }
+}
+
+// Elementwise activations as the fixtures spell them.  kind: 1 ReLU (cmpf ugt, select), 2 hard-sigmoid
+// (MobileNetV3.mlir:345-377: addf 3, divf 6, `olt 1, t ? 1 : t`, `ogt 0, t ? 0 : t`), 3 hard-swish (x times it),
+// 4 sigmoid (Yolov5s.mlir:158-164: negf, exp, addf 1, divf 1 / .), 5 SiLU (:165-169: mulf sigmoid(x), x).
+void nncv_oracle_activation(float* x, size_t n, int kind) {
+  auto hsig = [](float v) {
+    float t = (v + 3.0f) / 6.0f;
+    t = (1.0f < t) ? 1.0f : t;
+    t = (0.0f > t) ? 0.0f : t;
+    return t;
+  };
+  auto sig = [](float v) { return 1.0f / (std::exp(-v) + 1.0f); };
+#pragma omp parallel for schedule(static)
+  for (long i = 0; i < (long)n; ++i) {
+    const float v = x[i];
+    switch (kind) {
+      case 1: x[i] = !(v <= 0.0f) ? v : 0.0f; break;
+      case 2: x[i] = hsig(v); break;
+      case 3: x[i] = v * hsig(v); break;
+      case 4: x[i] = sig(v); break;
+      case 5: x[i] = sig(v) * v; break;
+      default: break;
+    }
+  }
+}
+
+// tensor.concat dim(1) of NCHW tensors (Yolov5s.mlir:276).
+void nncv_oracle_concat_channels(const float* const* in, const int* channels, int n_in, float* y, int N, long HW) {
+  long Ct = 0;
+  for (int i = 0; i < n_in; ++i) Ct += channels[i];
+  for (int n = 0; n < N; ++n) {
+    long off = 0;
+    for (int i = 0; i < n_in; ++i) {
+      std::copy(in[i] + (size_t)n * channels[i] * HW, in[i] + (size_t)(n + 1) * channels[i] * HW, y + ((size_t)n * Ct + off) * HW);
+      off += channels[i];
+    }
+  }
+}
+
+// Nearest 2x upsampling (Yolov5s.mlir:876-884): y[n,c,i,j] = x[n,c,i floordiv 2,j floordiv 2].
+void nncv_oracle_upsample2x(const float* x, float* y, int N, int C, int H, int W) {
+#pragma omp parallel for schedule(static)
+  for (long nc = 0; nc < (long)N * C; ++nc)
+    for (int i = 0; i < 2 * H; ++i)
+      for (int j = 0; j < 2 * W; ++j)
+        y[((size_t)nc * 2 * H + i) * 2 * W + j] = x[((size_t)nc * H + i / 2) * W + j / 2];
+}
+
 
 size_t nncv_oracle_resnet_param_count(int depth) {
   if (depth != 18 && depth != 50) return 0;

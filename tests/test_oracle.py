@@ -131,3 +131,41 @@ def test_mac_counts():
     assert len(conv_groups(18)) == 20 and len(conv_groups(50)) == 53
     assert ob.oracle().nncv_oracle_resnet_param_count(18) == sum(int(np.prod(s)) for _, s in tensor_order(18))
     assert ob.oracle().nncv_oracle_resnet_param_count(50) == sum(int(np.prod(s)) for _, s in tensor_order(50))
+
+
+# ---- operators of the mobile / detection fixtures (MobileNetV3.mlir, Yolov5s.mlir) ------------
+@pytest.mark.parametrize("stride,pad,k", [(1, 1, 3), (2, 1, 3), (2, 2, 5), (1, 0, 1)])
+def test_depthwise_conv_matches_torch(stride, pad, k):
+    g = np.random.default_rng(k * 10 + stride)
+    x = g.standard_normal((2, 24, 13, 17)).astype(np.float32)
+    w = g.standard_normal((24, k, k)).astype(np.float32)
+    ref = F.conv2d(torch.from_numpy(x), torch.from_numpy(w)[:, None], stride=stride, padding=pad, groups=24).numpy()
+    assert rel(ob.depthwise_conv2d(x, w, stride, pad), ref) < 2e-6
+    assert rel(ob.depthwise_conv2d(x, w, stride, pad, acc64=True), ref) < 2e-6
+
+
+def test_activations_match_torch_and_pass_nan():
+    x = np.random.default_rng(3).standard_normal(4096).astype(np.float32) * 4
+    t = torch.from_numpy(x)
+    for kind, fn in (("hard_sigmoid", F.hardsigmoid), ("hard_swish", F.hardswish), ("sigmoid", torch.sigmoid), ("silu", F.silu),
+                     ("relu", F.relu)):
+        assert np.abs(ob.activation(x, kind) - fn(t).numpy()).max() < 2e-6, kind
+    edge = np.array([-3.0, 3.0, -7.0, 9.0, np.nan], np.float32)
+    hs = ob.activation(edge, "hard_sigmoid")
+    assert hs[0] == 0 and hs[1] == 1 and hs[2] == 0 and hs[3] == 1 and np.isnan(hs[4])   # olt/ogt selects keep a NaN
+    assert np.isnan(ob.activation(edge, "silu")[4])
+
+
+def test_se_gate_concat_upsample_match_torch():
+    g = np.random.default_rng(4)
+    p = g.standard_normal((3, 16)).astype(np.float32)
+    w1, b1 = g.standard_normal((8, 16)).astype(np.float32), g.standard_normal(8).astype(np.float32)
+    w2, b2 = g.standard_normal((16, 8)).astype(np.float32), g.standard_normal(16).astype(np.float32)
+    tp = torch.from_numpy(p)
+    ref = F.hardsigmoid(F.linear(F.relu(F.linear(tp, torch.from_numpy(w1), torch.from_numpy(b1))), torch.from_numpy(w2),
+                                 torch.from_numpy(b2))).numpy()
+    assert np.abs(ob.se_gate(p, w1, b1, w2, b2) - ref).max() < 1e-5
+    x = g.standard_normal((2, 8, 5, 7)).astype(np.float32)
+    y = g.standard_normal((2, 16, 5, 7)).astype(np.float32)
+    assert np.array_equal(ob.concat_channels([x, y, x]), np.concatenate([x, y, x], 1))
+    assert np.array_equal(ob.upsample2x(x), F.interpolate(torch.from_numpy(x), scale_factor=2, mode="nearest").numpy())
