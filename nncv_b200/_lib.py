@@ -70,7 +70,7 @@ def lib() -> ctypes.CDLL:
     L.nncv_b200_device_status.restype = c_int
     L.nncv_b200_arena_plan.argtypes = [c_size_t, POINTER(c_int), POINTER(c_int), POINTER(c_size_t), c_size_t,
                                        POINTER(c_size_t), POINTER(c_size_t)]
-    L.nncv_b200_depthwise_conv_nhwc.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 11 + [c_void_p]
+    L.nncv_b200_depthwise_conv_nhwc.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 10 + [c_void_p]
     L.nncv_b200_activation.argtypes = [c_void_p, c_void_p, c_int, c_size_t, c_int, c_void_p]
     L.nncv_b200_se_gate.argtypes = [c_void_p] * 6 + [c_int] * 4 + [c_void_p]
     L.nncv_b200_scale_channels_nhwc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]

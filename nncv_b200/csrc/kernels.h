@@ -110,6 +110,10 @@ struct TconvArgs {
   Layout in_l{0, 0, 0}, out_l{0, 0, 0};
   int bn = 64, resident = 0;
   int pair = 0;                    // CTA pairs (tcgen05.mma.cta_group::2): weights packed for N tile bn / 2
+  // plain GEMM with B as it lies in memory: row-major [b_rows = C, Kout] 16-bit, read by TMA as an
+  // MN-major operand; wpack is then unused.  C and Kout multiples of 8.
+  const void* b_rowmajor = nullptr;
+  int b_rows = 0;
   DType ab = kF16, out_dtype = kF16;
   int relu = 0;
   int sm_count = 0;

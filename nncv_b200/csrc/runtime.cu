@@ -2011,6 +2011,22 @@ int nncv_b200_matmul(const void* A, const void* B, void* C, int M, int N, int K,
   if (ab_dtype != NNCV_B200_F16 && ab_dtype != NNCV_B200_BF16) return fail(NNCV_B200_EINVAL, "matmul: bad ab_dtype");
   if (c_dtype != NNCV_B200_F32 && c_dtype != ab_dtype) return fail(NNCV_B200_EINVAL, "matmul: c_dtype must be F32 or ab_dtype");
   if (K % 8 != 0) return fail(NNCV_B200_EINVAL, "matmul: the tcgen05 path needs K %% 8 == 0");
+  if (N % 8 == 0 && N >= 64 && K >= 64 && !g_force_gather && !(reinterpret_cast<uintptr_t>(B) & 15) && !(reinterpret_cast<uintptr_t>(A) & 15) &&
+      !(reinterpret_cast<uintptr_t>(C) & 15)) {
+    // B as it lies in memory: 64 x 64 boxes of the row-major [K, N] matrix are MN-major operand tiles,
+    // so the whole matmul is one kernel and needs no scratch
+    int bn = N >= 256 ? 256 : (N > 64 ? 128 : 64);
+    const long long mi = ((long long)M + 127) / 128;
+    while (bn > 64 && mi * ((N + bn - 1) / bn) < g_dev.sm_count) bn >>= 1;
+    TconvArgs a;
+    a.in = A; a.b_rowmajor = B; a.b_rows = K; a.shift = bias; a.out = C;
+    a.N = 1; a.H = 1; a.W = M; a.OH = 1; a.OW = M; a.C = K; a.Kout = N;
+    a.in_l = Layout{1, M, 0}; a.out_l = Layout{1, M, 0};
+    a.bn = bn; a.resident = 0; a.ab = (DType)ab_dtype; a.out_dtype = (DType)c_dtype; a.relu = relu;
+    a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
+    LAUNCH(launch_tconv(a, st));
+    return ok();
+  }
   if (K % 64 == 0 && tconv_supported(K, N, (DType)c_dtype, N) && N >= 64) {
     int bn, resident;
     tconv_pick((M + 127) / 128, K, N, 1, &bn, &resident);

@@ -74,11 +74,16 @@ struct TcParams {
 // issues MMAs that read both CTAs' shared memory, each CTA drains its own accumulator rows.  The
 // streamed kernel is bound by the L2->SM path (one A tile and one weight tile per 128 x BN x 64
 // block); halving the weight bytes per CTA is the point.  Barrier protocol as in conv3x3_pair.cu.
-template <int BN, bool RESIDENT, bool DUAL, bool PAIR>
+// BROW: the B operand is a plain row-major [K, N] matrix (linalg.matmul's right-hand side as it lies in
+// memory): 64 x 64 boxes of it land by TMA as MN-major 128-byte-swizzled tiles -- k rows of 128 bytes,
+// 8-row groups 1024 bytes apart, one box per 64 columns 8192 bytes apart -- and the instruction
+// descriptor marks B as MN-major, so nothing is repacked; rows and columns past the matrix read as zero.
+template <int BN, bool RESIDENT, bool DUAL, bool PAIR, bool BROW>
 __global__ void __launch_bounds__(kThreads, 1)
 tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_out,
-             const __grid_constant__ CUtensorMap tm_out2, const TcParams p) {
+             const __grid_constant__ CUtensorMap tm_out2, const __grid_constant__ CUtensorMap tm_b, const TcParams p) {
   static_assert(!PAIR || !RESIDENT, "the pair kernel streams its weights");
+  static_assert(!BROW || (!RESIDENT && !DUAL && !PAIR), "a row-major B is streamed by one CTA");
   constexpr int WTILE = (PAIR ? BN / 2 : BN) * 128;   // this CTA's part of a weight tile
   constexpr int ACC_W = DUAL ? 2 * BN : BN;   // columns of one accumulator buffer
   constexpr int ACC_COLS = 2 * ACC_W;         // two accumulator buffers
@@ -125,6 +130,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
     ptx::prefetch_tensormap(&tm_in);
     ptx::prefetch_tensormap(&tm_out);
     if (DUAL) ptx::prefetch_tensormap(&tm_out2);
+    if (BROW) ptx::prefetch_tensormap(&tm_b);
   }
   if (warp == 1) {
     if (PAIR) {
@@ -206,7 +212,11 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
             ptx::mbar_arrive_expect_tx(full + 8 * st, (uint32_t)stage_bytes);
             const uint32_t dst = sRing + st * stage_bytes;
             ptx::tma_load_4d(dst, &tm_in, cb * 64, xb + s, yb + r, n0, full + 8 * st);
-            if (!RESIDENT) {
+            if (BROW) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                ptx::tma_load_2d(dst + kABytes + (uint32_t)j * 8192u, &tm_b, n_tile * BN + j * 64, cb * 64, full + 8 * st);
+            } else if (!RESIDENT) {
               // pair: the weights are packed for N tile BN/2; this CTA takes tile 2 * n_tile + rank
               const int wt = PAIR ? 2 * n_tile + (int)rank : n_tile;
               const uint8_t* wsrc = (DUAL && tap == p.taps) ? p.wpack2 + ((size_t)wt * p.CB + cb) * WTILE
@@ -241,7 +251,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
     } else
     // ------------------------------------------------------------------ MMA issuer ------
     if (lane == 0) {
-      const uint32_t idesc = ptx::umma_idesc(PAIR ? 256 : 128, BN, p.bf16 ? 1 : 0);
+      const uint32_t idesc = ptx::umma_idesc(PAIR ? 256 : 128, BN, p.bf16 ? 1 : 0) | (BROW ? (1u << 16) : 0u);   // bit 16: B is MN-major
       const uint32_t peer_empty = PAIR ? ptx::map_to_cta(empty, 1) : 0u, peer_acc_full = PAIR ? ptx::map_to_cta(acc_full, 1) : 0u;
       bool okw = true;
       if (RESIDENT) okw = ptx::mbar_wait_abortable(w_full, 0, abort_flag);
@@ -266,8 +276,11 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
           ptx::tc_fence_after();
           const uint32_t a_addr = sRing + st * stage_bytes;
           const uint32_t a_lo = ptx::smem_desc_k128_lo(a_addr);
-          const uint32_t b_lo = ptx::smem_desc_k128_lo(
+          // MN-major B: leading-dimension offset 8192 bytes (next 64 columns), one k step of 16 = two 8-row groups
+          const uint32_t b_lo = BROW ? ((((a_addr + kABytes) & 0x3FFFFu) >> 4) | ((8192u >> 4) << 16))
+                                     : ptx::smem_desc_k128_lo(
               RESIDENT ? sW + (uint32_t)(second ? KB + cb : tap * p.CB + cb) * WTILE : a_addr + kABytes);
+          constexpr uint32_t kBStep = BROW ? (2048u >> 4) : 2u;
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             if (PAIR)
@@ -276,7 +289,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
                                  (second ? (cb | k4) : (cb | tap | k4)) != 0 ? 1u : 0u);
             else
               ptx::umma_f16(second ? d + BN : d, ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi),
-                            ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi), idesc,
+                            ptx::desc_from_halves(b_lo + k4 * kBStep, ptx::kSmemDescK128Hi), idesc,
                             (second ? (cb | k4) : (cb | tap | k4)) != 0 ? 1u : 0u);
           }
           if (PAIR) {
@@ -491,7 +504,19 @@ bool make_map4(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esz,
 
 constexpr size_t kSmemLimit = 227 * 1024;
 
-template <int BN, bool RESIDENT, bool DUAL = false, bool PAIR = false>
+// 2-D map over a row-major [K, N] 16-bit matrix, box 64 columns x 64 rows, 128-byte swizzle, zero fill.
+bool make_map_b(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, long long K, long long N) {
+  auto enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t gdim[2] = {(cuuint64_t)N, (cuuint64_t)K};
+  cuuint64_t gstr[1] = {(cuuint64_t)N * 2};
+  cuuint32_t box[2] = {64, 64};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(m, dt, 2, const_cast<void*>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool RESIDENT, bool DUAL = false, bool PAIR = false, bool BROW = false>
 cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
   const size_t wtile = (size_t)(PAIR ? BN / 2 : BN) * 128;
   const int KB = p.taps * p.CB;
@@ -517,7 +542,9 @@ cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
   CUtensorMap tm_out2 = tm_out;
   if (DUAL && !make_map4(&tm_out2, a.out2, dt, 2, a.Kout, ol.pitch, ol.img_rows, a.N, 64, p.tw, p.th, p.tn, 1, 1))
     return cudaErrorInvalidValue;
-  auto kern = tconv_kernel<BN, RESIDENT, DUAL, PAIR>;
+  CUtensorMap tm_b = tm_out;
+  if (BROW && !make_map_b(&tm_b, a.b_rowmajor, dt, a.b_rows, a.Kout)) return cudaErrorInvalidValue;
+  auto kern = tconv_kernel<BN, RESIDENT, DUAL, PAIR, BROW>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int sms = a.sm_count > 0 ? a.sm_count : 148;
@@ -545,12 +572,12 @@ cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    return cudaLaunchKernelEx(&cfg, kern, tm_in, tm_out, tm_out2, p);
+    return cudaLaunchKernelEx(&cfg, kern, tm_in, tm_out, tm_out2, tm_b, p);
   } else {
     const long long items = (long long)p.m_items * p.n_tiles;
     grid = dim3((unsigned)(items < sms ? items : sms), 1);
   }
-  return launch_pdl(kern, grid, dim3(kThreads), smem, stream, tm_in, tm_out, tm_out2, p);
+  return launch_pdl(kern, grid, dim3(kThreads), smem, stream, tm_in, tm_out, tm_out2, tm_b, p);
 }
 
 }  // namespace
@@ -588,16 +615,23 @@ void tconv_tile(int N, int OH, int OW, int* tw, int* th, int* tn) {
 }
 
 cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream) {
-  if (a.ab == kF32 || !tconv_supported(a.C, a.Kout, a.out_dtype, a.Kout)) return cudaErrorInvalidValue;
+  const bool brow = a.b_rowmajor != nullptr;
+  if (brow) {   // plain GEMM with a row-major B: K and N multiples of 8 (16-byte row pitches), nothing else
+    if (a.ab == kF32 || a.C % 8 != 0 || a.Kout % 8 != 0 || a.R != 1 || a.S != 1 || a.stride != 1 || a.pad != 0 || a.wpack2 ||
+        a.pair || a.resident || a.b_rows != a.C || (reinterpret_cast<uintptr_t>(a.b_rowmajor) & 15))
+      return cudaErrorInvalidValue;
+  } else if (a.ab == kF32 || !tconv_supported(a.C, a.Kout, a.out_dtype, a.Kout)) {
+    return cudaErrorInvalidValue;
+  }
   if ((reinterpret_cast<uintptr_t>(a.in) & 15) || (reinterpret_cast<uintptr_t>(a.out) & 15) ||
-      (reinterpret_cast<uintptr_t>(a.residual) & 31) || (reinterpret_cast<uintptr_t>(a.wpack) & 15))
+      (reinterpret_cast<uintptr_t>(a.residual) & 31) || (!brow && (reinterpret_cast<uintptr_t>(a.wpack) & 15)))
     return cudaErrorMisalignedAddress;
   TcParams p;
   p.wpack = static_cast<const uint8_t*>(a.wpack);
   p.scale = a.scale; p.shift = a.shift; p.residual = static_cast<const uint8_t*>(a.residual);
   p.wpack2 = static_cast<const uint8_t*>(a.wpack2); p.scale2 = a.scale2; p.shift2 = a.shift2;
   p.error_flag = a.error_flag;
-  p.Kout = a.Kout; p.CB = a.C / 64; p.taps = a.R * a.S; p.S = a.S; p.stride = a.stride; p.pad = a.pad;
+  p.Kout = a.Kout; p.CB = (a.C + 63) / 64; p.taps = a.R * a.S; p.S = a.S; p.stride = a.stride; p.pad = a.pad;
   p.in_off = a.in_l.off; p.out_off = a.out_l.off;
   p.OH = a.OH; p.OW = a.OW; p.NB = a.N;
   p.out_pitch = a.out_l.pitch; p.out_rows = a.out_l.img_rows;
@@ -613,6 +647,12 @@ cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream) {
   p.relu = a.relu; p.bf16 = a.ab == kBF16; p.out_f32 = a.out_dtype == kF32;
   p.stages = 0;
   if (p.residual && p.out_f32) return cudaErrorInvalidValue;
+  if (brow) {
+    if (a.bn == 64) return launch_cfg<64, false, false, false, true>(a, p, stream);
+    if (a.bn == 128) return launch_cfg<128, false, false, false, true>(a, p, stream);
+    if (a.bn == 256) return launch_cfg<256, false, false, false, true>(a, p, stream);
+    return cudaErrorInvalidConfiguration;
+  }
   if (a.pair) {     // CTA pairs: a.wpack (and a.wpack2) packed for N tile bn / 2, streamed weights, 16-bit output
     if (a.resident || p.out_f32 || (a.bn != 128 && a.bn != 256) || a.Kout % a.bn != 0) return cudaErrorInvalidValue;
     if (a.wpack2) {

@@ -62,7 +62,7 @@ def gemm():
             print(json.dumps({"sweep": "gemm", "M=N=K": n, "ab": "f16" if ab == F16 else "f32",
                               "c": "f16" if cdt == F16 else "f32", "bias_relu": epi, "ms": round(ms, 4),
                               "tflops": round(tf, 1), "frac_of_peak": round(tf / PEAK_TF, 3),
-                              "note": "includes repacking B[K,N] into K-major tiles"}), flush=True)
+                              "note": "one kernel: B read by TMA as it lies (row-major = MN-major operand)"}), flush=True)
 
 
 def conv(n=32):
