@@ -195,6 +195,11 @@ cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean
 cudaError_t launch_convert(const void* src, DType src_dt, void* dst, DType dst_dt, size_t n,
                            cudaStream_t stream);
 
+// ---- fp32 GEMM on tcgen05 with three tf32 products per k step (fp32-level accuracy) ---------------
+bool gemm_tf32x3_supported(int M, int N, int K);
+cudaError_t launch_gemm_tf32x3(const float* A, const float* B, float* C, int M, int N, int K, const float* bias, int relu,
+                               int sm_count, int* error_flag, cudaStream_t stream);
+
 // ---- memory-bound operators of the mobile / detection fixtures (NHWC, 16-byte accesses) --------
 enum Activation : int { kActNone = 0, kActRelu = 1, kActHardSigmoid = 2, kActHardSwish = 3, kActSigmoid = 4, kActSilu = 5 };
 // depthwise conv, weights [C][R*S] (fp32, or fp16 with fp16 activations), folded batch-norm, activation

@@ -2000,6 +2000,12 @@ int nncv_b200_matmul(const void* A, const void* B, void* C, int M, int N, int K,
   cudaStream_t st = (cudaStream_t)stream;
   if (ab_dtype == NNCV_B200_F32) {
     if (c_dtype != NNCV_B200_F32 || K % 4 != 0) return fail(NNCV_B200_EINVAL, "fp32 matmul needs fp32 C and K %% 4 == 0");
+    if (!g_force_gather && gemm_tf32x3_supported(M, N, K) && !(reinterpret_cast<uintptr_t>(A) & 15) &&
+        !(reinterpret_cast<uintptr_t>(B) & 15) && !(reinterpret_cast<uintptr_t>(C) & 15)) {
+      // tensor cores, three tf32 products per k step: fp32-level accuracy, no scratch
+      LAUNCH(launch_gemm_tf32x3((const float*)A, (const float*)B, (float*)C, M, N, K, bias, relu, g_dev.sm_count, g_dev.error_flag, st));
+      return ok();
+    }
     if ((rc = ensure_scratch((size_t)N * K * sizeof(float)))) return rc;
     LAUNCH(launch_repack_weights_f32(B, kF32, 1, N, 0, N, K, K, 1, (float*)g_dev.scratch, st));
     SimtConvArgs a;
