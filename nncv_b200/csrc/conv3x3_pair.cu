@@ -66,6 +66,9 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
   constexpr int kWStage = kWGroup * kWTile;
   constexpr int kPackBN = BNP / 2 < 64 ? 64 : BNP / 2;   // N tile of the packed weights
   constexpr int kPackTile = kPackBN * 128;
+  // accumulator buffers in TMEM: two when they fit, else one (the MMAs of the next item then wait for the epilogue)
+  constexpr uint32_t kAB = (2 * BNP * MT <= 512) ? 2u : 1u;
+  constexpr uint32_t kAccCols = kAB * BNP * MT;
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_abort;
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -111,7 +114,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
     ptx::prefetch_tensormap(&tm_out);
   }
   if (warp == 1) {
-    ptx::tmem_alloc_pair(tmem_slot, (uint32_t)(2 * BNP * MT));
+    ptx::tmem_alloc_pair(tmem_slot, kAccCols);
     ptx::tmem_relinquish_pair();
   }
   ptx::tc_fence_before();
@@ -201,8 +204,8 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
         int m_item, n_tile, sub, parts;
         if (!item_of(i, m_item, n_tile, sub, parts)) break;
         const uint32_t idesc = parts == 1 ? idesc_full : ptx::umma_idesc(256, kBNPair / parts, p.bf16 ? 1 : 0);
-        const uint32_t ab = acc_cnt & 1u;
-        if (!ptx::mbar_wait_cluster_abortable(acc_empty + 8 * ab, ((acc_cnt >> 1) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
+        const uint32_t ab = acc_cnt % kAB;
+        if (!ptx::mbar_wait_cluster_abortable(acc_empty + 8 * ab, ((acc_cnt / kAB) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
         ptx::tc_fence_after();
         const uint32_t d = tmem_base + ab * (uint32_t)(kBNPair * MT);
         for (int cb = 0; cb < p.CB && okw; ++cb) {
@@ -281,7 +284,7 @@ conv3x3_pair_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_cons
   ptx::cluster_sync_all();   // the peer's shared memory and barriers stay valid until both are done
   if (warp == 1) {
     __syncwarp();
-    ptx::tmem_dealloc_pair(tmem_base, (uint32_t)(2 * BNP * MT));
+    ptx::tmem_dealloc_pair(tmem_base, kAccCols);
   }
 }
 

@@ -7,9 +7,9 @@
 // (src/nncv/compiler/Conversion/MatMulOptimize/MatMul2NvMMA.cpp:37-90).
 //
 // A tf32 operand keeps 10 mantissa bits, so one product is good to about 1e-3.  Every operand x is
-// split into hi = x with its low 13 bits cleared (exactly a tf32 value) and lo = x - hi (exact in
-// fp32, then cut to tf32 as well); A*B ~= Ahi*Bhi + Ahi*Blo + Alo*Bhi with fp32 accumulation in TMEM,
-// the dropped Alo*Blo term being about 2^-22 of the product.
+// split into hi = x rounded to the nearest tf32 value and lo = x - hi (exact in fp32, then rounded
+// to tf32 as well); A*B ~= Ahi*Bhi + Ahi*Blo + Alo*Bhi with fp32 accumulation in TMEM, the dropped
+// Alo*Blo term being about 2^-24 of the product.
 // Data path: kind::tf32 takes K-major operands only (an MN-major B, which the 16-bit kinds accept,
 // gives wrong products -- measured), so the row-major B[K,N] is transposed on the way in.  TMA lands
 // 128 x 32 fp32 tiles of A with the 128-byte swizzle; two groups of four converter warps take
@@ -42,6 +42,12 @@ constexpr int kTile = 128 * 128;           // bytes of one operand tile: 128 row
 constexpr int kStageBytes = 4 * kTile;     // A, A_lo, B, B_lo
 constexpr int kStages = 3;
 constexpr int kSlabBytes = 128 * 128;      // 128 rows x 32 fp32
+
+// Nearest tf32 value (10 mantissa bits; ties away from zero): rounding, unlike cutting the low bits,
+// leaves no error of one sign to pile up over a long k loop (cutting gave rel-L2 1.5e-5 at K = 2048).
+__device__ __forceinline__ float tf32_round(float x) {
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+}
 
 struct GtParams {
   const float* bias;
@@ -89,7 +95,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
     ptx::prefetch_tensormap(&tm_c);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, 2 * kBN);
+    ptx::tmem_alloc(tmem_slot, 4 * kBN);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
@@ -139,7 +145,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
         const uint32_t ab = acc_cnt & 1u;
         if (!ptx::mbar_wait_abortable(acc_empty + 8 * ab, ((acc_cnt >> 1) & 1u) ^ 1u, abort_flag)) { okw = false; break; }
         ptx::tc_fence_after();
-        const uint32_t d = tmem_base + ab * kBN;
+        // two accumulators per buffer: the hi*hi products, and the two small cross terms.  The tensor core
+        // cuts (does not round) every accumulation into TMEM, an error of one sign per step: keeping the
+        // large sum to one step per k block of 8 instead of three makes it three times smaller
+        const uint32_t d = tmem_base + ab * (2 * kBN), dl = d + kBN;
         for (int kb = 0; kb < p.k_blocks; ++kb, ++cnt) {
           const uint32_t st = cnt % kStages;
           if (!ptx::mbar_wait_abortable(conv + 8 * st, (cnt / kStages) & 1u, abort_flag)) { okw = false; break; }
@@ -153,9 +162,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
             const uint64_t al = ptx::desc_from_halves(a_lo + k4 * 2, ptx::kSmemDescK128Hi);
             const uint64_t bh = ptx::desc_from_halves(b_hi + k4 * 2, ptx::kSmemDescK128Hi);
             const uint64_t bl = ptx::desc_from_halves(b_lo + k4 * 2, ptx::kSmemDescK128Hi);
-            ptx::umma_tf32(d, al, bh, idesc, (kb | (int)k4) != 0 ? 1u : 0u);   // small terms first
-            ptx::umma_tf32(d, ah, bl, idesc, 1u);
-            ptx::umma_tf32(d, ah, bh, idesc, 1u);
+            ptx::umma_tf32(dl, al, bh, idesc, (kb | (int)k4) != 0 ? 1u : 0u);
+            ptx::umma_tf32(dl, ah, bl, idesc, 1u);
+            ptx::umma_tf32(d, ah, bh, idesc, (kb | (int)k4) != 0 ? 1u : 0u);
           }
           ptx::tc_commit(empty + 8 * st);
         }
@@ -198,8 +207,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
           const float in[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            hi[e] = __uint_as_float(__float_as_uint(in[e]) & 0xFFFFE000u);
-            lo[e] = __uint_as_float(__float_as_uint(in[e] - hi[e]) & 0xFFFFE000u);
+            hi[e] = tf32_round(in[e]);
+            lo[e] = tf32_round(in[e] - hi[e]);
           }
           asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(src), "f"(hi[0]), "f"(hi[1]), "f"(hi[2]), "f"(hi[3]) : "memory");
           asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(src + kTile), "f"(lo[0]), "f"(lo[1]), "f"(lo[2]), "f"(lo[3]) : "memory");
@@ -211,8 +220,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
           float hi[4], lo[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            hi[e] = __uint_as_float(__float_as_uint(bv[4 * j + e]) & 0xFFFFE000u);
-            lo[e] = __uint_as_float(__float_as_uint(bv[4 * j + e] - hi[e]) & 0xFFFFE000u);
+            hi[e] = tf32_round(bv[4 * j + e]);
+            lo[e] = tf32_round(bv[4 * j + e] - hi[e]);
           }
           const uint32_t dst = brow + (((uint32_t)j ^ swz) << 4);
           asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "f"(hi[0]), "f"(hi[1]), "f"(hi[2]), "f"(hi[3]) : "memory");
@@ -242,9 +251,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
       for (int sl = 0; sl < kBN / 32; ++sl, ++jglob) {
         const uint32_t sb = (uint32_t)jglob & 1u;
         const int ncol = n0 + sl * 32;
-        uint32_t acc[32];
+        uint32_t acc[32], accl[32];
         __syncwarp();
-        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + ab * kBN + (uint32_t)(sl * 32), acc);
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + ab * (2 * kBN) + (uint32_t)(sl * 32), acc);
+        ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + ab * (2 * kBN) + kBN + (uint32_t)(sl * 32), accl);
         ptx::tmem_ld_wait();
         if (sl == kBN / 32 - 1) {
           ptx::tc_fence_before();
@@ -257,7 +267,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
             const int n = ncol + c4 * 4 + h;
-            float a = __uint_as_float(acc[c4 * 4 + h]);
+            float a = __uint_as_float(acc[c4 * 4 + h]) + __uint_as_float(accl[c4 * 4 + h]);
             if (p.bias && n < p.N) a += __ldg(p.bias + n);
             o[h] = p.relu ? (!(a <= 0.0f) ? a : 0.0f) : a;
           }
@@ -284,7 +294,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_consta
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    ptx::tmem_dealloc(tmem_base, 2 * kBN);
+    ptx::tmem_dealloc(tmem_base, 4 * kBN);
   }
 }
 

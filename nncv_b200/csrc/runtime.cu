@@ -528,7 +528,7 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
           for (int bn : {64, 128, 256})
             if (c->Kout % bn == 0) {   // CTA pairs: sub-tiles per item, without and with the sliced last round
               for (int mt : {1, 2, 4}) {
-                if (2 * bn * mt > 512) continue;
+                if (bn * mt > 512) continue;   // beyond 256 columns the accumulator is single-buffered
                 cand.push_back(ConvChoice{7, bn, mt, 0});
                 if (bn >= 128) cand.push_back(ConvChoice{7, bn, mt, 1});
               }

@@ -59,6 +59,18 @@ def test_no_gpu_means_loud_failure_not_cpu_fallback():
                                1, 8, 8, None)
     assert rc == 3
     assert L.nncv_b200_stem_variant(-1) == 0   # no stem launch has happened
+    # the operators added for the mobile / detection fixtures, the status query and the wait self-test
+    assert L.nncv_b200_depthwise_conv_nhwc(a.ctypes.data, a.ctypes.data, _lib.F32, None, None, a.ctypes.data, _lib.F16, 1, 8, 8, 8,
+                                           3, 3, 1, 1, 0, None) == 3
+    assert L.nncv_b200_activation(a.ctypes.data, a.ctypes.data, _lib.F16, 64, 1, None) == 3
+    assert L.nncv_b200_upsample2x_nhwc(a.ctypes.data, a.ctypes.data, _lib.F16, 1, 2, 2, 8, None) == 3
+    assert L.nncv_b200_device_status() == 3
+    assert L.nncv_b200_selftest_wait_timeout(10, None) == 3
+    # a plan loads nothing without a device either, but it is still parsed and checked on the host
+    assert L.nncv_b200_plan_check(b"resnet18", None, None, None) == 0
+    with pytest.raises(_lib.NncvError) as e2:
+        rt.load_blob("plan:nncv_b200_plan 1\nparams 10 out 2\n", np.zeros(10, np.float32))
+    assert e2.value.code == 1
 
 
 def test_missing_library_raises(monkeypatch):

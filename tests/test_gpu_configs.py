@@ -60,8 +60,10 @@ def test_config1_gemm_at_stated_sizes(size, ab, epilogue):
     rows = _sample_rows(m, size)
     ref = ob.matmul(ar[rows], br, bias, epilogue, acc64=True)
     assert rows.size * n >= 4096 and np.isfinite(c).all()
-    # same (rounded) operands on both sides: only the order of the fp32 sums differs
-    assert G.rel_l2(c[rows], ref) <= 1e-5
+    # same (rounded) operands on both sides: only the fp32 summation differs.  The tensor cores cut (not
+    # round) each accumulation into TMEM, a one-signed error of about 2^-25 per accumulation step: 256
+    # steps at K = 4096 for 16-bit operands (k step 16), 512 for fp32 (k step 8) -- hence 2e-5 there
+    assert G.rel_l2(c[rows], ref) <= (1e-5 if ab != F32 else 2e-5)
     if epilogue:
         assert (c >= 0).all()
     # every tile of C is covered by a cheap identity as well: C @ 1 = A @ (B @ 1) (linearity)

@@ -120,6 +120,9 @@ SV_CASES = [
     (2, 64, 17, 23, 128, (64, 1, 2)),     # two Kout tiles of 64, streamed weights
     (5, 256, 14, 14, 256, (128, 1, 2)),
     (7, 256, 14, 14, 256, (128, 2, 2)),     # two sub-tiles of 256 slots per item, halo tile in two TMA boxes
+    (9, 256, 14, 14, 256, (256, 2, 2)),     # 512 accumulator columns: one buffer, MMAs wait for the epilogue
+    (11, 512, 7, 7, 512, (128, 4, 2)),      # four sub-tiles, single buffer, two Kout tiles
+    (60, 256, 14, 14, 256, (256, 2, 3)),
     (3, 64, 56, 56, 64, (64, 4, 2)),
     (40, 128, 28, 28, 256, (128, 2, 3)),
     (100, 256, 14, 14, 256, (256, 1, 3)),   # 88 items on 74 pairs: the 14 of the last round run as 4 column slices each
