@@ -41,7 +41,6 @@ import numpy as np  # noqa: E402
 METRIC = "resnet18_fp16_images_per_s"
 UNIT = "images/s"
 H = W = 224
-SUSTAIN_STEPS = 300   # extra timed steps after the K the caller asked for; depends on nothing but this constant
 
 
 def peaks():
@@ -239,7 +238,7 @@ def secondary_configs(torch, rt, flush, sampler, tf_peak):
     L = lib()
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     P = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None
-    out = {"gemm": [], "conv3x3_n32": [], "nets": []}
+    out = {"gemm": [], "conv3x3_n32": [], "nets": [], "hbm_ops": []}
 
     def entry(ms, reps, flops, i0, **kw):
         tf = flops / ms / 1e9
@@ -290,6 +289,14 @@ def secondary_configs(torch, rt, flush, sampler, tf_peak):
                                             note="fp16, fused scale/shift + ReLU; the conv launch alone"))
         finally:
             L.nncv_b200_conv_destroy(h)
+    try:
+        from nncv_b200 import sweeps
+        import contextlib
+        import io
+        with contextlib.redirect_stdout(io.StringIO()):     # the sweep prints its own lines; this run prints one
+            out["hbm_ops"] = sweeps.hbm_ops()
+    except Exception as ex:
+        out["hbm_ops"] = [{"error": str(ex)[:200]}]
     s = torch.cuda.current_stream().cuda_stream
     for depth, dt, n, hw, name in ((18, F32, 1, 256, "ResNet-18 fp32 N=1 @256 (config 0)"),
                                    (50, F16, 512, 224, "ResNet-50 fp16 N=512 @224 (config 4)")):
@@ -413,13 +420,13 @@ def run_ours(args):
         ms_fwd = sum(a.elapsed_time(m) for (a, _), m in zip(evs, mids)) if world > 1 else ms_dev
         barrier()
         # The K timed steps last a few tens of milliseconds, shorter than a few sampling periods of
-        # nvidia-smi: the same step, timed the same way, runs SUSTAIN_STEPS more times so that the clock
+        # nvidia-smi: the same step, timed the same way, runs args.sustain more times so that the clock
         # record covers a timed region of about half a second.  The count is a constant: every rank
         # runs the same number of steps (they contain a collective).
         mids.clear()
-        evs_s = timed(step_device, SUSTAIN_STEPS)
+        evs_s = timed(step_device, args.sustain)
         c2 = sampler.pos() if sampler else 0
-        ms_sus = sum(a.elapsed_time(b) for a, b in evs_s)
+        ms_sus = sum(a.elapsed_time(b) for a, b in evs_s) if args.sustain > 0 else 0.0
         barrier()
         for _ in range(max(args.warmup, 3)):
             step_host()
@@ -484,7 +491,7 @@ def run_ours(args):
             clocks["sustained_window"] = sampler.window(c1, c2)
             clocks["e2e_window"] = sampler.window(c3, c4)
             clocks["note"] = ("sampled every 20 ms during the K timed steps and the sustained run of "
-                              f"{SUSTAIN_STEPS} further steps timed the same way")
+                              f"{args.sustain} further steps timed the same way")
         line = {
             "metric": METRIC, "value": ips, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
@@ -503,8 +510,8 @@ def run_ours(args):
             "clocks": clocks,
             "split": {"forward_ms_per_step": ms_fwd_step, "gather_ms_per_step": ms_step - ms_fwd_step,
                       "note": "max over ranks of each rank's own event pairs"},
-            "sustained": {"steps": SUSTAIN_STEPS, "ms_per_step": ms_sus / SUSTAIN_STEPS,
-                          "value": B * SUSTAIN_STEPS / (ms_sus * 1e-3)},
+            "sustained": ({"steps": args.sustain, "ms_per_step": ms_sus / args.sustain,
+                           "value": B * args.sustain / (ms_sus * 1e-3)} if args.sustain > 0 else None),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s",
                          "frac": (achieved / tf_peak) if achieved else None, "traffic": traffic,
                          "peak_source": f"{which} burst bf16/fp16 dense; sustained {tf_sus}",
@@ -556,6 +563,9 @@ def main():
     ap.add_argument("--batch", type=int, default=256, help="global batch (the benchmark config uses 256)")
     ap.add_argument("--layers", default="", metavar="FILE",
                     help="also write the per-launch records of one step of the attribution pass to FILE as JSON")
+    ap.add_argument("--sustain", type=int, default=300,
+                    help="further steps timed the same way after the K timed ones, so that clock samples fall into a timed "
+                         "region (0 for a short run under a profiler); the same for every rank")
     ap.add_argument("--no-secondary", action="store_true", help="skip the other benchmark configs (N = 1 only measures them)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -1,12 +1,15 @@
 """Kernel and network sweeps over the benchmark configs other than the headline one.
 
-    python -m nncv_b200.sweeps [gemm] [conv] [nets]
+    python -m nncv_b200.sweeps [gemm [SIZE]] [conv] [nets] [hbm]
 
   gemm : M=N=K in {512,1024,2048,4096}, fp16 in / fp32 accumulate (fp16 and fp32 C), optional fused
          bias + ReLU, and the fp32 CUDA-core path (config 1).
   conv : 3x3 stride-1 pad-1, batch 32 (and 256 with "conv256"), (C=K, H=W) in {(64,64),(128,32),(256,16),(512,8)}, fp16, fused
          scale/shift + ReLU (config 2), for the shifted-view kernel and the TMA-fed per-tap kernel.
   nets : ResNet-18 fp32 N=1 @256 (config 0), ResNet-50 fp16 N=512 @224 (config 4), device-resident.
+  hbm  : the memory-bound operators (depthwise conv + BN + hard-swish, activations, SE scaling, concat,
+         2x upsampling, max-pool, global average pool) on MobileNetV3 / YOLOv5-sized maps: GB/s of
+         algorithmic bytes (elements read + written) against the measured HBM copy bandwidth.
 One JSON line per measurement; times are CUDA-event medians on the launching stream with an L2 flush
 (256 MiB fill) before every timed call.  Torch only owns the device memory.
 """
@@ -48,9 +51,9 @@ def _time(fn, reps=7):
     return sorted(ts)[len(ts) // 2]
 
 
-def gemm():
+def gemm(sizes=(512, 1024, 2048, 4096)):
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    for n in (512, 1024, 2048, 4096):
+    for n in sizes:
         for ab, cdt, epi in ((F16, F32, False), (F16, F16, False), (F16, F16, True), (F32, F32, False)):
             tdt = torch.float16 if ab == F16 else torch.float32
             A = (torch.rand((n, n), device="cuda") * 2 - 1).to(tdt)
@@ -118,10 +121,60 @@ def nets():
         rt.unload()
 
 
+PEAK_GBS = 6540.5
+
+
+def hbm_ops():
+    """(name, GB/s, fraction of the measured HBM bandwidth) of the memory-bound operators."""
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    out = []
+    L = lib()
+
+    def rec(name, nbytes, fn):
+        ms = _time(fn, reps=9)
+        gbs = nbytes / ms / 1e6
+        out.append({"sweep": "hbm", "op": name, "mb": round(nbytes / 1e6, 1), "us": round(ms * 1e3, 1), "gbs": round(gbs, 1),
+                    "frac_of_hbm": round(gbs / PEAK_GBS, 3)})
+        print(json.dumps(out[-1]), flush=True)
+
+    n, c, hw = 64, 96, 112            # a MobileNetV3-large expansion layer at batch 64
+    X = torch.randn((n, hw, hw, c), device="cuda", dtype=torch.float16)
+    Y = torch.empty_like(X)
+    W = torch.randn((c, 3, 3), device="cuda")
+    sc, sh = torch.rand(c, device="cuda") + 0.5, torch.randn(c, device="cuda") * 0.1
+    rec("depthwise 3x3 s1 + BN + hard-swish, 64x112x112x96 fp16", 2 * X.numel() * 2,
+        lambda: check(L.nncv_b200_depthwise_conv_nhwc(_p(X), _p(W), F32, _p(sc), _p(sh), _p(Y), F16, n, hw, hw, c, 3, 3, 1, 1, 3, st)))
+    rec("hard-swish, 77 M fp16 elements", 2 * X.numel() * 2, lambda: check(L.nncv_b200_activation(_p(X), _p(Y), F16, X.numel(), 3, st)))
+    rec("SiLU, 77 M fp16 elements", 2 * X.numel() * 2, lambda: check(L.nncv_b200_activation(_p(X), _p(Y), F16, X.numel(), 5, st)))
+    G8 = torch.rand((n, c), device="cuda", dtype=torch.float16)
+    rec("SE channel scaling, 64x112x112x96 fp16", 2 * X.numel() * 2,
+        lambda: check(L.nncv_b200_scale_channels_nhwc(_p(X), _p(G8), _p(Y), F16, n, hw * hw, c, st)))
+    A = torch.randn((n, 80, 80, 128), device="cuda", dtype=torch.float16)    # YOLOv5s neck at batch 64
+    B = torch.randn((n, 80, 80, 128), device="cuda", dtype=torch.float16)
+    Cc = torch.empty((n, 80, 80, 256), device="cuda", dtype=torch.float16)
+    ptrs = (ctypes.c_void_p * 2)(A.data_ptr(), B.data_ptr())
+    ch = (ctypes.c_int * 2)(128, 128)
+    rec("concat 2 x (64x80x80x128) fp16", 2 * Cc.numel() * 2,
+        lambda: check(L.nncv_b200_concat_channels_nhwc(ptrs, ch, 2, _p(Cc), F16, n * 80 * 80, st)))
+    S = torch.randn((n, 40, 40, 256), device="cuda", dtype=torch.float16)
+    U = torch.empty((n, 80, 80, 256), device="cuda", dtype=torch.float16)
+    rec("upsample 2x, 64x40x40x256 fp16", (S.numel() + U.numel()) * 2, lambda: check(L.nncv_b200_upsample2x_nhwc(_p(S), _p(U), F16, n, 40, 40, 256, st)))
+    M = torch.randn((256, 112, 112, 64), device="cuda", dtype=torch.float16)
+    Mo = torch.empty((256, 56, 56, 64), device="cuda", dtype=torch.float16)
+    rec("max-pool 3x3 s2, 256x112x112x64 fp16", (M.numel() + Mo.numel()) * 2,
+        lambda: check(L.nncv_b200_maxpool_nhwc(_p(M), _p(Mo), F16, 256, 112, 112, 64, 3, 2, 1, st)))
+    Pq = torch.empty((256, 64), device="cuda", dtype=torch.float16)
+    rec("global average pool, 256x112x112x64 fp16", M.numel() * 2, lambda: check(L.nncv_b200_avgpool_nhwc(_p(M), _p(Pq), F16, 256, 112 * 112, 64, st)))
+    return out
+
+
 if __name__ == "__main__":
     which = sys.argv[1:] or ["gemm", "conv", "nets"]
+    sizes = tuple(int(a) for a in which if a.isdigit())
     if "gemm" in which:
-        gemm()
+        gemm(sizes or (512, 1024, 2048, 4096))
+    if "hbm" in which:
+        hbm_ops()
     if "conv" in which:
         conv()
     if "conv256" in which:
