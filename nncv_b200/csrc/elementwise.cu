@@ -40,18 +40,32 @@ __device__ __forceinline__ float hard_sigmoid(float x) {
 }
 __device__ __forceinline__ float sigmoid_ref(float x) { return 1.0f / (expf(-x) + 1.0f); }
 
+// With a 16-bit result the last bits of an fp32 quotient or exponential are rounded away, so those types
+// take a multiply by 1/6 and the hardware exponential / reciprocal (2 ulp of fp32) instead of IEEE division
+// and expf; fp32 tensors keep the exact forms.  NaN and the clamp order are the same in both.
+__device__ __forceinline__ float hard_sigmoid_fast(float x) {
+  float t = (x + 3.0f) * 0.16666667f;
+  t = (1.0f < t) ? 1.0f : t;
+  t = (0.0f > t) ? 0.0f : t;
+  return t;
+}
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.0f, __expf(-x) + 1.0f); }
+
+template <bool FAST>
 __device__ __forceinline__ float activate(float x, int act) {
   switch (act) {
     case kActRelu: return !(x <= 0.0f) ? x : 0.0f;        // cmpf ugt: NaN passes
-    case kActHardSigmoid: return hard_sigmoid(x);
-    case kActHardSwish: return x * hard_sigmoid(x);
-    case kActSigmoid: return sigmoid_ref(x);
-    case kActSilu: return x * sigmoid_ref(x);
+    case kActHardSigmoid: return FAST ? hard_sigmoid_fast(x) : hard_sigmoid(x);
+    case kActHardSwish: return x * (FAST ? hard_sigmoid_fast(x) : hard_sigmoid(x));
+    case kActSigmoid: return FAST ? sigmoid_fast(x) : sigmoid_ref(x);
+    case kActSilu: return x * (FAST ? sigmoid_fast(x) : sigmoid_ref(x));
     default: return x;
   }
 }
 
 // ---------------------------------------------------------------- depthwise convolution --
+// The general form (any filter size and stride, a single channel vector): the 3x3 / 5x5 cases of the
+// fixtures take the TMA-staged kernel of depthwise.cu instead.
 // One thread per (output pixel, vector of V channels); weights [C][R*S] as in the fixture's
 // collapsed filter tensor<Cx3x3>; per-channel scale/shift (folded batch-norm) and activation.
 template <typename T, typename WT>
@@ -89,7 +103,7 @@ __global__ void depthwise_kernel(const T* __restrict__ x, const WT* __restrict__
       float a = acc[e];
       if (scale) a *= __ldg(scale + c + e);
       if (shift) a += __ldg(shift + c + e);
-      o[e] = et<T>(activate(a, act));
+      o[e] = et<T>(activate<sizeof(T) == 2>(a, act));
     }
     *reinterpret_cast<uint4*>(y + (((size_t)n * OH + oy) * OW + ox) * C + c) = *reinterpret_cast<const uint4*>(o);
   }
@@ -104,7 +118,7 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ y, si
     const T* v = reinterpret_cast<const T*>(&raw);
     alignas(16) T o[V];
 #pragma unroll
-    for (int e = 0; e < V; ++e) o[e] = et<T>(activate(ef<T>(v[e]), act));
+    for (int e = 0; e < V; ++e) o[e] = et<T>(activate<sizeof(T) == 2>(ef<T>(v[e]), act));
     reinterpret_cast<uint4*>(y)[i] = *reinterpret_cast<const uint4*>(o);
   }
 }
@@ -183,16 +197,23 @@ __global__ void concat_kernel(const ConcatParams p, uint4* __restrict__ out, lon
 }
 
 // Nearest-neighbour 2x upsampling: out[n, y, x, :] = in[n, y / 2, x / 2, :].
+// One thread per input vector: one load, four stores (the two copies along x are adjacent in memory).
 __global__ void upsample2x_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int N, int H, int W, int cv) {
-  const long long total = (long long)N * (2 * H) * (2 * W) * cv;
+  const long long total = (long long)N * H * W * cv;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int c = (int)(i % cv);
     long long t = i / cv;
-    const int x = (int)(t % (2 * W));
-    t /= 2 * W;
-    const int y = (int)(t % (2 * H));
-    const int n = (int)(t / (2 * H));
-    out[i] = __ldg(in + (((size_t)n * H + (y >> 1)) * W + (x >> 1)) * cv + c);
+    const int x = (int)(t % W);
+    t /= W;
+    const int y = (int)(t % H);
+    const int n = (int)(t / H);
+    const uint4 v = __ldg(in + i);
+    uint4* o = out + (((size_t)n * 2 * H + 2 * y) * (2 * W) + 2 * x) * cv + c;
+    const size_t row = (size_t)2 * W * cv;
+    o[0] = v;
+    o[cv] = v;
+    o[row] = v;
+    o[row + cv] = v;
   }
 }
 
@@ -206,9 +227,17 @@ int grid_for(long long work, int threads) {
 }  // namespace
 
 cudaError_t launch_depthwise(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
-                             int N, int H, int W, int C, int R, int S, int stride, int pad, int act, cudaStream_t st) {
+                             int N, int H, int W, int C, int R, int S, int stride, int pad, int act, int sm_count, int* error_flag,
+                             cudaStream_t st) {
   const int V = 16 / (int)dtype_size(dt);
   if (C % V != 0 || w_dt == kBF16) return cudaErrorInvalidValue;
+  if (dt != kF16 && w_dt != kF32) return cudaErrorInvalidValue;
+  if (depthwise_tma_supported(dt, N, H, W, C, R, S, stride, pad) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+    const cudaError_t e = launch_depthwise_tma(x, w, w_dt, scale, shift, y, dt, N, H, W, C, R, S, stride, pad, act, sm_count, error_flag, st);
+    if (e == cudaSuccess) return e;
+    cudaGetLastError();
+  }
   const int OH = (H + 2 * pad - R) / stride + 1, OW = (W + 2 * pad - S) / stride + 1;
   if (OH <= 0 || OW <= 0) return cudaErrorInvalidValue;
   const long long work = (long long)N * OH * OW * (C / V);
@@ -271,7 +300,7 @@ cudaError_t launch_concat(const void* const* in, const int* channels, int n_in, 
 cudaError_t launch_upsample2x(const void* in, void* out, DType dt, int N, int H, int W, int C, cudaStream_t st) {
   const int V = 16 / (int)dtype_size(dt);
   if (C % V != 0) return cudaErrorInvalidValue;
-  upsample2x_kernel<<<grid_for((long long)N * 4 * H * W * (C / V), 256), 256, 0, st>>>((const uint4*)in, (uint4*)out, N, H, W, C / V);
+  upsample2x_kernel<<<grid_for((long long)N * H * W * (C / V), 256), 256, 0, st>>>((const uint4*)in, (uint4*)out, N, H, W, C / V);
   return cudaGetLastError();
 }
 

@@ -203,8 +203,15 @@ cudaError_t launch_gemm_tf32x3(const float* A, const float* B, float* C, int M, 
 // ---- memory-bound operators of the mobile / detection fixtures (NHWC, 16-byte accesses) --------
 enum Activation : int { kActNone = 0, kActRelu = 1, kActHardSigmoid = 2, kActHardSwish = 3, kActSigmoid = 4, kActSilu = 5 };
 // depthwise conv, weights [C][R*S] (fp32, or fp16 with fp16 activations), folded batch-norm, activation
+// 3x3 / 5x5, stride 1 / 2 with at least two 16-byte channel vectors take the TMA-staged kernel (depthwise.cu), the rest a
+// one-thread-per-output kernel; error_flag is the device status word for the staged kernel's bounded waits
 cudaError_t launch_depthwise(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
-                             int N, int H, int W, int C, int R, int S, int stride, int pad, int act, cudaStream_t st);
+                             int N, int H, int W, int C, int R, int S, int stride, int pad, int act, int sm_count, int* error_flag,
+                             cudaStream_t st);
+bool depthwise_tma_supported(DType dt, int N, int H, int W, int C, int R, int S, int stride, int pad);
+cudaError_t launch_depthwise_tma(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
+                                 int N, int H, int W, int C, int R, int S, int stride, int pad, int act, int sm_count,
+                                 int* error_flag, cudaStream_t st);
 cudaError_t launch_activation(const void* x, void* y, DType dt, size_t n, int act, cudaStream_t st);
 cudaError_t launch_scale_channels(const void* x, const void* gate, void* y, DType dt, int N, long long HW, int C, cudaStream_t st);
 cudaError_t launch_se_gate(const void* pooled, const float* w1, const float* b1, const float* w2, const float* b2, void* gate,

@@ -2265,7 +2265,7 @@ int nncv_b200_depthwise_conv_nhwc(const void* in, const void* weights, int w_dty
       dtype > 2 || act < 0 || act > 5)
     return fail(NNCV_B200_EINVAL, "depthwise_conv: bad argument");
   if (launch_depthwise(in, weights, (DType)w_dtype, scale, shift, out, (DType)dtype, N, H, W, C, R, S, stride, pad, act,
-                       (cudaStream_t)stream) != cudaSuccess) {
+                       g_dev.sm_count, g_dev.error_flag, (cudaStream_t)stream) != cudaSuccess) {
     cudaGetLastError();
     return fail(NNCV_B200_EINVAL, "depthwise_conv: C must be a multiple of %d, weights fp32 (or fp16 with fp16 activations), output not empty",
                 16 / (int)dtype_size((DType)dtype));

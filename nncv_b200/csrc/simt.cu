@@ -5,6 +5,7 @@
 // folded here into per-channel scale/shift), :138-143 (ReLU with unordered compare, NaN passes),
 // :144-151 (max-pool over a -inf padded map), :606-614 (sum-pool / HW), :193-197 (residual add).
 // All activations are NHWC; every helper moves 16 bytes per access.
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -14,6 +15,8 @@
 #include "ptx.cuh"
 
 namespace nncv_b200 {
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -156,6 +159,16 @@ __global__ void nchw_to_nhwc_kernel(const SrcT* __restrict__ src, DstT* __restri
 }
 
 // ------------------------------------------------------------------ pooling --------------
+template <typename T> struct Pair { using type = float2; };
+template <> struct Pair<__half> {
+  using type = __half2;
+  static __device__ __forceinline__ __half2 neg_inf() { return __half2half2(__ushort_as_half((unsigned short)0xfc00)); }
+};
+template <> struct Pair<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static __device__ __forceinline__ __nv_bfloat162 neg_inf() { return __bfloat162bfloat162(__ushort_as_bfloat16((unsigned short)0xff80)); }
+};
+
 // Max-pool over a -inf padded map; one thread per (output pixel, 16-byte channel vector).
 template <typename T>
 __global__ void maxpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int H,
@@ -163,37 +176,62 @@ __global__ void maxpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ d
                                     Layout il, Layout ol) {
   constexpr int V = 16 / sizeof(T);
   const int cv = C / V;
-  const long long total = (long long)N * OH * OW * cv;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(i % cv) * V;
-    long long t = i / cv;
-    const int ox = (int)(t % OW);
-    t /= OW;
-    const int oy = (int)(t % OH);
-    const int n = (int)(t / OH);
-    float m[V];
+  // the launcher keeps the count of (output pixel, vector) items below 2^31: the index arithmetic is
+  // 32-bit (four 64-bit divisions would cost more than the nine loads and maxima together)
+  const unsigned total = (unsigned)N * OH * OW * cv;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    unsigned t = i / (unsigned)cv;
+    const int c = (int)(i - t * cv) * V;
+    const unsigned t2 = t / (unsigned)OW;
+    const int ox = (int)(t - t2 * OW);
+    const int n = (int)(t2 / (unsigned)OH);
+    const int oy = (int)(t2 - (unsigned)n * OH);
+    alignas(16) T o[V];
+    if constexpr (sizeof(T) == 2) {
+      // 16-bit types: the maximum is exact in the storage type, so it is taken on packed pairs
+      // (NaN-propagating, like the scalar form below) without a round trip through fp32.
+      using T2 = typename Pair<T>::type;
+      T2 m2[4];
 #pragma unroll
-    for (int e = 0; e < V; ++e) m[e] = -INFINITY;
-    for (int r = 0; r < k; ++r) {
-      const int iy = oy * stride - pad + r;
-      if ((unsigned)iy >= (unsigned)H) continue;
-      for (int s = 0; s < k; ++s) {
-        const int ix = ox * stride - pad + s;
-        if ((unsigned)ix >= (unsigned)W) continue;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
-            src + (((size_t)n * il.img_rows + iy + il.off) * il.pitch + ix + il.off) * C + c));
-        const T* v = reinterpret_cast<const T*>(&raw);
+      for (int e = 0; e < 4; ++e) m2[e] = Pair<T>::neg_inf();
+      for (int r = 0; r < k; ++r) {
+        const int iy = oy * stride - pad + r;
+        if ((unsigned)iy >= (unsigned)H) continue;
+        for (int s = 0; s < k; ++s) {
+          const int ix = ox * stride - pad + s;
+          if ((unsigned)ix >= (unsigned)W) continue;
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+              src + (((size_t)n * il.img_rows + iy + il.off) * il.pitch + ix + il.off) * C + c));
+          const T2* v2 = reinterpret_cast<const T2*>(&raw);
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          const float f = to_f<T>(v[e]);
-          m[e] = (m[e] < f || f != f) ? f : m[e];  // maximumf: NaN propagates
+          for (int e = 0; e < 4; ++e) m2[e] = __hmax2_nan(m2[e], v2[e]);
         }
       }
-    }
-    alignas(16) T o[V];
 #pragma unroll
-    for (int e = 0; e < V; ++e) o[e] = from_f<T>(m[e]);
+      for (int e = 0; e < 4; ++e) reinterpret_cast<T2*>(o)[e] = m2[e];
+    } else {
+      float m[V];
+#pragma unroll
+      for (int e = 0; e < V; ++e) m[e] = -INFINITY;
+      for (int r = 0; r < k; ++r) {
+        const int iy = oy * stride - pad + r;
+        if ((unsigned)iy >= (unsigned)H) continue;
+        for (int s = 0; s < k; ++s) {
+          const int ix = ox * stride - pad + s;
+          if ((unsigned)ix >= (unsigned)W) continue;
+          const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+              src + (((size_t)n * il.img_rows + iy + il.off) * il.pitch + ix + il.off) * C + c));
+          const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            const float f = to_f<T>(v[e]);
+            m[e] = (m[e] < f || f != f) ? f : m[e];  // maximumf: NaN propagates
+          }
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < V; ++e) o[e] = from_f<T>(m[e]);
+    }
     *reinterpret_cast<uint4*>(dst + (((size_t)n * ol.img_rows + oy + ol.off) * ol.pitch + ox + ol.off) * C + c) =
         *reinterpret_cast<const uint4*>(o);
   }
@@ -242,6 +280,62 @@ __global__ void avgpool_nhwc_kernel(const T* __restrict__ src, T* __restrict__ d
       *reinterpret_cast<uint4*>(dst + (size_t)n * C + c) = *reinterpret_cast<const uint4*>(o);
     }
   }
+}
+
+// Global average pool of a large map (squeeze-and-excitation on early layers): a cluster of eight CTAs per
+// (image, group of up to 256 channel vectors), each CTA summing one eighth of the pixels with
+// threads laid out [pixel slice][channel vector] so that a warp reads whole pixels; the CTA's
+// slices are added through shared memory, the eight CTA totals through distributed shared memory
+// by the cluster's first CTA, in a fixed order.  No scratch memory, no atomics.
+constexpr int kPoolCluster = 8;
+template <typename T>
+__global__ void __cluster_dims__(kPoolCluster, 1, 1) __launch_bounds__(256)
+avgpool_cluster_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, int H, int W, int C, Layout il) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ __align__(16) float part[256 * V];     // [slice][vector][V]
+  __shared__ __align__(16) float tot[256 * V];      // [vector][V]: this CTA's sum
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int n = blockIdx.y;
+  const int cv = C / V;
+  const int v0 = blockIdx.z * 256;
+  const int cvb = min(256, cv - v0);
+  const int ps = 256 / cvb;
+  const int slice = threadIdx.x / cvb, vc = threadIdx.x - slice * cvb;
+  const int HW = H * W;
+  const int lo = (int)((long long)HW * rank / kPoolCluster), hi = (int)((long long)HW * (rank + 1) / kPoolCluster);
+  float s[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) s[e] = 0.0f;
+  if (slice < ps) {
+#pragma unroll 4
+    for (int px = lo + slice; px < hi; px += ps) {
+      const int y = px / W, x = px - y * W;
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+          src + (((size_t)n * il.img_rows + y + il.off) * il.pitch + x + il.off) * C + (size_t)(v0 + vc) * V));
+      const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int e = 0; e < V; ++e) s[e] += to_f<T>(v[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) part[(slice * cvb + vc) * V + e] = s[e];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < cvb * V; i += blockDim.x) {
+    float a = 0.0f;
+    for (int q = 0; q < ps; ++q) a += part[q * cvb * V + i];
+    tot[i] = a;
+  }
+  cluster.sync();
+  if (rank == 0) {
+    for (int i = threadIdx.x; i < cvb * V; i += blockDim.x) {
+      float a = 0.0f;
+#pragma unroll
+      for (int q = 0; q < kPoolCluster; ++q) a += *cluster.map_shared_rank(&tot[i], q);
+      dst[(size_t)n * C + (size_t)v0 * V + i] = from_f<T>(a / (float)HW);
+    }
+  }
+  cluster.sync();      // the other CTAs' shared memory stays alive until the first has read it
 }
 
 // Layout change, one thread per 16-byte vector of a destination slot; pads are written as zero.
@@ -351,6 +445,7 @@ cudaError_t launch_maxpool_nhwc(const void* src, void* dst, DType dt, int N, int
     constexpr int V = 16 / sizeof(T);
     if (C % V != 0) return cudaErrorInvalidValue;
     const long long total = (long long)N * OH * OW * (C / V);
+    if (total >= (1LL << 31) - (1LL << 21)) return cudaErrorInvalidValue;   // 16 GiB of fp16 output: beyond any plan here
     maxpool_nhwc_kernel<T><<<grid_for(total, 256), 256, 0, stream>>>(
         static_cast<const T*>(src), static_cast<T*>(dst), N, H, W, C, OH, OW, k, stride, pad, in_l,
         out_l);
@@ -365,6 +460,12 @@ cudaError_t launch_avgpool_nhwc(const void* src, void* dst, DType dt, int N, int
     using T = decltype(tag);
     constexpr int V = 16 / sizeof(T);
     if (C % V != 0) return cudaErrorInvalidValue;
+    if ((long long)H * W >= 512 && N <= 65535) {
+      const int cv = C / V;
+      avgpool_cluster_kernel<T><<<dim3(kPoolCluster, N, (cv + 255) / 256), 256, 0, stream>>>(
+          static_cast<const T*>(src), static_cast<T*>(dst), N, H, W, C, in_l);
+      return cudaGetLastError();
+    }
     const long long total = (long long)N * (C / V) * 8;
     avgpool_nhwc_kernel<T><<<grid_for(total, 256), 256, 0, stream>>>(
         static_cast<const T*>(src), static_cast<T*>(dst), N, H, W, C, in_l);

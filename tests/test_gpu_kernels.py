@@ -391,6 +391,23 @@ def test_avgpool(dtype):
     assert G.rel_l2(G.host(Y), ref) <= (1e-3 if dtype == F16 else 1e-6)
 
 
+@pytest.mark.parametrize("n,c,h,w", [(2, 72, 56, 56), (1, 4096, 23, 23), (3, 2088, 19, 27), (5, 8, 64, 65), (2, 120, 28, 28)])
+@pytest.mark.parametrize("dtype", [F16, F32, BF16])
+def test_avgpool_large_map(n, c, h, w, dtype):
+    """Maps of 512 pixels and more take the cluster kernel (eight CTAs per image, totals added through
+    distributed shared memory): channel-vector counts that are not powers of two, more than 256
+    vectors (several channel groups), pixel counts that do not divide by eight."""
+    g = _rng(n * c + h)
+    x = (g.standard_normal((n, c, h, w)) + 0.5).astype(np.float32)
+    X = G.dev(x.transpose(0, 2, 3, 1), dtype)
+    Y = torch.full((n, c), float("nan"), device="cuda", dtype=G.TORCH_DT[dtype])
+    check(lib().nncv_b200_avgpool_nhwc(G.p(X), G.p(Y), dtype, n, h * w, c, G.stream_ptr()))
+    torch.cuda.synchronize()
+    ref = ob.avgpool_global(G.host(X).transpose(0, 3, 1, 2))
+    assert np.abs(G.host(Y) - ref).max() <= {F16: 1e-3, F32: 2e-6, BF16: 8e-3}[dtype]
+    assert lib().nncv_b200_device_status() == 0
+
+
 def test_nchw_to_nhwc_and_bn_fold():
     g = _rng(13)
     x = g.standard_normal((2, 3, 10, 12)).astype(np.float32)

@@ -24,7 +24,7 @@ def nhwc(a):
 @pytest.mark.parametrize("case", [
     # n, c, h, w, k, stride, pad   (MobileNetV3-small: 16@128 s2, 72@64 s2, 88@32 s1, 96@32 5x5 s2, 576@8 5x5)
     (2, 16, 128, 128, 3, 2, 1), (2, 72, 64, 64, 3, 2, 1), (3, 88, 32, 32, 3, 1, 1), (2, 96, 32, 32, 5, 2, 2),
-    (4, 576, 8, 8, 5, 1, 2), (1, 8, 5, 7, 3, 1, 1)])
+    (4, 576, 8, 8, 5, 1, 2), (1, 8, 5, 7, 3, 1, 1), (1, 24, 37, 153, 3, 1, 1), (2, 40, 30, 29, 5, 1, 2), (3, 200, 15, 14, 3, 2, 1)])
 @pytest.mark.parametrize("dtype,act", [(F16, "hard_swish"), (F16, "relu"), (F32, "hard_swish"), (BF16, "none")])
 def test_depthwise_conv_bn_activation(case, dtype, act):
     n, c, h, w, k, stride, pad = case
@@ -46,6 +46,7 @@ def test_depthwise_conv_bn_activation(case, dtype, act):
     y = G.host(Y).transpose(0, 3, 1, 2)
     assert y.shape == ref.shape and np.isfinite(y).all()
     assert G.rel_l2(y, ref) <= TOL[dtype]
+    assert lib().nncv_b200_device_status() == 0      # no bounded wait of the TMA-staged kernel gave up
 
 
 @pytest.mark.parametrize("dtype", [F16, F32, BF16])
