@@ -308,14 +308,27 @@ avgpool_cluster_kernel(const T* __restrict__ src, T* __restrict__ dst, int N, in
 #pragma unroll
   for (int e = 0; e < V; ++e) s[e] = 0.0f;
   if (slice < ps) {
+    if (il.off == 0 && il.pitch == W && il.img_rows == H) {
+      // dense map: pixels are C elements apart, no row arithmetic
+      const T* ptr = src + ((size_t)n * HW + lo + slice) * C + (size_t)(v0 + vc) * V;
+      const size_t step = (size_t)ps * C;
 #pragma unroll 4
-    for (int px = lo + slice; px < hi; px += ps) {
-      const int y = px / W, x = px - y * W;
-      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
-          src + (((size_t)n * il.img_rows + y + il.off) * il.pitch + x + il.off) * C + (size_t)(v0 + vc) * V));
-      const T* v = reinterpret_cast<const T*>(&raw);
+      for (int px = lo + slice; px < hi; px += ps, ptr += step) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(ptr));
+        const T* v = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-      for (int e = 0; e < V; ++e) s[e] += to_f<T>(v[e]);
+        for (int e = 0; e < V; ++e) s[e] += to_f<T>(v[e]);
+      }
+    } else {
+#pragma unroll 4
+      for (int px = lo + slice; px < hi; px += ps) {
+        const int y = px / W, x = px - y * W;
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(
+            src + (((size_t)n * il.img_rows + y + il.off) * il.pitch + x + il.off) * C + (size_t)(v0 + vc) * V));
+        const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int e = 0; e < V; ++e) s[e] += to_f<T>(v[e]);
+      }
     }
 #pragma unroll
     for (int e = 0; e < V; ++e) part[(slice * cvb + vc) * V + e] = s[e];
