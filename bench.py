@@ -319,7 +319,78 @@ def secondary_configs(torch, rt, flush, sampler, tf_peak):
         finally:
             rt.unload()
             torch.cuda.empty_cache()
+    # MobileNetV3-small as nncv's fixture spells it (tests/Nets/MobileNetV3.mlir of the nncv tree), through the plan the importer
+    # wrote from that module: fp16, batch 256 @224, seeded random weights
+    try:
+        name = "MobileNetV3-small fp16 N=256 @224 (imported plan of nncv's fixture)"
+        text = open(os.path.join(ROOT, "tests", "golden", "mobilenetv3_from_mlir.plan")).read()
+        blob, flops_per_image = _plan_blob_and_flops(text, 224, 224)
+        n = 256
+        rt.load_blob("plan:" + text, blob.astype(np.float16), F16)
+        x = torch.randn((n, 3, 224, 224), device="cuda").to(torch.float16)
+        o = torch.empty((n, 1000), device="cuda", dtype=x.dtype)
+        rt.forward_device(o, x, s)
+        torch.cuda.synchronize()
+        i0 = sampler.pos() if sampler else 0
+        ms, reps = _timed_loop(torch, flush, lambda: rt.forward_device(o, x, s), min_ms=200.0, min_reps=5)
+        e = entry(ms, reps, flops_per_image * n, i0, config=name, batch=n)
+        e["images_per_s"] = round(n / ms * 1e3, 1)
+        e["note"] = "memory-bound network (0.11 GFLOP per image): images/s is the figure, the tensor-peak fraction is not a target"
+        out["nets"].append(e)
+        del x, o
+    except Exception as ex:
+        out["nets"].append({"config": name, "error": str(ex)[:200]})
+    finally:
+        rt.unload()
+        torch.cuda.empty_cache()
     return out
+
+
+def _plan_blob_and_flops(text, h, w):
+    """Seeded parameters for a plan text (conv weights ~ N(0, 2/fan_in), batch-norm scale and variance in [0.5, 1.5], the
+    rest small) and the multiply-add FLOPs of one image."""
+    g = np.random.default_rng(0)
+    total, nodes = 0, []
+    for line in text.splitlines():
+        t = line.split("#")[0].split()
+        if not t or t[0] == "nncv_b200_plan":
+            continue
+        if t[0] == "params":
+            total = int(t[1])
+            continue
+        nodes.append((t[0], {k: int(v) for k, v in (f.split("=") for f in t[1:])}))
+    blob = (g.standard_normal(total) * 0.05).astype(np.float32)
+    shape = {0: (h, w)}
+    flops = 0.0
+    for kind, f in nodes:
+        ih, iw = shape.get(f["in"], (1, 1))
+        if kind in ("conv", "dwconv"):
+            cout = f.get("cout", f.get("c"))
+            cin = 1 if kind == "dwconv" else f["cin"]
+            k = f["k"]
+            oh, ow = (ih + 2 * f["pad"] - k) // f["stride"] + 1, (iw + 2 * f["pad"] - k) // f["stride"] + 1
+            nw = cout * cin * k * k
+            blob[f["w"]:f["w"] + nw] = g.standard_normal(nw) * np.sqrt(2.0 / (cin * k * k))
+            for role in ("gamma", "var"):
+                if role in f:
+                    blob[f[role]:f[role] + cout] = g.uniform(0.5, 1.5, cout)
+            flops += 2.0 * nw * oh * ow
+            shape[f["id"]] = (oh, ow)
+        elif kind == "maxpool":
+            shape[f["id"]] = ((ih + 2 * f["pad"] - f["k"]) // f["stride"] + 1, (iw + 2 * f["pad"] - f["k"]) // f["stride"] + 1)
+        elif kind == "se":
+            for wk, cnt in (("w1", f["c"] * f["cr"]), ("w2", f["c"] * f["cr"])):
+                blob[f[wk]:f[wk] + cnt] = g.standard_normal(cnt) * np.sqrt(1.0 / f["c"])
+            flops += 4.0 * f["c"] * f["cr"]
+            shape[f["id"]] = (ih, iw)
+        elif kind == "fc":
+            cnt = f["cin"] * f["cout"]
+            blob[f["w"]:f["w"] + cnt] = g.standard_normal(cnt) * np.sqrt(1.0 / f["cin"])
+            flops += 2.0 * cnt
+            shape[f["id"]] = (1, 1)
+        else:
+            shape[f["id"]] = (1, 1)
+    return blob, flops
 
 
 def run_ours(args):

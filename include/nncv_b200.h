@@ -114,9 +114,14 @@ void _mlir_ciface_forward(nncv_memref2* dst, nncv_memref4* src, void* params);
  *   nncv_b200_plan 1
  *   params <elements in the blob> out <output features>
  *   conv id= in= res= cin= cout= k= stride= pad= relu= w= gamma= beta= mean= var=
- *   maxpool id= in= k= stride= pad=        avgpool id= in=        fc id= in= cin= cout= w= b=
- * (tensor 0 is the input; res = tensor added before the ReLU or -1; w, gamma, ... are element
- * offsets into the blob; the FC node comes last and reads a global average pool). */
+ *   maxpool id= in= k= stride= pad=        avgpool id= in=        fc id= in= cin= cout= w= b= [act=]
+ *   dwconv id= in= c= k= stride= pad= act= w= gamma= beta= mean= var=      (depthwise conv + batch-norm + activation,
+ *                                                  linalg.depthwise_conv_2d_nchw_chw of tests/Nets/MobileNetV3.mlir:301)
+ *   se id= in= c= cr= w1= b1= w2= b2=       (squeeze-and-excitation, MobileNetV3.mlir:319-389: scales tensor `in` in place)
+ * (tensor 0 is the input; res = tensor added before the activation or -1; w, gamma, ... are element
+ * offsets into the blob; a conv may carry act=<NNCV_B200_ACT_* code> instead of relu=1, b=<bias> instead of
+ * the batch-norm fields, and eps_bits=<fp32 bit pattern> when its batch-norm epsilon is not 1e-5; FC nodes
+ * read the global average pool or another FC node, and the last node is an FC without activation). */
 int nncv_b200_load(const char* net, const char* model_bin_path, const nncv_b200_opts* opts);
 /* Same, from a blob already in host memory (tensors back to back in file order). */
 int nncv_b200_load_blob(const char* net, const void* blob, size_t n_elements, size_t ele_width,

@@ -40,6 +40,7 @@ struct DwParams {
   const float* shift;  // [C] or null
   void* y;             // [N,OH,OW,C]
   int N, H, W, C, OH, OW, pad, act;
+  Layout in_l, out_l;  // input coordinates and output pixels are shifted by the layouts' pad offsets
   int tw, cbv;         // output columns per tile, 16-byte channel vectors per chunk (tw * cbv == 128)
   int tiles_x, tiles_y, n_tiles;   // spatial tiles (n_tiles = N * tiles_y * tiles_x)
   int stages;
@@ -175,8 +176,8 @@ __global__ void __launch_bounds__(kThreads, KS == 3 ? 3 : 2) depthwise_tma_kerne
     const uint32_t bar = ptx::smem_u32(&full_bar[s]);
     tile_info[s] = make_int4(n, ty * kTH, tx * tw, 0);   // read by the others after they have seen the barrier complete
     ptx::mbar_arrive_expect_tx(bar, p.stage_bytes);
-    ptx::tma_load_4d(ptx::smem_u32(smem + (size_t)s * p.stage_stride), &tm_in, c0, tx * tw * STRIDE - p.pad,
-                     ty * kTH * STRIDE - p.pad, n, bar);
+    ptx::tma_load_4d(ptx::smem_u32(smem + (size_t)s * p.stage_stride), &tm_in, c0, tx * tw * STRIDE - p.pad + p.in_l.off,
+                     ty * kTH * STRIDE - p.pad + p.in_l.off, n, bar);
   };
   int issued = 0;
   if (tid == 0)
@@ -260,7 +261,9 @@ __global__ void __launch_bounds__(kThreads, KS == 3 ? 3 : 2) depthwise_tma_kerne
             r2[e] = make_float2(act1<sizeof(T) == 4>(a.x, p.act), act1<sizeof(T) == 4>(a.y, p.act));
           }
         }
-        *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.y) + (((size_t)n * p.OH + oy) * p.OW + ox) * p.C + c) = pack<T>(r2);
+        *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.y) +
+                                  (((size_t)n * p.out_l.img_rows + oy + p.out_l.off) * p.out_l.pitch + ox + p.out_l.off) * p.C + c) =
+            pack<T>(r2);
       }
     }
   }
@@ -317,8 +320,8 @@ bool depthwise_tma_supported(DType dt, int N, int H, int W, int C, int R, int S,
 }
 
 cudaError_t launch_depthwise_tma(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
-                                 int N, int H, int W, int C, int R, int S, int stride, int pad, int act, int sm_count,
-                                 int* error_flag, cudaStream_t st) {
+                                 int N, int H, int W, int C, int R, int S, int stride, int pad, int act, Layout in_l, Layout out_l,
+                                 int sm_count, int* error_flag, cudaStream_t st) {
   if (!depthwise_tma_supported(dt, N, H, W, C, R, S, stride, pad) || (reinterpret_cast<uintptr_t>(x) & 15) ||
       (reinterpret_cast<uintptr_t>(y) & 15))
     return cudaErrorInvalidValue;
@@ -350,6 +353,12 @@ cudaError_t launch_depthwise_tma(const void* x, const void* w, DType w_dt, const
   p.stages = stages;
   p.w = w; p.w_half = w_dt == kF16; p.scale = scale; p.shift = shift; p.y = y;
   p.N = N; p.H = H; p.W = W; p.C = C; p.OH = OH; p.OW = OW; p.pad = pad; p.act = act;
+  if (in_l.pitch == 0) in_l = dense_layout(H, W);
+  if (out_l.pitch == 0) out_l = dense_layout(OH, OW);
+  // a padded layout's pad row / column is zero and everything beyond the map is out of the tensor map's range
+  // (zero-filled), so the halo reads the same values as over a dense map
+  if (in_l.off != 0 && (in_l.off != 1 || in_l.pitch != W + 1 || in_l.img_rows != H + 1)) return cudaErrorInvalidValue;
+  p.in_l = in_l; p.out_l = out_l;
   p.tiles_x = (OW + tw - 1) / tw; p.tiles_y = (OH + kTH - 1) / kTH;
   p.n_tiles = N * p.tiles_y * p.tiles_x;
   p.error_flag = error_flag;
@@ -359,8 +368,8 @@ cudaError_t launch_depthwise_tma(const void* x, const void* w, DType w_dt, const
   CUtensorMap tm;
   const CUtensorMapDataType tdt = dt == kF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                   : dt == kF16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  cuuint64_t gdim[4] = {(cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)N};
-  cuuint64_t gstr[3] = {(cuuint64_t)C * es, (cuuint64_t)W * C * es, (cuuint64_t)H * W * C * es};
+  cuuint64_t gdim[4] = {(cuuint64_t)C, (cuuint64_t)in_l.pitch, (cuuint64_t)in_l.img_rows, (cuuint64_t)N};
+  cuuint64_t gstr[3] = {(cuuint64_t)C * es, (cuuint64_t)in_l.pitch * C * es, (cuuint64_t)in_l.img_rows * in_l.pitch * C * es};
   cuuint32_t box[4] = {(cuuint32_t)(cbv * V), (cuuint32_t)IW, (cuuint32_t)IH, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   if (enc(&tm, tdt, 4, const_cast<void*>(x), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,

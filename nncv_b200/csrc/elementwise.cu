@@ -71,7 +71,7 @@ __device__ __forceinline__ float activate(float x, int act) {
 template <typename T, typename WT>
 __global__ void depthwise_kernel(const T* __restrict__ x, const WT* __restrict__ w, const float* __restrict__ scale,
                                  const float* __restrict__ shift, T* __restrict__ y, int N, int H, int W, int C, int OH,
-                                 int OW, int R, int S, int stride, int pad, int act) {
+                                 int OW, int R, int S, int stride, int pad, int act, Layout il, Layout ol) {
   constexpr int V = 16 / sizeof(T);
   const int cv = C / V;
   const long long total = (long long)N * OH * OW * cv;
@@ -91,7 +91,7 @@ __global__ void depthwise_kernel(const T* __restrict__ x, const WT* __restrict__
       for (int s = 0; s < S; ++s) {
         const int ix = ox * stride - pad + s;
         if ((unsigned)ix >= (unsigned)W) continue;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + (((size_t)n * H + iy) * W + ix) * C + c));
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + (((size_t)n * il.img_rows + iy + il.off) * il.pitch + ix + il.off) * C + c));
         const T* v = reinterpret_cast<const T*>(&raw);
 #pragma unroll
         for (int e = 0; e < V; ++e) acc[e] = fmaf(ef<T>(v[e]), ef<WT>(__ldg(w + (size_t)(c + e) * R * S + r * S + s)), acc[e]);
@@ -105,7 +105,7 @@ __global__ void depthwise_kernel(const T* __restrict__ x, const WT* __restrict__
       if (shift) a += __ldg(shift + c + e);
       o[e] = et<T>(activate<sizeof(T) == 2>(a, act));
     }
-    *reinterpret_cast<uint4*>(y + (((size_t)n * OH + oy) * OW + ox) * C + c) = *reinterpret_cast<const uint4*>(o);
+    *reinterpret_cast<uint4*>(y + (((size_t)n * ol.img_rows + oy + ol.off) * ol.pitch + ox + ol.off) * C + c) = *reinterpret_cast<const uint4*>(o);
   }
 }
 
@@ -227,24 +227,27 @@ int grid_for(long long work, int threads) {
 }  // namespace
 
 cudaError_t launch_depthwise(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
-                             int N, int H, int W, int C, int R, int S, int stride, int pad, int act, int sm_count, int* error_flag,
-                             cudaStream_t st) {
+                             int N, int H, int W, int C, int R, int S, int stride, int pad, int act, Layout in_l, Layout out_l,
+                             int sm_count, int* error_flag, cudaStream_t st) {
   const int V = 16 / (int)dtype_size(dt);
   if (C % V != 0 || w_dt == kBF16) return cudaErrorInvalidValue;
   if (dt != kF16 && w_dt != kF32) return cudaErrorInvalidValue;
   if (depthwise_tma_supported(dt, N, H, W, C, R, S, stride, pad) && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
-    const cudaError_t e = launch_depthwise_tma(x, w, w_dt, scale, shift, y, dt, N, H, W, C, R, S, stride, pad, act, sm_count, error_flag, st);
+    const cudaError_t e = launch_depthwise_tma(x, w, w_dt, scale, shift, y, dt, N, H, W, C, R, S, stride, pad, act, in_l, out_l, sm_count,
+                                               error_flag, st);
     if (e == cudaSuccess) return e;
     cudaGetLastError();
   }
   const int OH = (H + 2 * pad - R) / stride + 1, OW = (W + 2 * pad - S) / stride + 1;
   if (OH <= 0 || OW <= 0) return cudaErrorInvalidValue;
+  if (in_l.pitch == 0) in_l = dense_layout(H, W);
+  if (out_l.pitch == 0) out_l = dense_layout(OH, OW);
   const long long work = (long long)N * OH * OW * (C / V);
   const int g = grid_for(work, 256);
 #define NNCV_DW(T, WT)                                                                                                        \
   depthwise_kernel<T, WT><<<g, 256, 0, st>>>((const T*)x, (const WT*)w, scale, shift, (T*)y, N, H, W, C, OH, OW, R, S, stride, \
-                                             pad, act)
+                                             pad, act, in_l, out_l)
   if (dt == kF32) { if (w_dt != kF32) return cudaErrorInvalidValue; NNCV_DW(float, float); }
   else if (dt == kF16) { if (w_dt == kF32) NNCV_DW(__half, float); else NNCV_DW(__half, __half); }
   else { if (w_dt != kF32) return cudaErrorInvalidValue; NNCV_DW(__nv_bfloat16, float); }

@@ -189,9 +189,8 @@ cudaError_t launch_avgpool_nhwc(const void* src, void* dst, DType dt, int N, int
 cudaError_t launch_relayout(const void* src, Layout src_l, void* dst, Layout dst_l, DType dt, int N,
                             int H, int W, int C, cudaStream_t stream);
 // scale = gamma * rsqrt(var + 1e-5f); shift = beta - mean * scale  (inputs of type dt)
-cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean,
-                           const void* var, DType dt, int C, float* scale, float* shift,
-                           cudaStream_t stream);
+cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean, const void* var, DType dt, int C, float eps,
+                           float* scale, float* shift, cudaStream_t stream);
 cudaError_t launch_convert(const void* src, DType src_dt, void* dst, DType dst_dt, size_t n,
                            cudaStream_t stream);
 
@@ -205,13 +204,14 @@ enum Activation : int { kActNone = 0, kActRelu = 1, kActHardSigmoid = 2, kActHar
 // depthwise conv, weights [C][R*S] (fp32, or fp16 with fp16 activations), folded batch-norm, activation
 // 3x3 / 5x5, stride 1 / 2 with at least two 16-byte channel vectors take the TMA-staged kernel (depthwise.cu), the rest a
 // one-thread-per-output kernel; error_flag is the device status word for the staged kernel's bounded waits
+// in_l / out_l: where the pixels live (pitch 0 = dense NHWC)
 cudaError_t launch_depthwise(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
-                             int N, int H, int W, int C, int R, int S, int stride, int pad, int act, int sm_count, int* error_flag,
-                             cudaStream_t st);
+                             int N, int H, int W, int C, int R, int S, int stride, int pad, int act, Layout in_l, Layout out_l,
+                             int sm_count, int* error_flag, cudaStream_t st);
 bool depthwise_tma_supported(DType dt, int N, int H, int W, int C, int R, int S, int stride, int pad);
 cudaError_t launch_depthwise_tma(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
-                                 int N, int H, int W, int C, int R, int S, int stride, int pad, int act, int sm_count,
-                                 int* error_flag, cudaStream_t st);
+                                 int N, int H, int W, int C, int R, int S, int stride, int pad, int act, Layout in_l, Layout out_l,
+                                 int sm_count, int* error_flag, cudaStream_t st);
 cudaError_t launch_activation(const void* x, void* y, DType dt, size_t n, int act, cudaStream_t st);
 cudaError_t launch_scale_channels(const void* x, const void* gate, void* y, DType dt, int N, long long HW, int C, cudaStream_t st);
 cudaError_t launch_se_gate(const void* pooled, const float* w1, const float* b1, const float* w2, const float* b2, void* gate,

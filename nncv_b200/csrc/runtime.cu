@@ -12,6 +12,7 @@
 #include <condition_variable>
 #include <functional>
 #include <thread>
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -617,12 +618,16 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
 // `id`.  Built-in plans: ResNet-18 (constant order of Res18.mlir:12-109) and ResNet-50 (same rule,
 // torchvision v1.5 topology); any other plan arrives as text from the .mlir importer.
 struct PlanNode {
-  enum Kind { kConv = 0, kMaxPool = 1, kAvgPool = 2, kFc = 3 };
+  enum Kind { kConv = 0, kMaxPool = 1, kAvgPool = 2, kFc = 3, kDwConv = 4, kSe = 5 };
   int kind = kConv;
-  int id = 0, in = 0, res = -1;    // tensor ids; res: residual added before the ReLU (conv only)
+  int id = 0, in = 0, res = -1;    // tensor ids; res: residual added before the activation (conv only)
   int cin = 0, cout = 0, k = 1, stride = 1, pad = 0, relu = 0;
-  int has_bn = 0;
-  size_t off_w = 0, off_gamma = 0, off_beta = 0, off_mean = 0, off_var = 0, off_b = 0;
+  int act = 0;                     // activation code of the C ABI (0 none, 1 ReLU, 3 hard-swish, 5 SiLU); relu == (act == 1)
+  int has_bn = 0, has_bias = 0;    // conv: batch-norm, or a plain bias (off_b)
+  float eps = 1e-5f;               // batch-norm epsilon
+  int cr = 0;                      // se: squeezed width; off_w/off_b = first 1x1 conv, off_w2/off_b2 = second
+  size_t off_w = 0, off_gamma = 0, off_beta = 0, off_mean = 0, off_var = 0, off_b = 0, off_w2 = 0, off_b2 = 0;
+  int aux_idx = -1;                // dwconv / se / fc: index into the model's per-kind tables
   // derived when the model is built
   int conv_idx = -1;      // index into Model::convs
   int branch = -1;        // node of a 1x1 conv on the same input that may ride along in this conv's launch
@@ -728,7 +733,11 @@ Plan builtin_plan(int depth) {
 //   conv id=1 in=0 res=-1 cin=3 cout=64 k=7 stride=2 pad=3 relu=1 w=<off> gamma=<off> beta=<off> mean=<off> var=<off>
 //   maxpool id=2 in=1 k=3 stride=2 pad=1
 //   avgpool id=.. in=..
-//   fc id=.. in=.. cin=512 cout=1000 w=<off> b=<off>
+//   fc id=.. in=.. cin=512 cout=1000 w=<off> b=<off> [act=3]
+// and, for the MobileNetV3 fixture: conv fields act=<code> (instead of relu=1), b=<off> (a bias instead of
+// batch-norm), eps_bits=<fp32 bit pattern of the batch-norm epsilon when it is not 1e-5>;
+//   dwconv id=.. in=.. c=.. k=.. stride=.. pad=.. act=.. w=<off> gamma=.. beta=.. mean=.. var=..   (depthwise conv + BN + act)
+//   se id=.. in=.. c=.. cr=.. w1=<off> b1=<off> w2=<off> b2=<off>     (squeeze-and-excitation: scales its input)
 int parse_plan(const std::string& text, Plan* out) {
   Plan p;
   p.name = "plan";
@@ -772,6 +781,8 @@ int parse_plan(const std::string& text, Plan* out) {
     else if (tok[0] == "maxpool") n.kind = PlanNode::kMaxPool;
     else if (tok[0] == "avgpool") n.kind = PlanNode::kAvgPool;
     else if (tok[0] == "fc") n.kind = PlanNode::kFc;
+    else if (tok[0] == "dwconv") n.kind = PlanNode::kDwConv;
+    else if (tok[0] == "se") n.kind = PlanNode::kSe;
     else return fail(NNCV_B200_EINVAL, "plan line %d: unknown node kind \"%s\"", line_no, tok[0].c_str());
     for (size_t i = 1; i < tok.size(); ++i) {
       const size_t eq = tok[i].find('=');
@@ -786,9 +797,15 @@ int parse_plan(const std::string& text, Plan* out) {
       else if (k == "k") n.k = (int)v;
       else if (k == "stride") n.stride = (int)v;
       else if (k == "pad") n.pad = (int)v;
-      else if (k == "relu") n.relu = (int)v;
-      else if (k == "w") n.off_w = (size_t)v;
-      else if (k == "b") n.off_b = (size_t)v;
+      else if (k == "relu") { n.relu = (int)v; if (v) n.act = kActRelu; }
+      else if (k == "act") { n.act = (int)v; n.relu = v == kActRelu; }
+      else if (k == "c") n.cin = n.cout = (int)v;
+      else if (k == "cr") n.cr = (int)v;
+      else if (k == "w" || k == "w1") n.off_w = (size_t)v;
+      else if (k == "b" || k == "b1") { n.off_b = (size_t)v; n.has_bias = 1; }
+      else if (k == "w2") n.off_w2 = (size_t)v;
+      else if (k == "b2") n.off_b2 = (size_t)v;
+      else if (k == "eps_bits") { const uint32_t bits = (uint32_t)v; memcpy(&n.eps, &bits, 4); }
       else if (k == "gamma") { n.off_gamma = (size_t)v; n.has_bn = 1; }
       else if (k == "beta") n.off_beta = (size_t)v;
       else if (k == "mean") n.off_mean = (size_t)v;
@@ -822,8 +839,12 @@ int finalize_plan(Plan& p, bool act16) {
         return fail(NNCV_B200_EINVAL, "plan: conv node %zu has %d input channels, its input tensor has %d", i, n.cin, cin);
       if (!in_range(n.off_w, (size_t)n.cout * n.cin * n.k * n.k) ||
           (n.has_bn && (!in_range(n.off_gamma, n.cout) || !in_range(n.off_beta, n.cout) || !in_range(n.off_mean, n.cout) ||
-                        !in_range(n.off_var, n.cout))))
+                        !in_range(n.off_var, n.cout))) ||
+          (!n.has_bn && n.has_bias && !in_range(n.off_b, n.cout)))
         return fail(NNCV_B200_EINVAL, "plan: conv node %zu names parameters outside the blob", i);
+      if (n.act != kActNone && n.act != kActRelu && n.act != kActHardSwish && n.act != kActSilu)
+        return fail(NNCV_B200_EINVAL, "plan: conv node %zu has activation %d; none, ReLU, hard-swish and SiLU can follow a convolution", i, n.act);
+      if (!(n.eps > 0.f && n.eps < 1.f)) return fail(NNCV_B200_EINVAL, "plan: conv node %zu has a bad batch-norm epsilon", i);
       if (n.res >= 0) {
         if (!channels.count(n.res) || channels[n.res] != n.cout)
           return fail(NNCV_B200_EINVAL, "plan: conv node %zu adds tensor %d, which is missing or has other channels", i, n.res);
@@ -838,15 +859,38 @@ int finalize_plan(Plan& p, bool act16) {
       if (n.in == 0) return fail(NNCV_B200_EINVAL, "plan: bad average-pool node %zu", i);
       n.cin = n.cout = cin;
       channels[n.id] = cin;
+    } else if (n.kind == PlanNode::kDwConv) {
+      if (n.in == 0 || n.cin != cin || n.k <= 0 || n.stride <= 0 || n.pad < 0 || !n.has_bn || !(n.eps > 0.f && n.eps < 1.f))
+        return fail(NNCV_B200_EINVAL, "plan: depthwise node %zu must read a %d-channel activation and carry a batch-norm", i, n.cin);
+      if (!in_range(n.off_w, (size_t)n.cin * n.k * n.k) || !in_range(n.off_gamma, n.cin) || !in_range(n.off_beta, n.cin) ||
+          !in_range(n.off_mean, n.cin) || !in_range(n.off_var, n.cin))
+        return fail(NNCV_B200_EINVAL, "plan: depthwise node %zu names parameters outside the blob", i);
+      if (n.act != kActNone && n.act != kActRelu && n.act != kActHardSwish && n.act != kActSilu)
+        return fail(NNCV_B200_EINVAL, "plan: depthwise node %zu has activation %d", i, n.act);
+      channels[n.id] = cin;
+    } else if (n.kind == PlanNode::kSe) {
+      if (n.in == 0 || n.cin != cin || n.cr <= 0 || (size_t)(n.cin + n.cr) * sizeof(float) > 48 * 1024)
+        return fail(NNCV_B200_EINVAL, "plan: squeeze-and-excitation node %zu does not match its %d-channel input", i, cin);
+      if (!in_range(n.off_w, (size_t)n.cr * n.cin) || !in_range(n.off_b, n.cr) || !in_range(n.off_w2, (size_t)n.cr * n.cin) ||
+          !in_range(n.off_b2, n.cin))
+        return fail(NNCV_B200_EINVAL, "plan: squeeze-and-excitation node %zu names parameters outside the blob", i);
+      channels[n.id] = cin;
     } else {
-      if (n.cin != cin || n.cout != p.out_features || i + 1 != p.nodes.size() || !in_range(n.off_w, (size_t)n.cout * n.cin) ||
-          !in_range(n.off_b, n.cout) || producer.count(n.in) == 0 || p.nodes[producer[n.in]].kind != PlanNode::kAvgPool)
-        return fail(NNCV_B200_EINVAL, "plan: the FC node must come last, read a global average pool and match the output size");
+      const int pk = producer.count(n.in) ? p.nodes[producer[n.in]].kind : -1;
+      if (n.cin != cin || !in_range(n.off_w, (size_t)n.cout * n.cin) || !in_range(n.off_b, n.cout) ||
+          (pk != PlanNode::kAvgPool && pk != PlanNode::kFc))
+        return fail(NNCV_B200_EINVAL, "plan: FC node %zu must read a global average pool or another FC layer of %d features", i, n.cin);
+      if (i + 1 == p.nodes.size() ? (n.cout != p.out_features || n.act != kActNone)
+                                  : (n.act != kActNone && n.act != kActRelu && n.act != kActHardSwish))
+        return fail(NNCV_B200_EINVAL, "plan: the last FC node must match the output size and have no activation");
       channels[n.id] = n.cout;
     }
     producer[n.id] = (int)i;
   }
   if (p.nodes.back().kind != PlanNode::kFc) return fail(NNCV_B200_EINVAL, "plan: the last node must be the FC layer");
+  for (const PlanNode& n : p.nodes)
+    if (n.kind == PlanNode::kSe && readers[n.in] != 1)
+      return fail(NNCV_B200_EINVAL, "plan: tensor %d is scaled in place by squeeze-and-excitation node %d but has other readers", n.in, n.id);
   if (!act16) return NNCV_B200_OK;
   for (size_t i = 0; i < p.nodes.size(); ++i) {
     PlanNode& a = p.nodes[i];
@@ -885,10 +929,15 @@ struct Model {
   DType act_dt = kF16;       // activation / compute type
   DevBuf blob;               // raw params on the device
   DevBuf folded;             // scale/shift for every group, fp32
-  DevBuf fc_bias;            // fp32
+  DevBuf aux;                // fp32 copies of the small tensors: biases, depthwise filters, squeeze-and-excitation weights
   std::vector<std::unique_ptr<nncv_b200_conv>> convs;
   std::vector<float*> scale, shift;
-  std::unique_ptr<nncv_b200_conv> fc;
+  std::vector<std::unique_ptr<nncv_b200_conv>> fcs;   // FC layers in plan order (PlanNode::aux_idx)
+  std::vector<const float*> fc_bias;
+  struct DwW { const float *w, *scale, *shift; };
+  std::vector<DwW> dws;                                // depthwise nodes
+  struct SeW { const float *w1, *b1, *w2, *b2; };
+  std::vector<SeW> ses;                                // squeeze-and-excitation nodes
   int stem_node = -1;        // conv node served by the fused stem + max-pool kernel, or -1
   const void* host_blob_id = nullptr;  // pointer identity of the blob the plan was built from
   // per-shape workspace
@@ -957,26 +1006,59 @@ int model_build(Plan plan, const void* host_blob, size_t n_elements, size_t ele_
   const DType pdt = dt_from_width(ele_width);
   auto at = [&](size_t off) { return (const void*)(base + off * ele_width); };
 
-  size_t nfold = 0;
-  for (auto& n : m->plan.nodes)
-    if (n.kind == PlanNode::kConv) nfold += 2 * (size_t)n.cout;
+  size_t nfold = 0, naux = 0;
+  for (auto& n : m->plan.nodes) {
+    // every small tensor starts on a 16-byte boundary (the conv epilogues read scale / shift as vectors)
+    if (n.kind == PlanNode::kConv) { nfold += 2 * (size_t)n.cout; if (!n.has_bn && n.has_bias) naux += n.cout + 4; }
+    else if (n.kind == PlanNode::kDwConv) { nfold += 2 * (size_t)n.cin; naux += (size_t)n.cin * n.k * n.k + 4; }
+    else if (n.kind == PlanNode::kSe) naux += 2 * (size_t)n.cr * n.cin + n.cr + n.cin + 16;
+    else if (n.kind == PlanNode::kFc) naux += n.cout + 4;
+  }
   rc = m->folded.reserve(nfold * sizeof(float) + 16);
   if (rc) return rc;
+  rc = m->aux.reserve(naux * sizeof(float) + 16);
+  if (rc) return rc;
   float* fp = (float*)m->folded.p;
+  float* ap = (float*)m->aux.p;
+  auto to_f32 = [&](size_t off, size_t count) -> const float* {   // a small tensor of the blob as fp32
+    float* dst = ap;
+    ap += (count + 3) / 4 * 4;
+    if (launch_convert(at(off), pdt, dst, kF32, count, st) != cudaSuccess) return nullptr;
+    return dst;
+  };
   for (size_t i = 0; i < m->plan.nodes.size(); ++i) {
     PlanNode& g = m->plan.nodes[i];
     if (g.kind == PlanNode::kFc) {
       // FC: weight [out, in] is already "[Kout][C]" (the forward's transpose generic,
       // Res18.mlir:617-620, is absorbed by reading it K-major); bias in fp32.
       if (g.cin % 8 != 0) return fail(NNCV_B200_EINVAL, "plan: FC input width %d must be a multiple of 8", g.cin);
-      m->fc = std::make_unique<nncv_b200_conv>();
-      m->fc->device = g_dev.id;
-      m->fc->Kout = g.cout; m->fc->C = g.cin; m->fc->Cpad = g.cin; m->fc->dtype = m->act_dt;
-      m->fc->raw = at(g.off_w); m->fc->raw_dt = pdt;
-      m->fc->sn = g.cin; m->fc->sc = 1; m->fc->stap = 1;
-      rc = m->fc_bias.reserve((size_t)g.cout * sizeof(float));
-      if (rc) return rc;
-      LAUNCH(launch_convert(at(g.off_b), pdt, m->fc_bias.p, kF32, (size_t)g.cout, st));
+      auto fc = std::make_unique<nncv_b200_conv>();
+      fc->device = g_dev.id;
+      fc->Kout = g.cout; fc->C = g.cin; fc->Cpad = g.cin; fc->dtype = m->act_dt;
+      fc->raw = at(g.off_w); fc->raw_dt = pdt;
+      fc->sn = g.cin; fc->sc = 1; fc->stap = 1;
+      g.aux_idx = (int)m->fcs.size();
+      m->fcs.push_back(std::move(fc));
+      m->fc_bias.push_back(to_f32(g.off_b, (size_t)g.cout));
+      if (!m->fc_bias.back()) return fail(NNCV_B200_ECUDA, "converting the FC bias failed");
+      continue;
+    }
+    if (g.kind == PlanNode::kDwConv) {
+      // depthwise filter [C,1,k,k] in fp32; batch-norm folded like a convolution's
+      Model::DwW w{to_f32(g.off_w, (size_t)g.cin * g.k * g.k), fp, fp + g.cin};
+      if (!w.w) return fail(NNCV_B200_ECUDA, "converting a depthwise filter failed");
+      LAUNCH(launch_bn_fold(at(g.off_gamma), at(g.off_beta), at(g.off_mean), at(g.off_var), pdt, g.cin, g.eps, fp, fp + g.cin, st));
+      fp += 2 * g.cin;
+      g.aux_idx = (int)m->dws.size();
+      m->dws.push_back(w);
+      continue;
+    }
+    if (g.kind == PlanNode::kSe) {
+      Model::SeW w{to_f32(g.off_w, (size_t)g.cr * g.cin), to_f32(g.off_b, (size_t)g.cr), to_f32(g.off_w2, (size_t)g.cr * g.cin),
+                   to_f32(g.off_b2, (size_t)g.cin)};
+      if (!w.w1 || !w.b1 || !w.w2 || !w.b2) return fail(NNCV_B200_ECUDA, "converting squeeze-and-excitation weights failed");
+      g.aux_idx = (int)m->ses.size();
+      m->ses.push_back(w);
       continue;
     }
     if (g.kind != PlanNode::kConv) continue;
@@ -994,8 +1076,13 @@ int model_build(Plan plan, const void* host_blob, size_t n_elements, size_t ele_
       m->scale.push_back(fp);
       m->shift.push_back(fp + g.cout);
       LAUNCH(launch_bn_fold(at(g.off_gamma), at(g.off_beta), at(g.off_mean), at(g.off_var), pdt,
-                            g.cout, fp, fp + g.cout, st));
+                            g.cout, g.eps, fp, fp + g.cout, st));
       fp += 2 * g.cout;
+    } else if (g.has_bias) {
+      const float* b = to_f32(g.off_b, (size_t)g.cout);
+      if (!b) return fail(NNCV_B200_ECUDA, "converting a convolution bias failed");
+      m->scale.push_back(nullptr);
+      m->shift.push_back(const_cast<float*>(b));
     } else {
       m->scale.push_back(nullptr);
       m->shift.push_back(nullptr);
@@ -1265,7 +1352,62 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
         tens[bn.id] = d;
       }
       if (!done && (rc = run(n, in, o, res))) return rc;
+      if (n.act > kActRelu && begin_op({o.p})) {
+        // hard-swish / SiLU: an elementwise pass over the tensor in place; both map 0 to 0, so the zero pads of a
+        // padded layout stay zero
+        const size_t elems = (size_t)layout_slots(o.l, N) * o.c;
+        prof_begin(3, 0, 2.0 * aes * elems, (int)(elems / o.c), o.c, 0, 4, st);
+        LAUNCH(launch_activation(o.p, o.p, adt, elems, n.act, st));
+        prof_end(st);
+      }
       tens[n.id] = o;
+    } else if (n.kind == PlanNode::kDwConv) {
+      // depthwise conv + folded batch-norm + activation in one kernel (MobileNetV3.mlir:296-318)
+      const int oh = (in.h + 2 * n.pad - n.k) / n.stride + 1, ow = (in.w + 2 * n.pad - n.k) / n.stride + 1;
+      if (oh <= 0 || ow <= 0) return fail(NNCV_B200_EINVAL, "input %dx%d too small for the network", H, W);
+      Ten o;
+      o.l = lay(oh, ow); o.h = oh; o.w = ow; o.c = in.c;
+      if ((rc = next_act(m, N, oh, ow, in.c, o.l, st, &o.p))) return rc;
+      if (begin_op({in.p})) {
+        const Model::DwW& w = m.dws[n.aux_idx];
+        prof_begin(3, 2.0 * N * oh * ow * in.c * n.k * n.k, aes * in.c * N * ((double)in.h * in.w + (double)oh * ow), N * oh * ow, in.c,
+                   n.k * n.k, 5, st);
+        if (launch_depthwise(in.p, w.w, kF32, w.scale, w.shift, o.p, adt, N, in.h, in.w, in.c, n.k, n.k, n.stride, n.pad, n.act, in.l,
+                             o.l, g_dev.sm_count, g_dev.error_flag, st) != cudaSuccess) {
+          cudaGetLastError();
+          return fail(NNCV_B200_EINVAL, "depthwise node %d: %d channels are not a multiple of the 16-byte vector", n.id, in.c);
+        }
+        ++g_launches;
+        prof_end(st);
+      }
+      tens[n.id] = o;
+    } else if (n.kind == PlanNode::kSe) {
+      // squeeze-and-excitation (MobileNetV3.mlir:319-389): pooled = mean(x); gate = hard-sigmoid(W2 relu(W1 pooled + b1) + b2);
+      // x *= gate, in place (the plan checker has made sure nothing else reads the unscaled tensor)
+      const Model::SeW& w = m.ses[n.aux_idx];
+      Ten pooled, gate;
+      pooled.l = gate.l = dense_layout(1, 1);
+      pooled.h = pooled.w = gate.h = gate.w = 1;
+      pooled.c = gate.c = in.c;
+      if ((rc = next_act(m, N, 1, 1, in.c, pooled.l, st, &pooled.p))) return rc;
+      if ((rc = next_act(m, N, 1, 1, in.c, gate.l, st, &gate.p))) return rc;
+      if (begin_op({in.p})) {
+        prof_begin(3, 0, aes * in.c * N * (in.h * in.w + 1.0), N * in.h * in.w, in.c, 0, 2, st);
+        LAUNCH(launch_avgpool_nhwc(in.p, pooled.p, adt, N, in.h, in.w, in.c, in.l, st));
+        prof_end(st);
+      }
+      if (begin_op({pooled.p})) {
+        prof_begin(3, 4.0 * N * in.c * n.cr, 8.0 * in.c * n.cr, N, in.c, n.cr, 6, st);
+        LAUNCH(launch_se_gate(pooled.p, w.w1, w.b1, w.w2, w.b2, gate.p, adt, N, in.c, n.cr, st));
+        prof_end(st);
+      }
+      if (begin_op({in.p, gate.p})) {
+        const long long slots = (long long)in.l.img_rows * in.l.pitch;
+        prof_begin(3, 0, 2.0 * aes * in.c * N * slots, (int)(N * slots), in.c, 0, 7, st);
+        LAUNCH(launch_scale_channels(in.p, gate.p, in.p, adt, N, slots, in.c, st));
+        prof_end(st);
+      }
+      tens[n.id] = in;
     } else if (n.kind == PlanNode::kMaxPool) {
       const int oh = (in.h + 2 * n.pad - n.k) / n.stride + 1, ow = (in.w + 2 * n.pad - n.k) / n.stride + 1;
       if (oh <= 0 || ow <= 0) return fail(NNCV_B200_EINVAL, "input %dx%d too small for the network", H, W);
@@ -1291,16 +1433,30 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
       tens[n.id] = o;
     } else {
       // FC (Res18.mlir:617-628)
+      nncv_b200_conv* fc = m.fcs[n.aux_idx].get();
+      const float* bias = m.fc_bias[n.aux_idx];
+      if (ni + 1 != m.plan.nodes.size()) {
+        // a hidden FC layer (MobileNetV3.mlir:1784-1845): [N, cin] -> [N, cout] in the activation type, then its activation
+        Ten o;
+        o.l = dense_layout(1, 1); o.h = o.w = 1; o.c = n.cout;
+        if ((rc = next_act(m, N, 1, 1, n.cout, o.l, st, &o.p))) return rc;
+        if (begin_op({in.p}) &&
+            (rc = conv_run(fc, in.p, dense_layout(1, 1), o.p, dense_layout(1, 1), N, 1, 1, nullptr, bias, nullptr, n.act == kActRelu, adt,
+                           n.cout, st)))
+          return rc;
+        if (n.act > kActRelu && begin_op({o.p})) LAUNCH(launch_activation(o.p, o.p, adt, (size_t)N * n.cout, n.act, st));
+        tens[n.id] = o;
+        continue;
+      }
       const int of = m.plan.out_features;
       if (!begin_op({in.p})) return NNCV_B200_OK;   // the planning pass ends with the last reader of an activation tensor
       if (m.io_dt == adt && adt != kF32) {
         // 16-bit logits wanted and computed in the same type: the FC epilogue rounds once, exactly as
         // the fp32 -> io conversion kernel would, and that kernel is not launched
-        return conv_run(m.fc.get(), in.p, dense_layout(1, 1), m.logits_io.p, dense_layout(1, 1), N, 1, 1, nullptr,
-                        (const float*)m.fc_bias.p, nullptr, 0, adt, of, st);
+        return conv_run(fc, in.p, dense_layout(1, 1), m.logits_io.p, dense_layout(1, 1), N, 1, 1, nullptr, bias, nullptr, 0, adt, of,
+                        st);
       }
-      rc = conv_run(m.fc.get(), in.p, dense_layout(1, 1), m.logits32.p, dense_layout(1, 1), N, 1, 1, nullptr,
-                    (const float*)m.fc_bias.p, nullptr, 0, kF32, of, st);
+      rc = conv_run(fc, in.p, dense_layout(1, 1), m.logits32.p, dense_layout(1, 1), N, 1, 1, nullptr, bias, nullptr, 0, kF32, of, st);
       if (rc) return rc;
       if (m.io_dt != kF32)
         LAUNCH(launch_convert(m.logits32.p, kF32, m.logits_io.p, m.io_dt, (size_t)N * of, st));
@@ -1794,10 +1950,25 @@ long long nncv_b200_plan_text(const char* net, char* buf, size_t cap) {
       snprintf(line, sizeof(line), "conv id=%d in=%d res=%d cin=%d cout=%d k=%d stride=%d pad=%d relu=%d w=%zu", n.id, n.in, n.res,
                n.cin, n.cout, n.k, n.stride, n.pad, n.relu, n.off_w);
       t += line;
+      if (n.act > kActRelu) {
+        snprintf(line, sizeof(line), " act=%d", n.act);
+        t += line;
+      }
       if (n.has_bn) {
         snprintf(line, sizeof(line), " gamma=%zu beta=%zu mean=%zu var=%zu", n.off_gamma, n.off_beta, n.off_mean, n.off_var);
         t += line;
+      } else if (n.has_bias) {
+        snprintf(line, sizeof(line), " b=%zu", n.off_b);
+        t += line;
       }
+    } else if (n.kind == PlanNode::kDwConv) {
+      snprintf(line, sizeof(line), "dwconv id=%d in=%d c=%d k=%d stride=%d pad=%d act=%d w=%zu gamma=%zu beta=%zu mean=%zu var=%zu",
+               n.id, n.in, n.cin, n.k, n.stride, n.pad, n.act, n.off_w, n.off_gamma, n.off_beta, n.off_mean, n.off_var);
+      t += line;
+    } else if (n.kind == PlanNode::kSe) {
+      snprintf(line, sizeof(line), "se id=%d in=%d c=%d cr=%d w1=%zu b1=%zu w2=%zu b2=%zu", n.id, n.in, n.cin, n.cr, n.off_w, n.off_b,
+               n.off_w2, n.off_b2);
+      t += line;
     } else if (n.kind == PlanNode::kMaxPool) {
       snprintf(line, sizeof(line), "maxpool id=%d in=%d k=%d stride=%d pad=%d", n.id, n.in, n.k, n.stride, n.pad);
       t += line;
@@ -1806,6 +1977,16 @@ long long nncv_b200_plan_text(const char* net, char* buf, size_t cap) {
       t += line;
     } else {
       snprintf(line, sizeof(line), "fc id=%d in=%d cin=%d cout=%d w=%zu b=%zu", n.id, n.in, n.cin, n.cout, n.off_w, n.off_b);
+      t += line;
+      if (n.act) {
+        snprintf(line, sizeof(line), " act=%d", n.act);
+        t += line;
+      }
+    }
+    if ((n.kind == PlanNode::kConv || n.kind == PlanNode::kDwConv) && n.has_bn && fabsf(n.eps - 1e-5f) > 1e-9f) {
+      uint32_t bits;
+      memcpy(&bits, &n.eps, 4);
+      snprintf(line, sizeof(line), " eps_bits=%u", bits);
       t += line;
     }
     t += "\n";
@@ -2265,7 +2446,7 @@ int nncv_b200_depthwise_conv_nhwc(const void* in, const void* weights, int w_dty
       dtype > 2 || act < 0 || act > 5)
     return fail(NNCV_B200_EINVAL, "depthwise_conv: bad argument");
   if (launch_depthwise(in, weights, (DType)w_dtype, scale, shift, out, (DType)dtype, N, H, W, C, R, S, stride, pad, act,
-                       g_dev.sm_count, g_dev.error_flag, (cudaStream_t)stream) != cudaSuccess) {
+                       Layout{0, 0, 0}, Layout{0, 0, 0}, g_dev.sm_count, g_dev.error_flag, (cudaStream_t)stream) != cudaSuccess) {
     cudaGetLastError();
     return fail(NNCV_B200_EINVAL, "depthwise_conv: C must be a multiple of %d, weights fp32 (or fp16 with fp16 activations), output not empty",
                 16 / (int)dtype_size((DType)dtype));
@@ -2351,7 +2532,7 @@ int nncv_b200_bn_fold(const void* gamma, const void* beta, const void* mean, con
   int rc = device_init();
   if (rc) return rc;
   if (!gamma || !beta || !mean || !var || !scale || !shift || C <= 0) return fail(NNCV_B200_EINVAL, "bn_fold: bad argument");
-  LAUNCH(launch_bn_fold(gamma, beta, mean, var, (DType)dtype, C, scale, shift, (cudaStream_t)stream));
+  LAUNCH(launch_bn_fold(gamma, beta, mean, var, (DType)dtype, C, 1e-5f, scale, shift, (cudaStream_t)stream));
   return ok();
 }
 

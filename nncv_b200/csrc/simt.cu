@@ -372,11 +372,11 @@ __global__ void relayout_kernel(const uint4* __restrict__ src, Layout sl, uint4*
 }
 
 template <typename T>
-__global__ void bn_fold_kernel(const T* gamma, const T* beta, const T* mean, const T* var, int C,
+__global__ void bn_fold_kernel(const T* gamma, const T* beta, const T* mean, const T* var, int C, float eps,
                                float* scale, float* shift) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
-  const float eps = (float)1e-5;  // arith.truncf of the f64 constant (Res18.mlir:113,129)
+  // eps: arith.truncf of the module's f64 constant (1e-5 in Res18.mlir:113,129; 1e-3 in MobileNetV3.mlir)
   const float rs = 1.0f / sqrtf(to_f<T>(var[c]) + eps);
   const float sc = to_f<T>(gamma[c]) * rs;
   scale[c] = sc;
@@ -499,13 +499,13 @@ cudaError_t launch_relayout(const void* src, Layout src_l, void* dst, Layout dst
 }
 
 cudaError_t launch_bn_fold(const void* gamma, const void* beta, const void* mean,
-                           const void* var, DType dt, int C, float* scale, float* shift,
+                           const void* var, DType dt, int C, float eps, float* scale, float* shift,
                            cudaStream_t stream) {
   return by_dtype(dt, [&](auto tag) {
     using T = decltype(tag);
     bn_fold_kernel<T><<<(C + 127) / 128, 128, 0, stream>>>(
         static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<const T*>(mean),
-        static_cast<const T*>(var), C, scale, shift);
+        static_cast<const T*>(var), C, eps, scale, shift);
     return cudaGetLastError();
   });
 }

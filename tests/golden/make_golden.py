@@ -81,6 +81,7 @@ def plans():
     mlir_import.import_mlir_file(os.path.join(REF, "tests/Nets/Res18.mlir")).write(os.path.join(HERE, "res18_from_mlir.plan"))
     half = mlir_import.import_mlir_file(os.path.join(REF, "tests/Nets/Res18-half.mlir"))
     assert half.to_text() == open(os.path.join(HERE, "res18_from_mlir.plan")).read()
+    mlir_import.import_mlir_file(os.path.join(REF, "tests/Nets/MobileNetV3.mlir")).write(os.path.join(HERE, "mobilenetv3_from_mlir.plan"))
 
 
 if __name__ == "__main__":

@@ -70,6 +70,44 @@ def test_small_non_resnet_module(tmp_path, compute):
         assert G.rel_l2(got, ref) <= (1e-4 if compute == F32 else 1e-2)
 
 
+@pytest.mark.parametrize("compute", [F32, F16])
+def test_small_mobile_module(tmp_path, compute):
+    """conv + hard-swish, depthwise conv + BN + ReLU / hard-swish, squeeze-and-excitation (scaling in place), a residual
+    add without activation and an FC + hard-swish -> FC head, imported from linalg text in the MobileNetV3 fixture's spellings."""
+    text = mi.import_mlir(P.small_mobile_mlir()).to_text()
+    total, out, nodes = P.parse_plan_text(text)
+    blob = P.random_blob(total, nodes, seed=11)
+    bin_path = str(tmp_path / "mobile.bin")
+    write_model_bin(bin_path, nodes, blob)
+    rt.load("plan:" + text, bin_path, compute)
+    for n, h, w in ((2, 64, 48), (3, 97, 131), (1, 160, 192)):   # the last one pools a map of 1920 pixels in its first SE block
+        x = random_input(n, h, w, 13, "normal")
+        got = np.zeros((n, out), np.float32)
+        rt.forward(got, x)
+        ref = P.run_plan_cpu(nodes, blob, x, ob, acc64=True)
+        assert got.shape == (n, 10) and np.isfinite(got).all()
+        assert G.rel_l2(got, ref) <= (1e-4 if compute == F32 else 1e-2)
+
+
+@pytest.mark.parametrize("compute,n,hw", [(F32, 1, 128), (F16, 4, 224), (F16, 2, 256)])
+def test_mobilenetv3_from_the_reference_module(tmp_path, golden_dir, compute, n, hw):
+    """Plan = what the importer read from tests/Nets/MobileNetV3.mlir (210 tensor constants, 46 nodes); weights = a
+    container with exactly those tensors in module order, seeded random values."""
+    plan_path = os.path.join(golden_dir, "mobilenetv3_from_mlir.plan")
+    total, out, nodes = P.parse_plan_text(open(plan_path).read())
+    blob = P.random_blob(total, nodes, seed=4)
+    bin_path = str(tmp_path / "model.bin")
+    write_model_bin(bin_path, nodes, blob)
+    rt.load(plan_path, bin_path, compute)
+    x = random_input(n, hw, hw, 5, "normal")
+    got = np.zeros((n, 1000), np.float32)
+    rt.forward(got, x)
+    ref = P.run_plan_cpu(nodes, blob, x, ob, acc64=compute == F32)
+    assert np.isfinite(got).all()
+    assert G.rel_l2(got, ref) <= (1e-4 if compute == F32 else 1e-2)
+    assert (got.argmax(1) == ref.argmax(1)).all()
+
+
 def test_weights_that_do_not_match_the_plan_are_refused(tmp_path):
     text = mi.import_mlir(P.small_net_mlir()).to_text()
     total, out, nodes = P.parse_plan_text(text)
