@@ -116,6 +116,7 @@ struct TconvArgs {
   int b_rows = 0;
   DType ab = kF16, out_dtype = kF16;
   int relu = 0;
+  int act = 0;               // 0, or kActHardSwish / kActSilu fused into the epilogue (16-bit outputs only)
   int sm_count = 0;
   int* error_flag = nullptr;
 };
@@ -208,6 +209,11 @@ enum Activation : int { kActNone = 0, kActRelu = 1, kActHardSigmoid = 2, kActHar
 cudaError_t launch_depthwise(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
                              int N, int H, int W, int C, int R, int S, int stride, int pad, int act, Layout in_l, Layout out_l,
                              int sm_count, int* error_flag, cudaStream_t st);
+// 3x3 convolution on the 3-channel NCHW network input, 16 .. 64 output channels, scale / shift / activation, NHWC
+// output in `out_l` (16-bit activations); w: fp32 [Cout][3][3][3]
+bool stem3x3_supported(int Cin, int Cout, int R, int S, DType act_dt, int act);
+cudaError_t launch_stem3x3(const void* src, DType src_dt, const float* w, const float* scale, const float* shift, void* dst, DType dt,
+                           Layout out_l, int N, int H, int W, int Cout, int stride, int pad, int act, cudaStream_t st);
 bool depthwise_tma_supported(DType dt, int N, int H, int W, int C, int R, int S, int stride, int pad);
 cudaError_t launch_depthwise_tma(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
                                  int N, int H, int W, int C, int R, int S, int stride, int pad, int act, Layout in_l, Layout out_l,

@@ -340,6 +340,8 @@ struct nncv_b200_conv {
   DType raw_dt = kF32;
   long long sn = 0, sc = 0, stap = 0;
   DevBuf raw_owned;                                // set when create() copied the weights
+  int want_act = 0;       // set by the plan executor: activation beyond ReLU it would like fused (hard-swish, SiLU)
+  bool act_done = false;  // set by conv_run when the kernel it launched applied want_act
   std::map<int, std::unique_ptr<DevBuf>> packed;   // tcgen05 path: per N-tile width
   DevBuf w_f32;                                    // fp32 path: [Kout][R*S][Cpad]
   bool w_f32_ready = false;
@@ -355,15 +357,20 @@ struct nncv_b200_conv {
 
 namespace {
 
-int conv_prepare(nncv_b200_conv* c, int bn, cudaStream_t st, const void** wpack) {
-  auto it = c->packed.find(bn);
+// per_tap: the k blocks of 64 belong to one filter tap each (the TMA-fed kernels read 64 channels of one
+// tap per block, so every tap's channels are padded to a multiple of 64 with zeros); otherwise the taps'
+// channels are laid end to end (the gather kernel).  The two coincide when Cpad is a multiple of 64.
+int conv_prepare(nncv_b200_conv* c, int bn, cudaStream_t st, const void** wpack, bool per_tap = false) {
+  const int cpad = (per_tap && c->Cpad % 64 != 0) ? (c->Cpad + 63) / 64 * 64 : c->Cpad;
+  const int key = bn + (cpad != c->Cpad ? (1 << 20) : 0);
+  auto it = c->packed.find(key);
   if (it == c->packed.end()) {
     auto buf = std::make_unique<DevBuf>();
-    int rc = buf->reserve(packed_weight_bytes(c->Kout, c->Cpad, c->R, c->S, bn));
+    int rc = buf->reserve(packed_weight_bytes(c->Kout, cpad, c->R, c->S, bn));
     if (rc) return rc;
-    LAUNCH(launch_pack_weights(c->raw, c->raw_dt, c->sn, c->sc, c->stap, c->Kout, c->C, c->Cpad,
+    LAUNCH(launch_pack_weights(c->raw, c->raw_dt, c->sn, c->sc, c->stap, c->Kout, c->C, cpad,
                                c->R * c->S, bn, c->dtype, buf->p, st));
-    it = c->packed.emplace(bn, std::move(buf)).first;
+    it = c->packed.emplace(key, std::move(buf)).first;
   }
   *wpack = it->second->p;
   return NNCV_B200_OK;
@@ -426,13 +433,12 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
   // the per-tap kernel.  Which one, and with which tile, is timed once per (plan, shape).
   const bool sv_ok = c->algo == 2 && in_l.off == 1 && out_l.off == 1 && out_dt == c->dtype && ldo == c->Kout;
   if (c->algo == 2 && !sv_ok) return fail(NNCV_B200_EINVAL, "conv3x3: needs shared-pad NHWC input and output");
-  const bool tc_ok = !g_force_gather && !c->force_gather && tconv_supported(c->Cpad, c->Kout, out_dt, ldo) &&
-                     (out_dt == kF32 ? 32 : 64) <= c->Kout;
+  const bool tc_ok = !g_force_gather && !c->force_gather && tconv_supported(c->Cpad, c->Kout, out_dt, ldo) && c->Kout >= 8;
   if (sv_ok || (c->algo == 0 && tc_ok)) {
     auto launch_choice = [&](const ConvChoice& ch, bool profile) -> int {
       const void* wpack = nullptr;
       // the CTA-pair kernels (7: shifted-view, 8: per-tap) read weights packed for half their N tile
-      int rc = conv_prepare(c, (ch.kernel == 7 || ch.kernel == 8) ? (ch.bn / 2 < 64 ? 64 : ch.bn / 2) : ch.bn, st, &wpack);
+      int rc = conv_prepare(c, (ch.kernel == 7 || ch.kernel == 8) ? (ch.bn / 2 < 64 ? 64 : ch.bn / 2) : ch.bn, st, &wpack, true);
       if (rc) return rc;
       if (ch.kernel == 7) {   // CTA-pair shifted-view kernel
         Conv3x3Args a;
@@ -463,13 +469,14 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
       a.in = in; a.wpack = wpack; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
       a.pair = ch.kernel == 8;
       if (fb) {
-        rc = conv_prepare(fb->conv, a.pair ? 64 : 128, st, &a.wpack2);
+        rc = conv_prepare(fb->conv, a.pair ? 64 : 128, st, &a.wpack2, true);
         if (rc) return rc;
         a.scale2 = fb->scale; a.shift2 = fb->shift; a.out2 = fb->out;
       }
       a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
       a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.in_l = in_l; a.out_l = out_l;
       a.bn = ch.bn; a.resident = ch.resident; a.ab = c->dtype; a.out_dtype = out_dt; a.relu = relu;
+      if (c->want_act > kActRelu && out_dt != kF32 && !fb) { a.act = c->want_act; c->act_done = true; }
       a.sm_count = g_dev.sm_count; a.error_flag = g_dev.error_flag;
       if (profile) prof_begin(5, flops, bytes, (int)M, c->Kout, c->C * c->R * c->S, ch.bn * 10 + ch.resident + (a.pair ? 2 : 0), st);
       ++g_launches;
@@ -586,6 +593,7 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
       }
       ch = it->second;
     }
+    c->act_done = false;   // candidates timed above may have set it; only the launch that stays counts
     if (launch_choice(ch, true) != 0)
       return fail(NNCV_B200_ECUDA, "conv launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     return NNCV_B200_OK;
@@ -938,6 +946,8 @@ struct Model {
   std::vector<DwW> dws;                                // depthwise nodes
   struct SeW { const float *w1, *b1, *w2, *b2; };
   std::vector<SeW> ses;                                // squeeze-and-excitation nodes
+  int stem3_node = -1;                                 // 3x3 conv on the network input served by the direct kernel, or -1
+  const float* stem3_w = nullptr;                      // its filter, fp32 [Cout][27]
   int stem_node = -1;        // conv node served by the fused stem + max-pool kernel, or -1
   const void* host_blob_id = nullptr;  // pointer identity of the blob the plan was built from
   // per-shape workspace
@@ -1009,7 +1019,11 @@ int model_build(Plan plan, const void* host_blob, size_t n_elements, size_t ele_
   size_t nfold = 0, naux = 0;
   for (auto& n : m->plan.nodes) {
     // every small tensor starts on a 16-byte boundary (the conv epilogues read scale / shift as vectors)
-    if (n.kind == PlanNode::kConv) { nfold += 2 * (size_t)n.cout; if (!n.has_bn && n.has_bias) naux += n.cout + 4; }
+    if (n.kind == PlanNode::kConv) {
+      nfold += 2 * (size_t)n.cout;
+      if (!n.has_bn && n.has_bias) naux += n.cout + 4;
+      if (n.in == 0) naux += (size_t)n.cout * 27 + 4;
+    }
     else if (n.kind == PlanNode::kDwConv) { nfold += 2 * (size_t)n.cin; naux += (size_t)n.cin * n.k * n.k + 4; }
     else if (n.kind == PlanNode::kSe) naux += 2 * (size_t)n.cr * n.cin + n.cr + n.cin + 16;
     else if (n.kind == PlanNode::kFc) naux += n.cout + 4;
@@ -1086,6 +1100,12 @@ int model_build(Plan plan, const void* host_blob, size_t n_elements, size_t ele_
     } else {
       m->scale.push_back(nullptr);
       m->shift.push_back(nullptr);
+    }
+    if (g.in == 0 && g.res < 0 && m->stem3_node < 0 && stem3x3_supported(g.cin, g.cout, g.k, g.k, m->act_dt, g.act) &&
+        (g.has_bn || g.has_bias)) {
+      m->stem3_w = to_f32(g.off_w, (size_t)g.cout * 27);
+      if (!m->stem3_w) return fail(NNCV_B200_ECUDA, "converting the first convolution's filter failed");
+      m->stem3_node = (int)i;
     }
     if (g.stem_pool >= 0 && m->stem_node < 0) {
       rc = m->stem_w.reserve(stem_wpack_bytes());
@@ -1243,6 +1263,24 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
       continue;
     }
     if (n.kind == PlanNode::kMaxPool && n.absorbed && stem_fused_here) continue;
+    if (n.kind == PlanNode::kConv && n.in == 0 && (int)ni == m.stem3_node) {
+      // small-channel first layer straight from the NCHW input: no conversion pass, no padded GEMM (MobileNetV3.mlir:240-295)
+      const int oh = (H + 2 * n.pad - 3) / n.stride + 1, ow = (W + 2 * n.pad - 3) / n.stride + 1;
+      if (oh <= 0 || ow <= 0) return fail(NNCV_B200_EINVAL, "input %dx%d too small for the network", H, W);
+      Ten o;
+      o.l = lay(oh, ow); o.h = oh; o.w = ow; o.c = n.cout;
+      if ((rc = next_act(m, N, oh, ow, n.cout, o.l, st, &o.p))) return rc;
+      if (begin_op({})) {
+        prof_begin(3, 2.0 * N * oh * ow * n.cout * 27.0, (double)N * (3.0 * H * W * m.ele_width + aes * oh * ow * n.cout), N * oh * ow,
+                   n.cout, 27, 8, st);
+        LAUNCH(launch_stem3x3(src_dev, m.io_dt, m.stem3_w, m.scale[n.conv_idx], m.shift[n.conv_idx], o.p, adt, o.l, N, H, W, n.cout,
+                              n.stride, n.pad, n.act, st));
+        ++g_launches;
+        prof_end(st);
+      }
+      tens[n.id] = o;
+      continue;
+    }
     Ten in;
     if (n.in == 0) {
       // NCHW -> NHWC (channels padded), io type -> activation type; once per forward
@@ -1351,8 +1389,11 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
         }
         tens[bn.id] = d;
       }
+      c.want_act = n.act;
+      c.act_done = false;
       if (!done && (rc = run(n, in, o, res))) return rc;
-      if (n.act > kActRelu && begin_op({o.p})) {
+      c.want_act = 0;
+      if (n.act > kActRelu && !(c.act_done && !m.planning) && begin_op({o.p})) {
         // hard-swish / SiLU: an elementwise pass over the tensor in place; both map 0 to 0, so the zero pads of a
         // padded layout stay zero
         const size_t elems = (size_t)layout_slots(o.l, N) * o.c;

@@ -60,6 +60,7 @@ struct TcParams {
   int tiles_x, tiles_y, tiles_n, n_tiles, m_items;
   int stages;                // A (+ streamed weight) ring depth
   int relu, bf16, out_f32;
+  int act;   // 0, or kActHardSwish / kActSilu applied after the residual add (16-bit outputs)
 };
 
 // DUAL: a ResNet block that changes resolution applies a 3x3 stride-2 pad-1 convolution and a 1x1
@@ -355,11 +356,19 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         __syncwarp();
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + ab * ACC_W + (uint32_t)(oi * BN + sl * slab_cols + c0), acc);
         uint32_t res[2][8];
-        const bool use_res = residual_o != nullptr && valid && active && n_first + 32 <= p.Kout;
+        // 32-byte loads need a pixel pitch that is a multiple of 32 bytes and a full group of 32 columns; other
+        // widths (Kout a multiple of 8: column pairs never straddle the end) take guarded 4-byte loads
+        const bool use_res = residual_o != nullptr && valid && active && n_first < p.Kout;
         if (use_res) {
           const uint8_t* rp = residual_o + (pix * (size_t)p.Kout + n_first) * 2;
-          ptx::ldg_256(rp, res[0]);
-          ptx::ldg_256(rp + 32, res[1]);
+          if (n_first + 32 <= p.Kout && (p.Kout & 15) == 0) {
+            ptx::ldg_256(rp, res[0]);
+            ptx::ldg_256(rp + 32, res[1]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              res[e >> 3][e & 7] = (n_first + 2 * e < p.Kout) ? __ldg(reinterpret_cast<const uint32_t*>(rp + 4 * e)) : 0u;
+          }
         }
         __syncwarp();
         ptx::tmem_ld_wait();
@@ -402,6 +411,16 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
               else f = __half22float2(*reinterpret_cast<const __half2*>(&w));
               v[2 * e] += f.x;
               v[2 * e + 1] += f.y;
+            }
+          }
+          if (p.act != 0 && oi == 0) {
+            // hard-swish x * min(max(x + 3, 0), 6) / 6 or SiLU x / (1 + exp(-x)); a NaN stays NaN through the product with x
+            if (p.act == kActHardSwish) {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) v[e] *= fminf(fmaxf(fmaf(v[e], 0.16666667f, 0.5f), 0.0f), 1.0f);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) v[e] *= __fdividef(1.0f, __expf(-v[e]) + 1.0f);
             }
           }
           const uint32_t srow = sStage + sb * kSlabBytes + (uint32_t)row * 128u;
@@ -583,8 +602,9 @@ cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
 }  // namespace
 
 bool tconv_supported(int C, int Kout, DType out_dt, long long ldo) {
-  // channels in blocks of 64; the output row pitch must be 16-byte aligned for the tensor map
-  return C % 64 == 0 && C >= 64 && ldo == Kout && (Kout * (out_dt == kF32 ? 4 : 2)) % 16 == 0;
+  // channels are read in blocks of 64 (a last block that reaches past C is zero-filled by the copy engine and
+  // meets zero weights); pixel and output row pitches must be 16-byte aligned for the tensor maps
+  return C % 8 == 0 && C >= 8 && ldo == Kout && (Kout * (out_dt == kF32 ? 4 : 2)) % 16 == 0;
 }
 
 // M-tile shape: tw covers the output row in as few pieces as possible.
@@ -645,6 +665,7 @@ cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream) {
   if (mi <= 0 || mi * p.n_tiles > 0x7fffffffLL) return cudaErrorInvalidValue;
   p.m_items = (int)mi;
   p.relu = a.relu; p.bf16 = a.ab == kBF16; p.out_f32 = a.out_dtype == kF32;
+  p.act = a.act;
   p.stages = 0;
   if (p.residual && p.out_f32) return cudaErrorInvalidValue;
   if (brow) {
