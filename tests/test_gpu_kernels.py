@@ -287,6 +287,43 @@ def test_conv_per_tap_on_cta_pairs(case, dtype, res):
     assert G.rel_l2(y2, ref) <= (TOL_16 if dtype == F16 else 8e-3)
 
 
+@pytest.mark.parametrize("case", [
+    # n, c, h, w, k, r, stride, pad, bn     channel counts of MobileNetV3 / ResNet-50 that are not multiples of 64
+    (3, 16, 56, 56, 72, 1, 1, 0, 128), (2, 72, 28, 28, 24, 1, 1, 0, 64), (2, 88, 28, 28, 24, 1, 1, 0, 64), (4, 40, 14, 14, 240, 1, 1, 0, 128),
+    (1, 96, 14, 14, 40, 1, 1, 0, 64), (2, 24, 17, 19, 88, 3, 2, 1, 64), (2, 64, 28, 28, 256, 1, 1, 0, 256), (3, 256, 14, 14, 64, 1, 1, 0, 64),
+])
+@pytest.mark.parametrize("dtype,res", [(F16, False), (F16, True), (BF16, True)])
+def test_conv_ragged_channels(case, dtype, res):
+    """The TMA-fed kernel on channel counts that are not multiples of 64 (last channel block zero-filled by the copy engine,
+    weights packed per tap; output widths below 64 and not a multiple of 32, residual read with guarded loads), with streamed
+    and with resident weights.  Against the oracle, and the two against each other bit for bit."""
+    n, c, h, w, k, r, stride, pad, bn = case
+    g = _rng(n * 3 + c + h + k + r)
+    x = g.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = (g.standard_normal((k, c, r, r)) * np.sqrt(2.0 / (r * r * c))).astype(np.float32)
+    scale = g.uniform(0.5, 1.5, k).astype(np.float32)
+    shift = (g.standard_normal(k) * 0.1).astype(np.float32)
+    oh, ow = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - r) // stride + 1
+    rs = g.standard_normal((n, k, oh, ow)).astype(np.float32) if res else None
+    conv = G.Conv(wt, stride, pad, dtype)
+    try:
+        check(lib().nncv_b200_conv_set_tile(conv.h, bn, 1, 0))
+        y1, xq = conv.run(x, scale, shift, rs, True)
+        check(lib().nncv_b200_conv_set_tile(conv.h, 64, 1, 1))      # resident weights
+        y2, _ = conv.run(x, scale, shift, rs, True)
+    finally:
+        conv.close()
+    assert np.array_equal(y1, y2)
+    tdt = G.TORCH_DT[dtype]
+    ref = ob.conv2d(xq, torch.from_numpy(wt).to(tdt).float().numpy(), stride, pad, acc64=True)
+    ref = ref * scale[None, :, None, None] + shift[None, :, None, None]
+    if res:
+        ref = ref + torch.from_numpy(rs).to(tdt).float().numpy()
+    ref = np.where(ref > 0, ref, 0)
+    assert G.rel_l2(y1, ref) <= (TOL_16 if dtype == F16 else 8e-3)
+    assert lib().nncv_b200_device_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(3, 64, 56, 56, 128), (2, 128, 28, 28, 256), (5, 256, 14, 14, 512), (1, 64, 9, 13, 128)])
 @pytest.mark.parametrize("dtype", [F16, BF16])
 @pytest.mark.parametrize("pair", [False, True])
