@@ -463,6 +463,11 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
           }
         }
         ptx::fence_proxy_async_smem();
+        // One barrier per slab.  Before it the storing thread makes sure the previous slab's store has finished
+        // reading its staging buffer: past the barrier every thread may fill that buffer for the next slab while
+        // this slab's store (issued right after the barrier) reads the other one.  Nobody can run two slabs ahead,
+        // because the next barrier needs the storing thread too.
+        if (elected) ptx::bulk_wait_read<0>();
         ptx::named_bar_sync(1, kEpiThreads);
         if (elected) {
           if (PAIR && last_slab) {   // every thread of this CTA has read the accumulator: tell the leader
@@ -472,9 +477,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
           if (ncol < p.Kout)
             ptx::tma_store_4d((DUAL && oi) ? &tm_out2 : &tm_out, ncol, ox0 + p.out_off, oy0 + p.out_off, n0, sStage + sb * kSlabBytes);
           ptx::bulk_commit();
-          ptx::bulk_wait_read<1>();
         }
-        ptx::named_bar_sync(2, kEpiThreads);
       }
       ++acc_cnt;
       (void)esz;
