@@ -1,6 +1,6 @@
 """Kernel and network sweeps over the benchmark configs other than the headline one.
 
-    python -m nncv_b200.sweeps [gemm [SIZE]] [conv] [nets] [hbm]
+    python -m nncv_b200.sweeps [gemm [SIZE]] [conv] [nets] [hbm] [mobilenet [BATCH]]
 
   gemm : M=N=K in {512,1024,2048,4096}, fp16 in / fp32 accumulate (fp16 and fp32 C), optional fused
          bias + ReLU, and the fp32 CUDA-core path (config 1).
@@ -10,6 +10,8 @@
   hbm  : the memory-bound operators (depthwise conv + BN + hard-swish, activations, SE scaling, concat,
          2x upsampling, max-pool, global average pool) on MobileNetV3 / YOLOv5-sized maps: GB/s of
          algorithmic bytes (elements read + written) against the measured HBM copy bandwidth.
+  mobilenet : MobileNetV3-small fp16 @224 from a layer plan file (default: the plan the importer wrote from nncv's
+         tests/Nets/MobileNetV3.mlir, kept under tests/golden/), seeded weights, batch 256 unless given.
 One JSON line per measurement; times are CUDA-event medians on the launching stream with an L2 flush
 (256 MiB fill) before every timed call.  Torch only owns the device memory.
 """
@@ -168,8 +170,40 @@ def hbm_ops():
     return out
 
 
+def mobilenet(batch=256, plan_path=None):
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    plan_path = plan_path or os.path.join(root, "tests", "golden", "mobilenetv3_from_mlir.plan")
+    text = open(plan_path).read()
+    g = np.random.default_rng(0)
+    total = int(next(l for l in text.splitlines() if l.startswith("params")).split()[1])
+    blob = (g.standard_normal(total) * 0.05).astype(np.float32)
+    for line in text.splitlines():          # batch-norm scales and variances must be positive
+        f = dict(t.split("=") for t in line.split()[1:] if "=" in t)
+        c = int(f.get("cout", f.get("c", 0)))
+        for role in ("gamma", "var"):
+            if role in f:
+                blob[int(f[role]):int(f[role]) + c] = g.uniform(0.5, 1.5, c)
+    rt.load_blob("plan:" + text, blob.astype(np.float16), F16)
+    x = torch.randn((batch, 3, 224, 224), device="cuda").to(torch.float16)
+    o = torch.empty((batch, 1000), device="cuda", dtype=x.dtype)
+    s = torch.cuda.current_stream().cuda_stream
+    rt.forward_device(o, x, s)
+    torch.cuda.synchronize()
+    ms = _time(lambda: rt.forward_device(o, x, s))
+    print(json.dumps({"sweep": "mobilenet", "config": "MobileNetV3-small fp16 @224, imported plan", "batch": batch, "ms": round(ms, 4),
+                      "images_per_s": round(batch / ms * 1e3, 1), "finite": bool(torch.isfinite(o.float()).all())}), flush=True)
+    rt.unload()
+
+
 if __name__ == "__main__":
     which = sys.argv[1:] or ["gemm", "conv", "nets"]
+    if "mobilenet" in which:
+        nums = [int(a) for a in which if a.isdigit()]
+        mobilenet(nums[0] if nums else 256)
+        which = [a for a in which if a != "mobilenet" and not a.isdigit()]
+        if not which:
+            sys.exit(0)
     sizes = tuple(int(a) for a in which if a.isdigit())
     if "gemm" in which:
         gemm(sizes or (512, 1024, 2048, 4096))
