@@ -171,6 +171,9 @@ struct SimtConvArgs {
   int N = 0, H = 0, W = 0, C = 0, OH = 0, OW = 0, Kout = 0, R = 1, S = 1, stride = 1, pad = 0;
   long long ldo = 0;
   int relu = 0;
+  float* scratch = nullptr;         // optional: room for a split reduction's partial sums ([splits][M][Kout])
+  size_t scratch_bytes = 0;
+  int sm_count = 0;
 };
 cudaError_t launch_conv_simt_f32(const SimtConvArgs& a, cudaStream_t stream);
 // W[n][c][tap] (strides) -> [Kout][taps][Cpad] fp32

@@ -340,6 +340,7 @@ struct nncv_b200_conv {
   DType raw_dt = kF32;
   long long sn = 0, sc = 0, stap = 0;
   DevBuf raw_owned;                                // set when create() copied the weights
+  DevBuf splitk;          // fp32 path: partial sums of a split reduction (small batches only)
   int want_act = 0;       // set by the plan executor: activation beyond ReLU it would like fused (hard-swish, SiLU)
   bool act_done = false;  // set by conv_run when the kernel it launched applied want_act
   std::map<int, std::unique_ptr<DevBuf>> packed;   // tcgen05 path: per N-tile width
@@ -413,6 +414,19 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
     a.residual = (const float*)residual; a.out = (float*)out;
     a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.OH = OH; a.OW = OW; a.Kout = c->Kout;
     a.R = c->R; a.S = c->S; a.stride = c->stride; a.pad = c->pad; a.ldo = ldo; a.relu = relu;
+    a.sm_count = g_dev.sm_count;
+    {
+      // a small batch leaves few output tiles: room for the partial sums of a reduction split over more CTAs
+      const long long tiles = (((long long)N * OH * OW + 63) / 64) * ((c->Kout + 63) / 64);
+      if (tiles < g_dev.sm_count) {
+        const size_t want = (size_t)32 * N * OH * OW * c->Kout * sizeof(float);
+        const size_t cap = (size_t)16 << 20;
+        int rc = c->splitk.reserve(want < cap ? want : cap);
+        if (rc) return rc;
+        a.scratch = (float*)c->splitk.p;
+        a.scratch_bytes = c->splitk.bytes;
+      }
+    }
     const double Ms = (double)N * OH * OW;
     prof_begin(1, 2.0 * Ms * c->Kout * c->C * c->R * c->S,
                4.0 * ((double)N * H * W * c->C + (double)c->Kout * c->C * c->R * c->S +

@@ -47,6 +47,9 @@ struct SimtParams {
   long long ldo;
   int M, H, W, C, OH, OW, Kout, R, S, stride, pad, Kred;
   int relu;
+  int splits;        // > 1: blockIdx.z takes one slice of the reduction and writes raw sums to `partial`
+  int k_chunk;       // reduction elements per slice (a multiple of kTK)
+  float* partial;    // [splits][M][Kout]
 };
 
 __global__ void __launch_bounds__(256) conv_simt_f32_kernel(const SimtParams p) {
@@ -72,10 +75,12 @@ __global__ void __launch_bounds__(256) conv_simt_f32_kernel(const SimtParams p) 
   const bool nvalid = nb < p.Kout;
   const int ty = t >> 4, tx = t & 15;
   float acc[4][4] = {};
-  for (int k0 = 0; k0 < p.Kred; k0 += kTK) {
+  const int k_begin = p.splits > 1 ? (int)blockIdx.z * p.k_chunk : 0;
+  const int k_end = p.splits > 1 ? min(p.Kred, k_begin + p.k_chunk) : p.Kred;
+  for (int k0 = k_begin; k0 < k_end; k0 += kTK) {
     const int kidx = k0 + lk;
     float4 av = make_float4(0.f, 0.f, 0.f, 0.f), bv = av;
-    if (kidx < p.Kred) {
+    if (kidx < k_end) {
       const int tap = kidx / p.C, c0 = kidx - tap * p.C;
       const int r = tap / p.S, s = tap - r * p.S;
       const int iy = iy0 + r, ix = ix0 + s;
@@ -107,12 +112,32 @@ __global__ void __launch_bounds__(256) conv_simt_f32_kernel(const SimtParams p) 
       const int n = blockIdx.y * kTN + tx * 4 + j;
       if (n >= p.Kout) continue;
       float v = acc[i][j];
+      if (p.splits > 1) {   // the epilogue runs in conv_simt_reduce_kernel, over the slices in a fixed order
+        p.partial[((size_t)blockIdx.z * p.M + mo) * p.Kout + n] = v;
+        continue;
+      }
       if (p.scale) v *= __ldg(p.scale + n);
       if (p.shift) v += __ldg(p.shift + n);
       if (p.residual) v += p.residual[(size_t)mo * p.ldo + n];
       if (p.relu) v = !(v <= 0.0f) ? v : 0.0f;
       p.out[(size_t)mo * p.ldo + n] = v;
     }
+  }
+}
+
+// Second pass of a split reduction: out = epilogue(sum over the slices, in slice order).
+__global__ void conv_simt_reduce_kernel(const SimtParams p) {
+  const long long total = (long long)p.M * p.Kout;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long mo = i / p.Kout;
+    const int n = (int)(i - mo * p.Kout);
+    float v = 0.0f;
+    for (int z = 0; z < p.splits; ++z) v += p.partial[(size_t)z * total + i];
+    if (p.scale) v *= __ldg(p.scale + n);
+    if (p.shift) v += __ldg(p.shift + n);
+    if (p.residual) v += p.residual[(size_t)mo * p.ldo + n];
+    if (p.relu) v = !(v <= 0.0f) ? v : 0.0f;
+    p.out[(size_t)mo * p.ldo + n] = v;
   }
 }
 
@@ -417,7 +442,30 @@ cudaError_t launch_conv_simt_f32(const SimtConvArgs& a, cudaStream_t stream) {
   p.M = (int)M; p.H = a.H; p.W = a.W; p.C = a.C; p.OH = a.OH; p.OW = a.OW; p.Kout = a.Kout;
   p.R = a.R; p.S = a.S; p.stride = a.stride; p.pad = a.pad; p.Kred = a.R * a.S * a.C; p.relu = a.relu;
   dim3 grid((unsigned)((M + kTM - 1) / kTM), (unsigned)((a.Kout + kTN - 1) / kTN));
+  // Few output tiles and a long reduction (one image, late layers: 8 CTAs walking K = 4608): slice the reduction
+  // over blockIdx.z so that the GPU is filled, raw sums to scratch, epilogue in a second pass.
+  p.splits = 1; p.k_chunk = p.Kred; p.partial = nullptr;
+  const long long ctas = (long long)grid.x * grid.y;
+  const int sms = a.sm_count > 0 ? a.sm_count : 148;
+  if (a.scratch && ctas < sms && p.Kred >= 8 * kTK) {
+    int splits = (int)((2LL * sms + ctas - 1) / ctas);
+    const int max_by_k = p.Kred / (4 * kTK);                 // at least four k steps per slice
+    if (splits > max_by_k) splits = max_by_k;
+    if (splits > 32) splits = 32;
+    while (splits > 1 && (size_t)splits * M * a.Kout * sizeof(float) > a.scratch_bytes) --splits;
+    if (splits > 1) {
+      const int steps = (p.Kred + kTK - 1) / kTK;
+      p.k_chunk = (steps + splits - 1) / splits * kTK;
+      p.splits = (p.Kred + p.k_chunk - 1) / p.k_chunk;       // no empty slice
+      p.partial = a.scratch;
+      grid.z = (unsigned)p.splits;
+    }
+  }
   conv_simt_f32_kernel<<<grid, 256, 0, stream>>>(p);
+  if (p.splits > 1) {
+    const long long total = M * a.Kout;
+    conv_simt_reduce_kernel<<<grid_for(total, 256), 256, 0, stream>>>(p);
+  }
   return cudaGetLastError();
 }
 
