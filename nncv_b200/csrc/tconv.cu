@@ -333,10 +333,29 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
       const int nimg = n0 + tnn, oy = oy0 + ti, ox = ox0 + tj;
       const bool valid = nimg < p.NB && oy < p.OH && ox < p.OW;
       const size_t pix = ((size_t)nimg * p.out_rows + oy + p.out_off) * p.out_pitch + ox + p.out_off;
+      if (p.residual != nullptr) {
+        // pull the residual rows of the NEXT item from HBM into L2 while this item's accumulator is awaited
+        // and drained, so that the epilogue's per-row loads of the next item do not start from DRAM
+        int n0n, oy0n, ox0n, n_tile_n;
+        if (item_of(i + 1, n0n, oy0n, ox0n, n_tile_n)) {
+          const int nin = n0n + tnn, oyn = oy0n + ti, oxn = ox0n + tj;
+          if (nin < p.NB && oyn < p.OH && oxn < p.OW) {
+            const size_t pixn = ((size_t)nin * p.out_rows + oyn + p.out_off) * p.out_pitch + oxn + p.out_off;
+            const int cfirst = n_tile_n * BN + (p.out_f32 ? 0 : half * 32);
+            for (int sl = 0; sl < slabs; ++sl) {
+              const int col = cfirst + sl * slab_cols;
+              if (col < p.Kout)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + (pixn * (size_t)p.Kout + col) * 2));
+            }
+          }
+        }
+      }
       const bool got = PAIR ? ptx::mbar_wait_cluster_abortable(acc_full + 8 * ab, (acc_cnt >> 1) & 1u, abort_flag)
                             : ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt >> 1) & 1u, abort_flag);
       if (!ptx::named_bar_and(3, kEpiThreads, got)) { okw = false; break; }
       ptx::tc_fence_after();
+      uint32_t res_next[2][8];   // residual of the next slab of this item, in flight one slab ahead
+      bool have_next = false;
       for (int oi = 0; oi < (DUAL ? 2 : 1); ++oi)
       for (int sl = 0; sl < slabs; ++sl, ++jglob) {
         const float* scale_o = oi ? p.scale2 : p.scale;
@@ -361,13 +380,24 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         const bool use_res = residual_o != nullptr && valid && active && n_first < p.Kout;
         if (use_res) {
           const uint8_t* rp = residual_o + (pix * (size_t)p.Kout + n_first) * 2;
-          if (n_first + 32 <= p.Kout && (p.Kout & 15) == 0) {
+          if (have_next) {   // fetched while the previous slab was converted and stored
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { res[0][e] = res_next[0][e]; res[1][e] = res_next[1][e]; }
+          } else if (n_first + 32 <= p.Kout && (p.Kout & 15) == 0) {
             ptx::ldg_256(rp, res[0]);
             ptx::ldg_256(rp + 32, res[1]);
           } else {
 #pragma unroll
             for (int e = 0; e < 16; ++e)
               res[e >> 3][e & 7] = (n_first + 2 * e < p.Kout) ? __ldg(reinterpret_cast<const uint32_t*>(rp + 4 * e)) : 0u;
+          }
+          // the next slab's residual of this row goes into flight now (the same item: the row stays, the columns move on)
+          have_next = false;
+          const int n_next = n_first + slab_cols;
+          if (sl + 1 < slabs && n_next + 32 <= p.Kout && (p.Kout & 15) == 0) {
+            ptx::ldg_256(rp + slab_cols * 2, res_next[0]);
+            ptx::ldg_256(rp + slab_cols * 2 + 32, res_next[1]);
+            have_next = true;
           }
         }
         __syncwarp();
