@@ -217,6 +217,22 @@ cudaError_t launch_depthwise(const void* x, const void* w, DType w_dt, const flo
 bool stem3x3_supported(int Cin, int Cout, int R, int S, DType act_dt, int act);
 cudaError_t launch_stem3x3(const void* src, DType src_dt, const float* w, const float* scale, const float* shift, void* dst, DType dt,
                            Layout out_l, int N, int H, int W, int Cout, int stride, int pad, int act, cudaStream_t st);
+// 1x1 stride-1 convolution with at most 128 channels on either side, on CUDA cores (16-bit NHWC, any layout)
+struct PointwiseArgs {
+  const void* in = nullptr;
+  const float* w = nullptr;          // [Kout][C] fp32
+  const float* scale = nullptr;
+  const float* shift = nullptr;
+  const void* residual = nullptr;    // output layout
+  void* out = nullptr;
+  Layout in_l{0, 0, 0}, out_l{0, 0, 0};
+  int N = 0, H = 0, W = 0, C = 0, Kout = 0;
+  DType ab = kF16;
+  int relu = 0, act = 0;             // act: 0, kActHardSwish or kActSilu (applied after the residual add)
+  int sm_count = 0;
+};
+bool pointwise_supported(int C, int Kout, int R, int S, int stride, int pad, DType dt);
+cudaError_t launch_pointwise(const PointwiseArgs& a, cudaStream_t st);
 bool depthwise_tma_supported(DType dt, int N, int H, int W, int C, int R, int S, int stride, int pad);
 cudaError_t launch_depthwise_tma(const void* x, const void* w, DType w_dt, const float* scale, const float* shift, void* y, DType dt,
                                  int N, int H, int W, int C, int R, int S, int stride, int pad, int act, Layout in_l, Layout out_l,

@@ -437,6 +437,30 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
     return NNCV_B200_OK;
   }
   const long long M = (long long)N * OH * OW;
+  // Pointwise convolutions with up to 32 channels on both sides (MobileNetV3's 16 -> 16 at 112 x 112) are bound by HBM
+  // and lose on tiles padded to 64 channels: they take the CUDA-core kernel (27 us against 109 us at batch 256; with
+  // more channels the tensor-core kernel wins: 16 -> 72 measured 156 us against 141 us, 88 -> 24 64 against 43).  The
+  // rule depends on the layer alone, never on the batch or on a timing, so a batch split over devices or into halves
+  // gives the same bits as the whole batch.
+  if (!fb && !g_force_gather && !c->force_gather && c->cfg3.bn == 0 && out_dt == c->dtype && ldo == c->Kout &&
+      pointwise_supported(c->Cpad, c->Kout, c->R, c->S, c->stride, c->pad, c->dtype) && c->Cpad <= 32 && c->Kout <= 32) {
+    if (!c->w_f32_ready) {
+      int rc = c->w_f32.reserve((size_t)c->Kout * c->Cpad * sizeof(float));
+      if (rc) return rc;
+      LAUNCH(launch_repack_weights_f32(c->raw, c->raw_dt, c->sn, c->sc, c->stap, c->Kout, c->C, c->Cpad, 1, (float*)c->w_f32.p, st));
+      c->w_f32_ready = true;
+    }
+    PointwiseArgs a;
+    a.in = in; a.w = (const float*)c->w_f32.p; a.scale = scale; a.shift = shift; a.residual = residual; a.out = out;
+    a.in_l = in_l; a.out_l = out_l; a.N = N; a.H = H; a.W = W; a.C = c->Cpad; a.Kout = c->Kout; a.ab = c->dtype; a.relu = relu;
+    a.sm_count = g_dev.sm_count;
+    if (c->want_act > kActRelu) { a.act = c->want_act; c->act_done = true; }
+    prof_begin(9, 2.0 * (double)M * c->Kout * c->C, 2.0 * (double)M * (c->Cpad + c->Kout * (residual ? 2 : 1)), (int)M, c->Kout, c->C, 16, st);
+    ++g_launches;
+    LAUNCH(launch_pointwise(a, st));
+    prof_end(st);
+    return NNCV_B200_OK;
+  }
   if (fb && (c->dtype == kF32 || out_dt != c->dtype || ldo != c->Kout || !fused_branch_ok(*c, *fb->conv)))
     return fail(NNCV_B200_EINVAL, "conv: the fused 1x1 branch does not fit this convolution");
   const double flops = 2.0 * (double)M * c->Kout * c->C * (c->R * c->S + (fb ? 1 : 0));

@@ -324,6 +324,40 @@ def test_conv_ragged_channels(case, dtype, res):
     assert lib().nncv_b200_device_status() == 0
 
 
+@pytest.mark.parametrize("case", [(3, 16, 56, 56, 16), (2, 32, 28, 28, 24), (2, 24, 29, 31, 32), (5, 16, 17, 112, 16), (2, 8, 14, 14, 32),
+                                  (1, 8, 9, 7, 8)])
+@pytest.mark.parametrize("dtype,res,relu", [(F16, False, True), (F16, True, False), (BF16, True, True)])
+def test_conv_pointwise_few_channels(case, dtype, res, relu):
+    """1x1 stride-1 convolutions with at most 32 channels on both sides take the CUDA-core pointwise kernel (a rule on the
+    layer alone): against the oracle, and within 16-bit rounding of the tensor-core kernel forced on the same inputs."""
+    n, c, h, w, k = case
+    g = _rng(n + c + h + k)
+    x = g.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = (g.standard_normal((k, c, 1, 1)) * np.sqrt(2.0 / c)).astype(np.float32)
+    scale = g.uniform(0.5, 1.5, k).astype(np.float32)
+    shift = (g.standard_normal(k) * 0.1).astype(np.float32)
+    rs = g.standard_normal((n, k, h, w)).astype(np.float32) if res else None
+    conv = G.Conv(wt, 1, 0, dtype)
+    try:
+        launches0 = lib().nncv_b200_launch_count()
+        y1, xq = conv.run(x, scale, shift, rs, relu)
+        check(lib().nncv_b200_conv_set_tile(conv.h, 64, 1, 0))       # the TMA-fed tensor-core kernel
+        y2, _ = conv.run(x, scale, shift, rs, relu)
+    finally:
+        conv.close()
+    assert lib().nncv_b200_launch_count() > launches0
+    tdt = G.TORCH_DT[dtype]
+    ref = ob.conv2d(xq, torch.from_numpy(wt).to(tdt).float().numpy(), 1, 0, acc64=True)
+    ref = ref * scale[None, :, None, None] + shift[None, :, None, None]
+    if res:
+        ref = ref + torch.from_numpy(rs).to(tdt).float().numpy()
+    if relu:
+        ref = np.where(ref > 0, ref, 0)
+    tol = TOL_16 if dtype == F16 else 8e-3
+    assert G.rel_l2(y1, ref) <= tol and G.rel_l2(y2, ref) <= tol and G.rel_l2(y1, y2) <= tol
+    assert lib().nncv_b200_device_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(3, 64, 56, 56, 128), (2, 128, 28, 28, 256), (5, 256, 14, 14, 512), (1, 64, 9, 13, 128)])
 @pytest.mark.parametrize("dtype", [F16, BF16])
 @pytest.mark.parametrize("pair", [False, True])
