@@ -40,6 +40,7 @@ constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kABytes = 128 * 128;
 constexpr int kSlabBytes = 128 * 128;
+constexpr int kOutBufs = 2;     // staging buffers of the epilogue: kOutBufs - 1 stores may be reading shared memory at once
 constexpr int kMaxStages = 8;
 
 struct TcParams {
@@ -99,7 +100,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
   const uint32_t sRing = base;
   const uint32_t sW = sRing + (uint32_t)p.stages * stage_bytes;       // resident weights
   const uint32_t sStage = sW + (RESIDENT ? (uint32_t)(KB + (DUAL ? p.CB : 0)) * WTILE : 0u);   // resident: main tiles, then the branch's
-  const uint32_t bars = sStage + 2 * kSlabBytes;
+  const uint32_t bars = sStage + kOutBufs * kSlabBytes;
   const uint32_t full = bars, empty = bars + 8 * kMaxStages;
   const uint32_t acc_full = empty + 8 * kMaxStages, acc_empty = acc_full + 16;
   const uint32_t w_full = acc_empty + 16;
@@ -362,7 +363,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         const float* shift_o = oi ? p.shift2 : p.shift;
         const uint8_t* residual_o = oi ? nullptr : p.residual;
         const bool relu_o = oi ? false : p.relu != 0;
-        const uint32_t sb = (uint32_t)jglob & 1u;
+        const uint32_t sb = (uint32_t)jglob % (uint32_t)kOutBufs;
         const int ncol = n_tile * BN + sl * slab_cols;     // first column of the slab
         // this warp's 32 accumulator columns inside the slab: 16-bit output -> columns
         // [half*32, +32) of a 64-column slab; fp32 output -> both halves share a 32-column
@@ -497,7 +498,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         // reading its staging buffer: past the barrier every thread may fill that buffer for the next slab while
         // this slab's store (issued right after the barrier) reads the other one.  Nobody can run two slabs ahead,
         // because the next barrier needs the storing thread too.
-        if (elected) ptx::bulk_wait_read<0>();
+        if (elected) ptx::bulk_wait_read<kOutBufs - 2>();
         ptx::named_bar_sync(1, kEpiThreads);
         if (elected) {
           if (PAIR && last_slab) {   // every thread of this CTA has read the accumulator: tell the leader
@@ -572,7 +573,7 @@ template <int BN, bool RESIDENT, bool DUAL = false, bool PAIR = false, bool BROW
 cudaError_t launch_cfg(const TconvArgs& a, TcParams p, cudaStream_t stream) {
   const size_t wtile = (size_t)(PAIR ? BN / 2 : BN) * 128;
   const int KB = p.taps * p.CB;
-  const size_t fixed = 1024 + 2 * kSlabBytes + 512;
+  const size_t fixed = 1024 + kOutBufs * kSlabBytes + 512;
   const size_t stage = RESIDENT ? kABytes : kABytes + wtile;
   const size_t wres = RESIDENT ? (size_t)(KB + (DUAL ? p.CB : 0)) * wtile : 0;
   if (fixed + wres + 2 * stage > kSmemLimit) return cudaErrorInvalidConfiguration;
@@ -737,8 +738,8 @@ cudaError_t launch_tconv(const TconvArgs& a, cudaStream_t stream) {
 // N tile and residency: keep all weights of one Kout tile in shared memory when they fit beside
 // four A stages; otherwise stream them with the widest tile the grid can still fill.
 void tconv_pick(long long m_items, int C, int Kout, int taps, int* bn, int* resident) {
-  const size_t budget = kSmemLimit - (1024 + 2 * kSlabBytes + 512) - 4 * (size_t)kABytes;
-  const size_t kb = (size_t)taps * (C / 64);
+  const size_t budget = kSmemLimit - (1024 + kOutBufs * kSlabBytes + 512) - 4 * (size_t)kABytes;
+  const size_t kb = (size_t)taps * ((C + 63) / 64);
   for (int b : {128, 64}) {
     if (Kout >= b && kb * b * 128 <= budget) {
       *bn = b; *resident = 1;

@@ -291,6 +291,7 @@ def test_conv_per_tap_on_cta_pairs(case, dtype, res):
     # n, c, h, w, k, r, stride, pad, bn     channel counts of MobileNetV3 / ResNet-50 that are not multiples of 64
     (3, 16, 56, 56, 72, 1, 1, 0, 128), (2, 72, 28, 28, 24, 1, 1, 0, 64), (2, 88, 28, 28, 24, 1, 1, 0, 64), (4, 40, 14, 14, 240, 1, 1, 0, 128),
     (1, 96, 14, 14, 40, 1, 1, 0, 64), (2, 24, 17, 19, 88, 3, 2, 1, 64), (2, 64, 28, 28, 256, 1, 1, 0, 256), (3, 256, 14, 14, 64, 1, 1, 0, 64),
+    (2, 128, 28, 28, 512, 1, 1, 0, 128), (3, 64, 56, 56, 128, 3, 2, 1, 128),
 ])
 @pytest.mark.parametrize("dtype,res", [(F16, False), (F16, True), (BF16, True)])
 def test_conv_ragged_channels(case, dtype, res):
