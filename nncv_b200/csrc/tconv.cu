@@ -93,6 +93,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_abort;
+  __shared__ __align__(16) float s_scale[256], s_shift[256];   // per-channel scale / shift of the N tile in work (single-output kernels)
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   const int KB = p.taps * p.CB;
@@ -326,6 +327,7 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
     const int tj = row % p.tw, ti = (row / p.tw) % p.th, tnn = row / (p.tw * p.th);
     uint32_t acc_cnt = 0;
     int jglob = 0;   // slab counter for the two staging buffers
+    int cur_ntile = -1;
     bool okw = true;
     for (int i = 0; okw; ++i) {
       int n0, oy0, ox0, n_tile;
@@ -350,6 +352,17 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
             }
           }
         }
+      }
+      if (!DUAL && n_tile != cur_ntile) {
+        // scale / shift of this N tile into shared memory: the slabs read them as broadcast vectors instead of sixteen
+        // global loads per thread and slab.  Every thread has passed the last slab's barrier of the previous item, so
+        // nobody still reads the old values; the barrier below publishes the new ones.
+        for (int c = (int)threadIdx.x - 64; c < BN; c += kEpiThreads) {
+          const int col = n_tile * BN + c;
+          s_scale[c] = (p.scale && col < p.Kout) ? __ldg(p.scale + col) : 1.0f;
+          s_shift[c] = (p.shift && col < p.Kout) ? __ldg(p.shift + col) : 0.0f;
+        }
+        cur_ntile = n_tile;
       }
       const bool got = PAIR ? ptx::mbar_wait_cluster_abortable(acc_full + 8 * ab, (acc_cnt >> 1) & 1u, abort_flag)
                             : ptx::mbar_wait_abortable(acc_full + 8 * ab, (acc_cnt >> 1) & 1u, abort_flag);
@@ -410,7 +423,17 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
         }
         if (active) {
           float v[32];
-          if (n_first + 32 <= p.Kout) {
+          if constexpr (!DUAL) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              const float4 sc = *reinterpret_cast<const float4*>(&s_scale[sl * slab_cols + c0 + e]);
+              const float4 sh = *reinterpret_cast<const float4*>(&s_shift[sl * slab_cols + c0 + e]);
+              v[e] = fmaf(__uint_as_float(acc[e]), sc.x, sh.x);
+              v[e + 1] = fmaf(__uint_as_float(acc[e + 1]), sc.y, sh.y);
+              v[e + 2] = fmaf(__uint_as_float(acc[e + 2]), sc.z, sh.z);
+              v[e + 3] = fmaf(__uint_as_float(acc[e + 3]), sc.w, sh.w);
+            }
+          } else if (n_first + 32 <= p.Kout) {
 #pragma unroll
             for (int e = 0; e < 32; e += 4) {
               float4 sc = make_float4(1.f, 1.f, 1.f, 1.f), sh = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -555,7 +578,7 @@ bool make_map4(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int esz,
          CUDA_SUCCESS;
 }
 
-constexpr size_t kSmemLimit = 227 * 1024;
+constexpr size_t kSmemLimit = 225 * 1024;   // dynamic part: the kernel also holds 2 KB of static shared memory (scale / shift of an N tile)
 
 // 2-D map over a row-major [K, N] 16-bit matrix, box 64 columns x 64 rows, 128-byte swizzle, zero fill.
 bool make_map_b(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, long long K, long long N) {
