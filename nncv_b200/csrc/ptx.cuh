@@ -105,6 +105,19 @@ __device__ __forceinline__ uint32_t pack_half2_sat(float lo, float hi) {
   return r;
 }
 
+// The same conversion with ReLU folded in: negative values become +0, a NaN stays NaN (the canonical one), so one
+// instruction replaces the conversion and the packed maximum with zero.
+__device__ __forceinline__ uint32_t pack_half2_sat_relu(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.relu.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_bf162_relu(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
 // ---------------------------------------------------------------- cp.async ------------
 // 16-byte global->shared copy; src_bytes == 0 writes zeros (used for padding / ragged rows).
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {

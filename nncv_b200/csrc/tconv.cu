@@ -498,15 +498,16 @@ tconv_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ 
 #pragma unroll
               for (int h = 0; h < 4; ++h) {
                 const float a = v[c4 * 8 + h * 2], b = v[c4 * 8 + h * 2 + 1];
+                // conversion and ReLU in one instruction (cvt.rn.relu: negative -> +0, NaN stays NaN)
                 if (p.bf16) {
-                  __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
-                  if (relu_o) x = __hmax2_nan(x, __floats2bfloat162_rn(0.f, 0.f));
-                  o[h] = *reinterpret_cast<uint32_t*>(&x);
+                  if (relu_o) {
+                    o[h] = ptx::pack_bf162_relu(a, b);
+                  } else {
+                    const __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
+                    o[h] = *reinterpret_cast<const uint32_t*>(&x);
+                  }
                 } else {
-                  const uint32_t xs = ptx::pack_half2_sat(a, b);
-            __half2 x = *reinterpret_cast<const __half2*>(&xs);
-                  if (relu_o) x = __hmax2_nan(x, __floats2half2_rn(0.f, 0.f));
-                  o[h] = *reinterpret_cast<uint32_t*>(&x);
+                  o[h] = relu_o ? ptx::pack_half2_sat_relu(a, b) : ptx::pack_half2_sat(a, b);
                 }
               }
               const uint32_t chunk = (uint32_t)(half * 4 + c4);
