@@ -383,15 +383,16 @@ conv3x3_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         for (int h = 0; h < 4; ++h) {
           const float a = v[c4 * 8 + h * 2], b = v[c4 * 8 + h * 2 + 1];
           uint32_t packed;
+          // conversion and ReLU in one instruction (cvt.rn.relu: negative -> +0, a NaN stays NaN, like cmpf ugt + select)
           if (p.bf16) {
-            __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
-            if (p.relu) x = __hmax2_nan(x, __floats2bfloat162_rn(0.f, 0.f));
-            packed = *reinterpret_cast<uint32_t*>(&x);
+            if (p.relu) {
+              packed = ptx::pack_bf162_relu(a, b);
+            } else {
+              const __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
+              packed = *reinterpret_cast<const uint32_t*>(&x);
+            }
           } else {
-            const uint32_t xs = ptx::pack_half2_sat(a, b);
-            __half2 x = *reinterpret_cast<const __half2*>(&xs);
-            if (p.relu) x = __hmax2_nan(x, __floats2half2_rn(0.f, 0.f));  // NaN passes, like cmpf ugt
-            packed = *reinterpret_cast<uint32_t*>(&x);
+            packed = p.relu ? ptx::pack_half2_sat_relu(a, b) : ptx::pack_half2_sat(a, b);
           }
           o[h] = valid ? packed : 0u;
         }
