@@ -24,6 +24,8 @@
 #include <string>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/nncv_b200.h"
 #include "kernels.h"
 
@@ -181,6 +183,26 @@ struct ProfRec {
   float ms;
 };
 bool g_autotune = getenv("NNCV_B200_AUTOTUNE") ? atoi(getenv("NNCV_B200_AUTOTUNE")) != 0 : true;
+// NNCV_B200_LOG=1: one line to stderr per model load, activation plan and tuning decision (2: also every plan node of a
+// forward).  NNCV_B200_NVTX=1: an NVTX range around every plan node of a forward, named after the node, for timeline
+// tools.  Both are off by default and cost one branch when off.  (nncv's counterparts: its `-debug`-style LLVM options and
+// the timers its fixtures carry, tests/Nets/Res18.mlir has none.)
+int g_log_level = getenv("NNCV_B200_LOG") ? atoi(getenv("NNCV_B200_LOG")) : 0;
+bool g_nvtx = getenv("NNCV_B200_NVTX") ? atoi(getenv("NNCV_B200_NVTX")) != 0 : false;
+void log_line(int level, const char* fmt, ...) {
+  if (g_log_level < level) return;
+  va_list ap;
+  va_start(ap, fmt);
+  fputs("[nncv_b200] ", stderr);
+  vfprintf(stderr, fmt, ap);
+  fputc('\n', stderr);
+  va_end(ap);
+}
+struct NvtxRange {   // RAII: pops on every exit path of the enclosing block
+  bool on;
+  explicit NvtxRange(const char* name) : on(g_nvtx) { if (on) nvtxRangePushA(name); }
+  ~NvtxRange() { if (on) nvtxRangePop(); }
+};
 bool g_force_gather = false;  // tuning/test hook: route algo-0 convs through the gather kernel
 bool g_prof_on = false;
 int g_prof_dev = -1;            // records are taken on this device only (worker threads of a fan-out skip them)
@@ -627,6 +649,8 @@ int conv_run(nncv_b200_conv* c, const void* in, Layout in_l, void* out, Layout o
           char cval[64];
           snprintf(cval, sizeof(cval), "%d %d %d %d", best_ch.kernel, best_ch.bn, best_ch.mt, best_ch.resident);
           g_tune_cache.put(ckey, cval);
+          log_line(1, "tuned %s -> kernel %d tile %d x%d mode %d (%.1f us, %zu candidates)", ckey, best_ch.kernel, best_ch.bn, best_ch.mt,
+                   best_ch.resident, best * 250.0f, cand.size());
         }
       }
       ch = it->second;
@@ -1154,6 +1178,8 @@ int model_build(Plan plan, const void* host_blob, size_t n_elements, size_t ele_
     }
   }
   CU(cudaStreamSynchronize(st));
+  log_line(1, "loaded %s on device %d: %zu nodes, %zu parameters of %zu bytes, compute type %d", m->plan.name.c_str(), g_dev.id,
+           m->plan.nodes.size(), m->plan.total, ele_width, (int)m->act_dt);
   m->host_blob_id = host_blob;
   model_reset();
   g_dev.model = m.release();
@@ -1224,6 +1250,7 @@ int finish_act_plan(Model& m) {
   int rc = m.arena.reserve(base);
   if (rc) return rc;
   CU(cudaMemset(m.arena.p, 0, m.arena.bytes));
+  log_line(1, "activation arena: %zu tensors in %zu bytes (%zu bytes as private buffers)", m.act_plan.size(), base, unshared);
   m.planned = true;
   return NNCV_B200_OK;
 }
@@ -1267,8 +1294,13 @@ int model_forward_device(Model& m, const void* src_dev, int N, int H, int W, cud
   const bool stem_fused_here = m.fused_stem && W <= 512 && H >= 7 && W >= 7;
   bool input_converted = false;
   const int cpad0 = adt == kF32 ? 4 : 8;
+  static const char* const kKindName[] = {"conv", "maxpool", "avgpool", "fc", "dwconv", "se"};
   for (size_t ni = 0; ni < m.plan.nodes.size(); ++ni) {
     const PlanNode& n = m.plan.nodes[ni];
+    char range_name[64] = "";
+    if (g_nvtx || g_log_level >= 2) snprintf(range_name, sizeof(range_name), "%s id=%d in=%d c=%d->%d k=%d", kKindName[n.kind], n.id, n.in, n.cin, n.cout, n.k);
+    NvtxRange range(range_name);
+    if (!m.planning) log_line(2, "node %s", range_name);
     if (n.kind == PlanNode::kConv && n.in == 0 && stem_fused_here && (int)ni == m.stem_node) {
       // stem conv + BN + ReLU + max-pool in one kernel (Res18.mlir:118-151)
       const int oh = (H + 6 - 7) / 2 + 1, ow = (W + 6 - 7) / 2 + 1;

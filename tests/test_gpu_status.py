@@ -54,3 +54,29 @@ def test_forward_reports_a_pending_timeout_and_recovers():
         assert np.array_equal(out, good)
     finally:
         rt.unload()
+
+
+def test_log_and_nvtx_switches(tmp_path):
+    """NNCV_B200_LOG=1 reports the load, the activation arena and the tuning decisions on stderr; NNCV_B200_NVTX=1 wraps
+    every plan node in an NVTX range (nothing listens here: the ranges must simply cost nothing and change nothing)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import numpy as np, sys\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "from nncv_b200 import runtime as rt\n"
+        "from nncv_b200._lib import F16\n"
+        "from nncv_b200.split_params import random_input, random_state_dict, to_flat_array\n"
+        "blob = to_flat_array(18, random_state_dict(18, 0), np.float16).blob()\n"
+        "rt.load_blob('resnet18', blob, F16)\n"
+        "x = random_input(2, 64, 64, 0, 'normal').astype(np.float16)\n"
+        "y = np.zeros((2, 1000), np.float16)\n"
+        "rt.forward(y, x)\n"
+        "print('finite', bool(np.isfinite(y.astype(np.float32)).all()))\n")
+    env = dict(os.environ, NNCV_B200_LOG="1", NNCV_B200_NVTX="1")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "finite True" in r.stdout
+    assert "[nncv_b200] loaded resnet18" in r.stderr and "activation arena:" in r.stderr and "tuned conv" in r.stderr
