@@ -89,7 +89,8 @@ def test_small_mobile_module(tmp_path, compute):
         assert G.rel_l2(got, ref) <= (1e-4 if compute == F32 else 1e-2)
 
 
-@pytest.mark.parametrize("compute,n,hw", [(F32, 1, 128), (F16, 4, 224), (F16, 2, 256)])
+@pytest.mark.parametrize("compute,n,hw", [(F32, 1, (128, 128)), (F16, 4, (224, 224)), (F16, 2, (256, 256)), (F16, 1, (225, 193)),
+                                          (F32, 3, (64, 96)), (F16, 1, (33, 35))])
 def test_mobilenetv3_from_the_reference_module(tmp_path, golden_dir, compute, n, hw):
     """Plan = what the importer read from tests/Nets/MobileNetV3.mlir (210 tensor constants, 46 nodes); weights = a
     container with exactly those tensors in module order, seeded random values."""
@@ -99,7 +100,7 @@ def test_mobilenetv3_from_the_reference_module(tmp_path, golden_dir, compute, n,
     bin_path = str(tmp_path / "model.bin")
     write_model_bin(bin_path, nodes, blob)
     rt.load(plan_path, bin_path, compute)
-    x = random_input(n, hw, hw, 5, "normal")
+    x = random_input(n, hw[0], hw[1], 5, "normal")
     got = np.zeros((n, 1000), np.float32)
     rt.forward(got, x)
     ref = P.run_plan_cpu(nodes, blob, x, ob, acc64=compute == F32)
