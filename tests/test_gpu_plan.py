@@ -12,7 +12,7 @@ torch = pytest.importorskip("torch")
 from oracle import binding as ob  # noqa: E402
 from nncv_b200 import mlir_import as mi  # noqa: E402
 from nncv_b200 import runtime as rt  # noqa: E402
-from nncv_b200._lib import F16, F32, NncvError, lib  # noqa: E402
+from nncv_b200._lib import BF16, F16, F32, NncvError, lib  # noqa: E402
 from nncv_b200.memref import MemRefFlatArray  # noqa: E402
 from nncv_b200.split_params import random_input  # noqa: E402
 import gpu_util as G  # noqa: E402
@@ -90,7 +90,7 @@ def test_small_mobile_module(tmp_path, compute):
 
 
 @pytest.mark.parametrize("compute,n,hw", [(F32, 1, (128, 128)), (F16, 4, (224, 224)), (F16, 2, (256, 256)), (F16, 1, (225, 193)),
-                                          (F32, 3, (64, 96)), (F16, 1, (33, 35))])
+                                          (F32, 3, (64, 96)), (F16, 1, (33, 35)), (BF16, 2, (128, 128))])
 def test_mobilenetv3_from_the_reference_module(tmp_path, golden_dir, compute, n, hw):
     """Plan = what the importer read from tests/Nets/MobileNetV3.mlir (210 tensor constants, 46 nodes); weights = a
     container with exactly those tensors in module order, seeded random values."""
@@ -105,7 +105,8 @@ def test_mobilenetv3_from_the_reference_module(tmp_path, golden_dir, compute, n,
     rt.forward(got, x)
     ref = P.run_plan_cpu(nodes, blob, x, ob, acc64=compute == F32)
     assert np.isfinite(got).all()
-    assert G.rel_l2(got, ref) <= (1e-4 if compute == F32 else 1e-2)
+    # bf16 (8 mantissa bits) through 46 layers measures 1e-2 .. 3e-2 depending on the seed; fp16 1e-3 .. 2e-3; fp32 1e-6
+    assert G.rel_l2(got, ref) <= {F32: 1e-4, F16: 1e-2, BF16: 5e-2}[compute]
     assert (got.argmax(1) == ref.argmax(1)).all()
 
 
